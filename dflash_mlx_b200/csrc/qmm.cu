@@ -1,0 +1,587 @@
+// M<=16 int4 affine quantised matmul for sm_100a:  y[M,N] = x[M,K] . (nib*scale + bias)[N,K]^T.
+//
+// Replaces dflash_mlx/verify_qmm.py (Metal kernels `verify_mma2big`, `verify_mma2big_pipe`).
+//
+// Design (weight streaming, HBM bound):
+//   * one persistent CTA per SM: 8 consumer warps + 1 TMA producer warp;
+//   * the weight matrix is cut into units of 64 rows x (8 quantisation groups); one unit is one
+//     pipeline stage (packed nibbles via 128B-swizzled TMA boxes + its scales + its biases);
+//   * K is cut into slabs of <= 2048 columns.  A CTA works inside ONE slab, so its 16 x slabK slice of
+//     the activations is loaded once into shared memory and stays there.  The units of a slab are
+//     ordered row-tile-major and dealt out to the slab's CTAs as equal contiguous spans (stream-K),
+//     so every SM streams the same number of weight bytes;
+//   * inside a stage warp w owns quantisation group w for all 64 rows.  The packed words go straight
+//     from shared memory to registers; a nibble becomes the bf16 number 128+nib with one LOP3 (the
+//     exponent trick) and feeds mma.sync.m16n8k16 as the A operand (16 weight rows x 16 k), the
+//     activations are the B operand (16 k x 8 tokens).  The k order inside an MMA is permuted so that
+//     one 32-bit word of weights and one 128-bit load of activations line up without shuffles;
+//   * scale and bias are applied to the fp32 accumulator once per group:
+//         out += s * acc_g + (b - 128 s) * sum_{k in g} x[k]
+//     (the group sums of x come from one extra MMA against a matrix of ones), so weights enter the
+//     tensor core as exact integers and there is no per-weight FMA;
+//   * at the end of a (slab, row tile) segment the 8 warps reduce through shared memory.  If the
+//     segment is the tile's only contribution the result is stored directly; otherwise it is written
+//     as an fp32 piece to the workspace and the LAST contributor (atomic ticket) sums all pieces in a
+//     fixed order - deterministic, no inter-CTA waiting.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace dflash {
+namespace {
+
+constexpr int kBN = 64;             // weight rows per unit
+constexpr int kConsumerWarps = 8;   // = quantisation groups per unit
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;
+constexpr int kSlabKMax = 2048;
+constexpr int kXRowBytes = kSlabKMax * 2 + 16;  // +16 B: rows land on different banks
+constexpr int kXBytes = 16 * kXRowBytes;
+constexpr int kRedBytes = kConsumerWarps * 8 * 32 * 16;  // [warp][quad][lane] float4
+constexpr int kMaxSlabs = 64;
+
+struct QmmPlan {
+  int M, K, N, NT, S, maxp;
+  int slab_chunk0[kMaxSlabs + 1];
+  int slab_cta0[kMaxSlabs + 1];
+};
+
+template <int G>
+struct Cfg {
+  static constexpr int BK = 8 * G;
+  static constexpr int kWRowBytes = BK / 2;
+  static constexpr int kBoxes = kWRowBytes / 128;
+  static constexpr int kWBytes = kBN * kWRowBytes;
+  static constexpr int kSBBytes = kBN * 16;
+  static constexpr int kStageBytes = kWBytes + 2 * kSBBytes;
+  static constexpr int kStages = (G == 128) ? 3 : (G == 64 ? 6 : 8);
+  static constexpr int WPT = G / 32;  // packed words per thread per weight row
+  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kRedBytes + 8 * (2 * kStages + 1) + 16;
+};
+
+// Which weight row of a 16-row tile half a lane group reads: chosen per group size so that the
+// swizzled shared-memory reads of a quarter/half warp fall on distinct banks.
+template <int G>
+__device__ __forceinline__ int row_perm(int g) {
+  if (G == 64) return ((g & 3) << 1) | (g >> 2);
+  if (G == 128) return (g >> 1) | ((g & 1) << 2);
+  return g;
+}
+
+__device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
+  return (int)(((u + 1) * ctas - 1) / units);
+}
+
+struct SlabGeom {
+  int c0, cs, cta0, ctas;
+  long long units;
+};
+__device__ __forceinline__ SlabGeom slab_geom(const QmmPlan& p, int s) {
+  SlabGeom g;
+  g.c0 = p.slab_chunk0[s];
+  g.cs = p.slab_chunk0[s + 1] - g.c0;
+  g.cta0 = p.slab_cta0[s];
+  g.units = (long long)p.NT * g.cs;
+  long long ctas = p.slab_cta0[s + 1] - g.cta0;
+  g.ctas = (int)(ctas < g.units ? ctas : g.units);
+  return g;
+}
+// How many CTAs of slab s contribute to row tile nt, and the first of them (slab-local index).
+__device__ __forceinline__ int tile_pieces(const SlabGeom& g, int nt, int* first) {
+  int a = cta_of((long long)nt * g.cs, g.units, g.ctas);
+  int b = cta_of((long long)(nt + 1) * g.cs - 1, g.units, g.ctas);
+  *first = a;
+  return b - a + 1;
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads, 1)
+qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+                  const __grid_constant__ CUtensorMap tmB, const T* __restrict__ x, const T* __restrict__ bias,
+                  T* __restrict__ y, float4* __restrict__ pieces, unsigned* __restrict__ counters,
+                  const __grid_constant__ QmmPlan plan, int* __restrict__ err) {
+  using C = Cfg<G>;
+  using TR = MmaTraits<T>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stages = smem;
+  uint8_t* xbuf = stages + C::kStages * C::kStageBytes;
+  float4* red = (float4*)(xbuf + kXBytes);
+  uint64_t* bars = (uint64_t*)((uint8_t*)red + kRedBytes);
+  volatile int* flag = (volatile int*)(bars + 2 * C::kStages + 1);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * C::kStages, bar_x = bar_empty + 8 * C::kStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which slab, which span of its units ----
+  int s = 0;
+  while (s + 1 < plan.S && (int)blockIdx.x >= plan.slab_cta0[s + 1]) ++s;
+  const SlabGeom sg = slab_geom(plan, s);
+  const int bl = (int)blockIdx.x - sg.cta0;
+  if (bl >= sg.ctas) return;  // more CTAs than units in this slab
+  const long long u_begin = (long long)bl * sg.units / sg.ctas, u_end = (long long)(bl + 1) * sg.units / sg.ctas;
+  const int NT = plan.NT, M = plan.M, K = plan.K, N = plan.N;
+  const int slabK = sg.cs * C::BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, kConsumerWarps);
+    }
+    mbar_init(bar_x, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // =============================== producer ===============================
+    if (lane == 0) {
+      const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+      mbar_arrive_expect_tx(bar_x, (uint32_t)(M * slabK * 2));
+      for (int r = 0; r < M; ++r)
+        bulk_load_1d(smem_u32(xbuf + r * kXRowBytes), x + (size_t)r * K + (size_t)sg.c0 * C::BK, (uint32_t)(slabK * 2),
+                     bar_x);
+      int stage = 0;
+      uint32_t par = 1;
+      int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
+      for (long long u = u_begin; u < u_end; ++u) {
+        if (!mbar_wait(bar_empty + 8 * stage, par)) {
+          atomicExch(err, 1);
+          break;
+        }
+        const uint32_t full = bar_full + 8 * stage;
+        const uint32_t dst = smem_u32(stages + stage * C::kStageBytes);
+        mbar_arrive_expect_tx(full, C::kStageBytes);
+#pragma unroll
+        for (int j = 0; j < C::kBoxes; ++j)
+          tma_load_2d(dst + j * (kBN * 128), &tmW, (sg.c0 + kc) * C::kWRowBytes + 128 * j, nt * kBN, full, pol_stream);
+        tma_load_2d(dst + C::kWBytes, &tmS, (sg.c0 + kc) * 8, nt * kBN, full, pol_keep);
+        tma_load_2d(dst + C::kWBytes + C::kSBBytes, &tmB, (sg.c0 + kc) * 8, nt * kBN, full, pol_keep);
+        if (++stage == C::kStages) { stage = 0; par ^= 1; }
+        if (++kc == sg.cs) { kc = 0; ++nt; }
+      }
+    }
+    return;
+  }
+
+  // =============================== consumers ===============================
+  const int ctid = threadIdx.x;  // 0..255
+  const int g = lane >> 2, c = lane & 3;
+  const int rp = row_perm<G>(g);
+  bool aborted = false;
+
+  // rows >= M of the activation slab are zeros
+  for (int r = M; r < 16; ++r)
+    for (int i = ctid; i < slabK * 2 / 16; i += kConsumers) ((uint4*)(xbuf + r * kXRowBytes))[i] = make_uint4(0, 0, 0, 0);
+  named_bar_sync(1, kConsumers);
+  if (!mbar_wait(bar_x, 0)) { aborted = true; atomicExch(err, 2); }
+
+  float out[4][2][4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) out[t][h][j] = 0.f;
+
+  // position of this warp's group inside a stage row: box, first 16-byte chunk
+  constexpr int kGroupBytes = G / 2;
+  const int box = (warp * kGroupBytes) >> 7;
+  const int lbyte = ((warp * kGroupBytes) & 127) + c * 4 * C::WPT;  // logical byte inside the 128-byte box row
+  const int phys = ((((lbyte >> 4) ^ rp) << 4) | (lbyte & 15));     // 128B swizzle: chunk ^= (row & 7)
+
+  int stage = 0;
+  uint32_t par = 0;
+  int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
+  for (long long u = u_begin; u < u_end; ++u) {
+    if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 3); }
+    const uint8_t* st = stages + stage * C::kStageBytes;
+
+    // ---- activation fragments (B operand) of this warp's group, both token halves ----
+    uint32_t xb[2][2 * C::WPT][2];
+    float xs[2][4];
+    {
+      const uint8_t* xcol = xbuf + (size_t)(kc * C::BK + warp * G + c * 8 * C::WPT) * 2;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4* p = (const uint4*)(xcol + (g + 8 * h) * kXRowBytes);
+#pragma unroll
+        for (int i = 0; i < C::WPT; ++i) {
+          const uint4 X = p[i];
+          xb[h][2 * i][0] = prmt(X.x, X.z, 0x5410);      // (k0, k4)
+          xb[h][2 * i][1] = prmt(X.x, X.z, 0x7632);      // (k1, k5)
+          xb[h][2 * i + 1][0] = prmt(X.y, X.w, 0x5410);  // (k2, k6)
+          xb[h][2 * i + 1][1] = prmt(X.y, X.w, 0x7632);  // (k3, k7)
+        }
+        xs[h][0] = xs[h][1] = xs[h][2] = xs[h][3] = 0.f;
+#pragma unroll
+        for (int m = 0; m < 2 * C::WPT; ++m)
+          TR::mma(xs[h], TR::kOnes, TR::kOnes, TR::kOnes, TR::kOnes, xb[h][m][0], xb[h][m][1]);
+      }
+    }
+
+    const uint16_t* S16 = (const uint16_t*)(st + C::kWBytes);
+    const uint16_t* B16 = (const uint16_t*)(st + C::kWBytes + C::kSBBytes);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int r_lo = 16 * t + rp;
+      const uint8_t* wl = st + box * (kBN * 128) + r_lo * 128 + phys;
+      const uint8_t* wh = wl + 8 * 128;
+      uint32_t U[C::WPT], V[C::WPT];
+      if constexpr (C::WPT == 1) {
+        U[0] = *(const uint32_t*)wl;
+        V[0] = *(const uint32_t*)wh;
+      } else if constexpr (C::WPT == 2) {
+        const uint2 a = *(const uint2*)wl, b = *(const uint2*)wh;
+        U[0] = a.x; U[1] = a.y;
+        V[0] = b.x; V[1] = b.y;
+      } else {
+        const uint4 a = *(const uint4*)wl, b = *(const uint4*)wh;
+        U[0] = a.x; U[1] = a.y; U[2] = a.z; U[3] = a.w;
+        V[0] = b.x; V[1] = b.y; V[2] = b.z; V[3] = b.w;
+      }
+      const float s_lo = TR::bits_to_float(S16[r_lo * 8 + warp]), s_hi = TR::bits_to_float(S16[(r_lo + 8) * 8 + warp]);
+      const float b_lo = TR::bits_to_float(B16[r_lo * 8 + warp]), b_hi = TR::bits_to_float(B16[(r_lo + 8) * 8 + warp]);
+      const float bq_lo = fmaf(-TR::kMagicValue, s_lo, b_lo), bq_hi = fmaf(-TR::kMagicValue, s_hi, b_hi);
+
+      uint32_t PU[C::WPT][4], PV[C::WPT][4];
+#pragma unroll
+      for (int i = 0; i < C::WPT; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          PU[i][q] = lop3_and_or(U[i] >> (4 * q), 0x000F000Fu, TR::kMagic);  // (nib q, nib q+4) as 128+nib
+          PV[i][q] = lop3_and_or(V[i] >> (4 * q), 0x000F000Fu, TR::kMagic);
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < C::WPT; ++i) {
+          TR::mma(acc, PU[i][0], PV[i][0], PU[i][1], PV[i][1], xb[h][2 * i][0], xb[h][2 * i][1]);
+          TR::mma(acc, PU[i][2], PV[i][2], PU[i][3], PV[i][3], xb[h][2 * i + 1][0], xb[h][2 * i + 1][1]);
+        }
+        out[t][h][0] = fmaf(s_lo, acc[0], fmaf(bq_lo, xs[h][0], out[t][h][0]));
+        out[t][h][1] = fmaf(s_lo, acc[1], fmaf(bq_lo, xs[h][1], out[t][h][1]));
+        out[t][h][2] = fmaf(s_hi, acc[2], fmaf(bq_hi, xs[h][0], out[t][h][2]));
+        out[t][h][3] = fmaf(s_hi, acc[3], fmaf(bq_hi, xs[h][1], out[t][h][3]));
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+    if (++stage == C::kStages) { stage = 0; par ^= 1; }
+
+    const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
+    if (seg_end) {
+      // ---- reduce the 8 warps' partial tiles through shared memory ----
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          red[(warp * 8 + t * 2 + h) * 32 + lane] = make_float4(out[t][h][0], out[t][h][1], out[t][h][2], out[t][h][3]);
+          out[t][h][0] = out[t][h][1] = out[t][h][2] = out[t][h][3] = 0.f;
+        }
+      named_bar_sync(1, kConsumers);
+      float4 v = red[(0 * 8 + warp) * 32 + lane];
+#pragma unroll
+      for (int w2 = 1; w2 < kConsumerWarps; ++w2) {
+        const float4 a = red[(w2 * 8 + warp) * 32 + lane];
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+      }
+      // this thread now owns: quad `warp` = (tile warp>>1, token half warp&1) of lane `lane`
+      const int n_lo = nt * kBN + 16 * (warp >> 1) + rp, n_hi = n_lo + 8;
+      const int tok = 8 * (warp & 1) + 2 * c;
+
+      // pieces this row tile receives in total, and this CTA's piece index inside its slab
+      int total = 0, first_here = 0;
+      for (int s2 = lane; s2 < plan.S; s2 += 32) {
+        const SlabGeom g2 = slab_geom(plan, s2);
+        int f;
+        total += tile_pieces(g2, nt, &f);
+      }
+      total = __reduce_add_sync(0xffffffffu, total);
+      tile_pieces(sg, nt, &first_here);
+
+      bool do_store = true;
+      if (total > 1) {
+        const size_t slot = ((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid;
+        pieces[slot] = v;
+        __threadfence();
+        named_bar_sync(1, kConsumers);
+        if (ctid == 0) {
+          const unsigned old = atomicAdd(&counters[nt], 1u);
+          *flag = (old == (unsigned)(total - 1));
+        }
+        named_bar_sync(1, kConsumers);
+        do_store = (*flag != 0);
+        if (do_store) {
+          __threadfence();
+          v = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s2 = 0; s2 < plan.S; ++s2) {
+            const SlabGeom g2 = slab_geom(plan, s2);
+            int f;
+            const int np = tile_pieces(g2, nt, &f);
+            for (int p = 0; p < np; ++p) {
+              const float4 a = ld_cg_f4(&pieces[((size_t)(s2 * plan.maxp + p) * NT + nt) * kConsumers + ctid]);
+              v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+          }
+          if (ctid == 0) counters[nt] = 0;  // ready for the next launch
+        }
+      }
+      if (do_store) {
+        float bl0 = 0.f, bh0 = 0.f;
+        if (bias != nullptr) {
+          if (n_lo < N) bl0 = TR::to_float(bias[n_lo]);
+          if (n_hi < N) bh0 = TR::to_float(bias[n_hi]);
+        }
+        if (n_lo < N) {
+          if (tok < M) y[(size_t)tok * N + n_lo] = TR::from_float(v.x + bl0);
+          if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_lo] = TR::from_float(v.y + bl0);
+        }
+        if (n_hi < N) {
+          if (tok < M) y[(size_t)tok * N + n_hi] = TR::from_float(v.z + bh0);
+          if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_hi] = TR::from_float(v.w + bh0);
+        }
+      }
+      named_bar_sync(1, kConsumers);  // `red` and `flag` are free again
+    }
+    if (++kc == sg.cs) { kc = 0; ++nt; }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// General kernel: any K % 32 == 0, K % G == 0, any N, any alignment of the row starts.  One warp per
+// output column; exact fp32 dequantisation.  Used for shapes the streaming kernel does not take.
+template <typename T>
+__global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq,
+                                                          const T* __restrict__ scales, const T* __restrict__ biases,
+                                                          const T* __restrict__ bias, T* __restrict__ y, int M, int K,
+                                                          int N, int G) {
+  using TR = MmaTraits<T>;
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= N) return;
+  float acc[16];
+#pragma unroll
+  for (int m = 0; m < 16; ++m) acc[m] = 0.f;
+  const int words = K / 8, groups = K / G;
+  for (int j = lane; j < words; j += 32) {
+    const uint32_t w = wq[(size_t)n * words + j];
+    const int grp = (j * 8) / G;
+    const float s = TR::to_float(scales[(size_t)n * groups + grp]), b = TR::to_float(biases[(size_t)n * groups + grp]);
+    float wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[i] = fmaf((float)((w >> (4 * i)) & 0xF), s, b);
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      if (m < M) {
+        const T* xr = x + (size_t)m * K + j * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[m] = fmaf(TR::to_float(xr[i]), wv[i], acc[m]);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < 16; ++m) {
+    float v = acc[m];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0 && m < M) y[(size_t)m * N + n] = TR::from_float(v + (bias ? TR::to_float(bias[n]) : 0.f));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+int g_max_blocks = 0;
+
+bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
+  const int BK = 8 * G;
+  const int C = K / BK;
+  const int csmax = kSlabKMax / BK;
+  p->M = M; p->K = K; p->N = N;
+  p->NT = (N + kBN - 1) / kBN;
+  p->S = (C + csmax - 1) / csmax;
+  if (p->S > kMaxSlabs) return false;
+  for (int i = 0; i <= p->S; ++i) p->slab_chunk0[i] = (int)((long long)i * C / p->S);
+  const long long U = (long long)p->NT * C;
+  long long grid = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
+  if (grid > U) grid = U;
+  if (grid < p->S) grid = p->S;
+  for (int i = 0; i <= p->S; ++i) p->slab_cta0[i] = (int)(grid * p->slab_chunk0[i] / C);
+  for (int i = 1; i <= p->S; ++i)
+    if (p->slab_cta0[i] < p->slab_cta0[i - 1] + 1) p->slab_cta0[i] = p->slab_cta0[i - 1] + 1;
+  p->slab_cta0[p->S] = (int)grid;
+  for (int i = p->S - 1; i >= 1; --i)
+    if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 1) p->slab_cta0[i] = p->slab_cta0[i + 1] - 1;
+  int maxp = 1;
+  for (int i = 0; i < p->S; ++i) {
+    const int cs = p->slab_chunk0[i + 1] - p->slab_chunk0[i];
+    const long long Us = (long long)p->NT * cs;
+    long long ctas = p->slab_cta0[i + 1] - p->slab_cta0[i];
+    if (ctas > Us) ctas = Us;
+    const long long L = Us / ctas;
+    const int mp = (int)((cs - 1 + L - 1) / L) + 1;
+    if (cs > 1 && mp > maxp) maxp = mp;
+  }
+  p->maxp = maxp;
+  return true;
+}
+
+size_t counters_bytes(int NT) { return ((size_t)NT * 4 + 255) & ~(size_t)255; }
+size_t plan_workspace(const QmmPlan& p) {
+  return counters_bytes(p.NT) + (size_t)p.S * p.maxp * p.NT * kConsumers * sizeof(float4);
+}
+
+bool fast_path_ok(const void* x, const void* wq, const void* sc, const void* bi, int K, int G) {
+  if (K % (8 * G) != 0) return false;
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  return al(x) && al(wq) && al(sc) && al(bi);
+}
+
+struct MapKey {
+  const void* p; int rows, inner, kind;
+  bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && inner == o.inner && kind == o.kind; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.inner * 7919u) ^ (size_t)k.kind;
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// kind 0: packed weights, uint8 [rows, inner bytes], box 128 x 64, 128B swizzle.
+// kind 1: scales / biases, uint16 [rows, inner elements], box 8 x 64, no swizzle.
+bool get_map(const void* ptr, int rows, int inner, int kind, CUtensorMap* out) {
+  MapKey key{ptr, rows, inner, kind};
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return true; }
+  }
+  tensormap_encode_fn enc = get_tensormap_encoder();
+  if (!enc) return false;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r;
+  if (kind == 0) {
+    cuuint64_t strides[1] = {(cuuint64_t)inner};
+    cuuint32_t box[2] = {128, (cuuint32_t)kBN};
+    r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
+    cuuint32_t box[2] = {8, (cuuint32_t)kBN};
+    r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d) rows=%d inner=%d kind=%d", (int)r, rows, inner, kind);
+    return false;
+  }
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  if (g_maps.size() > 16384) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+template <typename T, int G>
+int launch_stream(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y,
+                  const QmmPlan& plan, void* ws, cudaStream_t st, int device) {
+  using C = Cfg<G>;
+  CUtensorMap tw, ts, tb;
+  if (!get_map(wq, plan.N, plan.K / 2, 0, &tw) || !get_map(sc, plan.N, plan.K / G, 1, &ts) ||
+      !get_map(bi, plan.N, plan.K / G, 1, &tb))
+    return DFLASH_ERR_LAUNCH;
+  auto kern = qmm_stream_kernel<T, G>;
+  static bool attr_done[64] = {};
+  if (!attr_done[device & 63]) {
+    cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+    if (e0 != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e0));
+    attr_done[device & 63] = true;
+  }
+  cudaError_t e;
+  unsigned* counters = (unsigned*)ws;
+  float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
+  const int grid = plan.slab_cta0[plan.S];
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tw, ts, tb, (const T*)x, (const T*)bias, (T*)y, pieces, counters, plan,
+                                              device_error_word(device));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm launch: %s", cudaGetErrorString(e));
+  return DFLASH_OK;
+}
+
+template <typename T>
+int launch_any(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K,
+               int N, int G, void* ws, size_t ws_bytes, cudaStream_t st) {
+  int device = 0;
+  cudaGetDevice(&device);
+  QmmPlan plan;
+  if (fast_path_ok(x, wq, sc, bi, K, G) && make_plan(M, K, N, G, device, &plan)) {
+    const size_t need = plan_workspace(plan);
+    if (ws == nullptr || ws_bytes < need)
+      return fail(DFLASH_ERR_WORKSPACE, "verify_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
+    if (((uintptr_t)ws & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+    switch (G) {
+      case 32: return launch_stream<T, 32>(x, wq, sc, bi, bias, y, plan, ws, st, device);
+      case 64: return launch_stream<T, 64>(x, wq, sc, bi, bias, y, plan, ws, st, device);
+      default: return launch_stream<T, 128>(x, wq, sc, bi, bias, y, plan, ws, st, device);
+    }
+  }
+  qmm_general_kernel<T><<<(N + 7) / 8, 256, 0, st>>>((const T*)x, (const uint32_t*)wq, (const T*)sc, (const T*)bi,
+                                                     (const T*)bias, (T*)y, M, K, N, G);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm general launch: %s", cudaGetErrorString(e));
+  return DFLASH_OK;
+}
+
+}  // namespace
+}  // namespace dflash
+
+using namespace dflash;
+
+extern "C" void dflash_verify_qmm_set_max_blocks(int max_blocks) { g_max_blocks = max_blocks < 0 ? 0 : max_blocks; }
+
+extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int group_size) {
+  if (M < 1 || K < 1 || N < 1 || (group_size != 32 && group_size != 64 && group_size != 128)) return 0;
+  if (K % (8 * group_size) != 0) return 256;  // general kernel: no workspace (a token amount keeps callers uniform)
+  int device = 0;
+  cudaGetDevice(&device);
+  QmmPlan plan;
+  if (!make_plan(M, K, N, group_size, device, &plan)) return 256;
+  return plan_workspace(plan);
+}
+
+extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,
+                                 const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w_q || !scales || !biases || !y) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm: null operand");
+  if (M < 1 || M > 16) return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm: M=%d outside 1..16", M);
+  if (group_size != 32 && group_size != 64 && group_size != 128)
+    return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm: group_size=%d not in {32,64,128}", group_size);
+  if (K < group_size || K % group_size != 0 || K % 32 != 0 || N < 1)
+    return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm: K=%d N=%d not supported (K %% G == 0, K %% 32 == 0)", K, N);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DFLASH_BF16)
+    return launch_any<__nv_bfloat16>(x, w_q, scales, biases, bias, y, M, K, N, group_size, workspace, workspace_bytes, st);
+  if (dtype == DFLASH_F16)
+    return launch_any<__half>(x, w_q, scales, biases, bias, y, M, K, N, group_size, workspace, workspace_bytes, st);
+  return fail(DFLASH_ERR_BAD_ARG, "verify_qmm: dtype %d (want bf16 or f16)", dtype);
+}
+
+extern "C" int dflash_verify_qmm_plan(int M, int K, int N, int group_size, int* out, int capacity) {
+  if (!out || (group_size != 32 && group_size != 64 && group_size != 128) || K % (8 * group_size) != 0)
+    return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_plan: bad arguments");
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); device = 0; }
+  QmmPlan p;
+  if (!make_plan(M, K, N, group_size, device, &p)) return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm_plan: too many K slabs");
+  const int need = 4 + 2 * (p.S + 1);
+  if (capacity < need) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_plan: capacity %d < %d", capacity, need);
+  out[0] = p.NT; out[1] = p.S; out[2] = p.maxp; out[3] = p.slab_cta0[p.S];
+  for (int i = 0; i <= p.S; ++i) { out[4 + i] = p.slab_chunk0[i]; out[4 + p.S + 1 + i] = p.slab_cta0[i]; }
+  return need;
+}
