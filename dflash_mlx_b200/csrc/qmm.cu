@@ -40,6 +40,7 @@ constexpr int kXRowBytes = kSlabKMax * 2 + 16;  // +16 B: rows land on different
 constexpr int kXBytes = 16 * kXRowBytes;
 constexpr int kRedBytes = kConsumerWarps * 8 * 32 * 16;  // [warp][quad][lane] float4
 constexpr int kMaxSlabs = 64;
+constexpr int kMaxRowTiles = 16384;  // ticket counters kept in a fixed prefix of the workspace
 
 struct QmmPlan {
   int M, K, N, NT, S, maxp;
@@ -69,30 +70,74 @@ __device__ __forceinline__ int row_perm(int g) {
   return g;
 }
 
-__device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
-  return (int)(((u + 1) * ctas - 1) / units);
+// Which CTA of a slab owns unit u when `units` units are dealt out as equal contiguous spans.  The host
+// guarantees (units + 1) * ctas < 2^31, so 32-bit arithmetic is exact.
+__device__ __forceinline__ int cta_of(unsigned u, unsigned units, unsigned ctas) {
+  return (int)(((u + 1u) * ctas - 1u) / units);
 }
 
 struct SlabGeom {
   int c0, cs, cta0, ctas;
-  long long units;
+  unsigned units;
 };
 __device__ __forceinline__ SlabGeom slab_geom(const QmmPlan& p, int s) {
   SlabGeom g;
   g.c0 = p.slab_chunk0[s];
   g.cs = p.slab_chunk0[s + 1] - g.c0;
   g.cta0 = p.slab_cta0[s];
-  g.units = (long long)p.NT * g.cs;
-  long long ctas = p.slab_cta0[s + 1] - g.cta0;
+  g.units = (unsigned)p.NT * (unsigned)g.cs;
+  const unsigned ctas = (unsigned)(p.slab_cta0[s + 1] - g.cta0);
   g.ctas = (int)(ctas < g.units ? ctas : g.units);
   return g;
 }
 // How many CTAs of slab s contribute to row tile nt, and the first of them (slab-local index).
 __device__ __forceinline__ int tile_pieces(const SlabGeom& g, int nt, int* first) {
-  int a = cta_of((long long)nt * g.cs, g.units, g.ctas);
-  int b = cta_of((long long)(nt + 1) * g.cs - 1, g.units, g.ctas);
+  int a = cta_of((unsigned)nt * g.cs, g.units, g.ctas);
+  int b = cta_of((unsigned)(nt + 1) * g.cs - 1u, g.units, g.ctas);
   *first = a;
   return b - a + 1;
+}
+
+// Output element ownership after the cross-warp reduction: consumer thread (warp, lane) holds, for row
+// tile nt, weight rows n_lo = 64 nt + 16 (warp>>1) + rp and n_lo + 8, tokens tok = 8 (warp&1) + 2 c and tok+1.
+template <typename T>
+__device__ __forceinline__ void store_tile(const float4& v, T* __restrict__ y, const T* __restrict__ bias, int nt,
+                                           int warp, int rp, int c, int M, int N) {
+  using TR = MmaTraits<T>;
+  const int n_lo = nt * kBN + 16 * (warp >> 1) + rp, n_hi = n_lo + 8;
+  const int tok = 8 * (warp & 1) + 2 * c;
+  float bl0 = 0.f, bh0 = 0.f;
+  if (bias != nullptr) {
+    if (n_lo < N) bl0 = TR::to_float(bias[n_lo]);
+    if (n_hi < N) bh0 = TR::to_float(bias[n_hi]);
+  }
+  if (n_lo < N) {
+    if (tok < M) y[(size_t)tok * N + n_lo] = TR::from_float(v.x + bl0);
+    if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_lo] = TR::from_float(v.y + bl0);
+  }
+  if (n_hi < N) {
+    if (tok < M) y[(size_t)tok * N + n_hi] = TR::from_float(v.z + bh0);
+    if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_hi] = TR::from_float(v.w + bh0);
+  }
+}
+
+// Run by the CTA that took the last ticket of row tile nt: sum the fp32 pieces in a fixed order.
+template <typename T>
+__device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pieces, unsigned* counters,
+                                           T* __restrict__ y, const T* __restrict__ bias, int nt, int ctid, int warp,
+                                           int rp, int c) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s2 = 0; s2 < plan.S; ++s2) {
+    const SlabGeom g2 = slab_geom(plan, s2);
+    int f;
+    const int np = tile_pieces(g2, nt, &f);
+    for (int p = 0; p < np; ++p) {
+      const float4 a = ld_cg_f4(&pieces[((size_t)(s2 * plan.maxp + p) * plan.NT + nt) * kConsumers + ctid]);
+      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+  }
+  if (ctid == 0) counters[nt] = 0;  // ready for the next launch
+  store_tile<T>(v, y, bias, nt, warp, rp, c, plan.M, plan.N);
 }
 
 template <typename T, int G>
@@ -120,7 +165,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const SlabGeom sg = slab_geom(plan, s);
   const int bl = (int)blockIdx.x - sg.cta0;
   if (bl >= sg.ctas) return;  // more CTAs than units in this slab
-  const long long u_begin = (long long)bl * sg.units / sg.ctas, u_end = (long long)(bl + 1) * sg.units / sg.ctas;
+  const unsigned u_begin = (unsigned)bl * sg.units / sg.ctas, u_end = (unsigned)(bl + 1) * sg.units / sg.ctas;
   const int NT = plan.NT, M = plan.M, K = plan.K, N = plan.N;
   const int slabK = sg.cs * C::BK;
 
@@ -145,7 +190,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       int stage = 0;
       uint32_t par = 1;
       int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
-      for (long long u = u_begin; u < u_end; ++u) {
+      for (unsigned u = u_begin; u < u_end; ++u) {
         if (!mbar_wait(bar_empty + 8 * stage, par)) {
           atomicExch(err, 1);
           break;
@@ -170,6 +215,8 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const int g = lane >> 2, c = lane & 3;
   const int rp = row_perm<G>(g);
   bool aborted = false;
+  int pend_nt = -1, pend_total = 0;  // a row tile whose ticket has been taken but not yet looked at
+  unsigned pend_ticket = 0;
 
   // rows >= M of the activation slab are zeros
   for (int r = M; r < 16; ++r)
@@ -194,7 +241,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   int stage = 0;
   uint32_t par = 0;
   int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
-  for (long long u = u_begin; u < u_end; ++u) {
+  for (unsigned u = u_begin; u < u_end; ++u) {
     if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 3); }
     const uint8_t* st = stages + stage * C::kStageBytes;
 
@@ -273,6 +320,13 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
     const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
     if (seg_end) {
+      // A ticket taken at the previous segment end has long since returned: publish whether this CTA was
+      // the last contributor of that tile (the barrier below makes `flag` visible).
+      if (pend_nt >= 0 && ctid == 0) {
+        const int last = (pend_ticket == (unsigned)(pend_total - 1));
+        if (last) __threadfence();
+        *flag = last;
+      }
       // ---- reduce the 8 warps' partial tiles through shared memory ----
 #pragma unroll
       for (int t = 0; t < 4; ++t)
@@ -288,10 +342,6 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const float4 a = red[(w2 * 8 + warp) * 32 + lane];
         v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
       }
-      // this thread now owns: quad `warp` = (tile warp>>1, token half warp&1) of lane `lane`
-      const int n_lo = nt * kBN + 16 * (warp >> 1) + rp, n_hi = n_lo + 8;
-      const int tok = 8 * (warp & 1) + 2 * c;
-
       // pieces this row tile receives in total, and this CTA's piece index inside its slab
       int total = 0, first_here = 0;
       for (int s2 = lane; s2 < plan.S; s2 += 32) {
@@ -302,51 +352,34 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       total = __reduce_add_sync(0xffffffffu, total);
       tile_pieces(sg, nt, &first_here);
 
-      bool do_store = true;
       if (total > 1) {
-        const size_t slot = ((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid;
-        pieces[slot] = v;
-        __threadfence();
-        named_bar_sync(1, kConsumers);
+        pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid] = v;
+      } else {
+        store_tile<T>(v, y, bias, nt, warp, rp, c, M, N);
+      }
+      if (pend_nt >= 0 && *flag) finalize_tile<T>(plan, pieces, counters, y, bias, pend_nt, ctid, warp, rp, c);
+      named_bar_sync(1, kConsumers);  // every piece store is issued; `red` and `flag` are free again
+      if (total > 1) {
         if (ctid == 0) {
-          const unsigned old = atomicAdd(&counters[nt], 1u);
-          *flag = (old == (unsigned)(total - 1));
+          __threadfence();  // cumulative: orders the whole CTA's piece stores (seen through the barrier) before the ticket
+          pend_ticket = atomicAdd(&counters[nt], 1u);
         }
-        named_bar_sync(1, kConsumers);
-        do_store = (*flag != 0);
-        if (do_store) {
-          __threadfence();
-          v = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s2 = 0; s2 < plan.S; ++s2) {
-            const SlabGeom g2 = slab_geom(plan, s2);
-            int f;
-            const int np = tile_pieces(g2, nt, &f);
-            for (int p = 0; p < np; ++p) {
-              const float4 a = ld_cg_f4(&pieces[((size_t)(s2 * plan.maxp + p) * NT + nt) * kConsumers + ctid]);
-              v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-            }
-          }
-          if (ctid == 0) counters[nt] = 0;  // ready for the next launch
-        }
+        pend_nt = nt;
+        pend_total = total;
+      } else {
+        pend_nt = -1;
       }
-      if (do_store) {
-        float bl0 = 0.f, bh0 = 0.f;
-        if (bias != nullptr) {
-          if (n_lo < N) bl0 = TR::to_float(bias[n_lo]);
-          if (n_hi < N) bh0 = TR::to_float(bias[n_hi]);
-        }
-        if (n_lo < N) {
-          if (tok < M) y[(size_t)tok * N + n_lo] = TR::from_float(v.x + bl0);
-          if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_lo] = TR::from_float(v.y + bl0);
-        }
-        if (n_hi < N) {
-          if (tok < M) y[(size_t)tok * N + n_hi] = TR::from_float(v.z + bh0);
-          if (tok + 1 < M) y[(size_t)(tok + 1) * N + n_hi] = TR::from_float(v.w + bh0);
-        }
-      }
-      named_bar_sync(1, kConsumers);  // `red` and `flag` are free again
     }
     if (++kc == sg.cs) { kc = 0; ++nt; }
+  }
+  if (pend_nt >= 0) {
+    if (ctid == 0) {
+      const int last = (pend_ticket == (unsigned)(pend_total - 1));
+      if (last) __threadfence();
+      *flag = last;
+    }
+    named_bar_sync(1, kConsumers);
+    if (*flag) finalize_tile<T>(plan, pieces, counters, y, bias, pend_nt, ctid, warp, rp, c);
   }
 }
 
@@ -400,7 +433,7 @@ bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
   p->M = M; p->K = K; p->N = N;
   p->NT = (N + kBN - 1) / kBN;
   p->S = (C + csmax - 1) / csmax;
-  if (p->S > kMaxSlabs) return false;
+  if (p->S > kMaxSlabs || p->NT > kMaxRowTiles) return false;
   for (int i = 0; i <= p->S; ++i) p->slab_chunk0[i] = (int)((long long)i * C / p->S);
   const long long U = (long long)p->NT * C;
   long long grid = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
@@ -421,12 +454,15 @@ bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
     const long long L = Us / ctas;
     const int mp = (int)((cs - 1 + L - 1) / L) + 1;
     if (cs > 1 && mp > maxp) maxp = mp;
+    if ((Us + 1) * (p->slab_cta0[i + 1] - p->slab_cta0[i]) >= (1ll << 31)) return false;
   }
   p->maxp = maxp;
   return true;
 }
 
-size_t counters_bytes(int NT) { return ((size_t)NT * 4 + 255) & ~(size_t)255; }
+// The ticket counters sit in a fixed-size prefix of the workspace, so that the bytes they occupy never
+// hold anything else (the workspace is zero-filled once and shared by calls of every shape).
+size_t counters_bytes(int) { return (size_t)kMaxRowTiles * 4; }
 size_t plan_workspace(const QmmPlan& p) {
   return counters_bytes(p.NT) + (size_t)p.S * p.maxp * p.NT * kConsumers * sizeof(float4);
 }
