@@ -34,12 +34,10 @@ namespace {
 constexpr int kBN = 64;             // weight rows per unit
 constexpr int kConsumerWarps = 8;   // = quantisation groups per unit
 constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;
-constexpr int kSlabKMax = 2048;
-constexpr int kXRowBytes = kSlabKMax * 2 + 16;  // +16 B: rows land on different banks
-constexpr int kXBytes = 16 * kXRowBytes;
-constexpr int kRedBytes = kConsumerWarps * 8 * 32 * 16;  // [warp][quad][lane] float4
+constexpr int kThreads = 2 * kConsumers;  // two workers of 8 warps; thread 0 of a worker also issues its TMA loads
+constexpr int kRedBytes = 4 * 8 * 32 * 16;     // per worker: [4 warps][quad][lane] float4
 constexpr int kMaxSlabs = 64;
+constexpr int kMaxPend = 32;  // partial tiles a worker may hold before it takes their tickets
 constexpr int kMaxRowTiles = 16384;  // ticket counters kept in a fixed prefix of the workspace
 
 struct QmmPlan {
@@ -56,9 +54,13 @@ struct Cfg {
   static constexpr int kWBytes = kBN * kWRowBytes;
   static constexpr int kSBBytes = kBN * 16;
   static constexpr int kStageBytes = kWBytes + 2 * kSBBytes;
-  static constexpr int kStages = (G == 128) ? 3 : (G == 64 ? 6 : 8);
+  static constexpr int kStages = (G == 128) ? 2 : (G == 64 ? 3 : 5);  // per worker
   static constexpr int WPT = G / 32;  // packed words per thread per weight row
-  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kRedBytes + 8 * (2 * kStages + 1) + 16;
+  static constexpr int kSlabKMax = (G == 128) ? 1024 : 2048;
+  static constexpr int kXRowBytes = kSlabKMax * 2 + 16;  // +16 B: rows land on different banks
+  static constexpr int kXBytes = 16 * kXRowBytes;
+  static constexpr size_t kSmemBytes =
+      1024 + (size_t)2 * kStages * kStageBytes + kXBytes + 2 * kRedBytes + 8 * (4 * kStages + 1) + 2 * 3 * kMaxPend * 4;
 };
 
 // Which weight row of a 16-row tile half a lane group reads: chosen per group size so that the
@@ -150,78 +152,113 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   using TR = MmaTraits<T>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* stages = smem;
-  uint8_t* xbuf = stages + C::kStages * C::kStageBytes;
-  float4* red = (float4*)(xbuf + kXBytes);
-  uint64_t* bars = (uint64_t*)((uint8_t*)red + kRedBytes);
-  volatile int* flag = (volatile int*)(bars + 2 * C::kStages + 1);
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * C::kStages, bar_x = bar_empty + 8 * C::kStages;
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Two independent workers share the CTA (and its activation slab): warps 0-7 are worker 0, warps 8-15
+  // worker 1.  Each owns a span of units, a ring of stages and its barriers; its first thread issues the
+  // TMA loads (kStages-1 units ahead), so all 16 warps compute and each SM sub-partition holds 4 warps.
+  const int worker = warp >> 3;
+  const int wwarp = warp & 7;  // warp index inside the worker
 
-  // ---- which slab, which span of its units ----
+  uint8_t* stages = smem + (size_t)worker * C::kStages * C::kStageBytes;
+  uint8_t* xbuf = smem + (size_t)2 * C::kStages * C::kStageBytes;
+  float4* red = (float4*)(xbuf + C::kXBytes + (size_t)worker * kRedBytes);
+  uint64_t* bars = (uint64_t*)(xbuf + C::kXBytes + 2 * kRedBytes);
+  volatile int* pend = (volatile int*)(bars + 4 * C::kStages + 1) + worker * 3 * kMaxPend;  // [nt | total | last]
+  const uint32_t bar_full = smem_u32(bars) + worker * 16 * C::kStages, bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_x = smem_u32(bars) + 32 * C::kStages;
+
+  // ---- which slab, which span of its units (virtual CTA = 2 * blockIdx.x + worker) ----
+  const int vcta = 2 * (int)blockIdx.x + worker;
   int s = 0;
-  while (s + 1 < plan.S && (int)blockIdx.x >= plan.slab_cta0[s + 1]) ++s;
+  while (s + 1 < plan.S && 2 * (int)blockIdx.x >= plan.slab_cta0[s + 1]) ++s;  // slab starts are even
   const SlabGeom sg = slab_geom(plan, s);
-  const int bl = (int)blockIdx.x - sg.cta0;
-  if (bl >= sg.ctas) return;  // more CTAs than units in this slab
-  const unsigned u_begin = (unsigned)bl * sg.units / sg.ctas, u_end = (unsigned)(bl + 1) * sg.units / sg.ctas;
+  const int bl = vcta - sg.cta0;
+  const bool has_work = bl < sg.ctas;
+  if (2 * (int)blockIdx.x - sg.cta0 >= sg.ctas) return;  // neither worker has units
+  const unsigned u_begin = has_work ? (unsigned)bl * sg.units / sg.ctas : 0u;
+  const unsigned u_end = has_work ? (unsigned)(bl + 1) * sg.units / sg.ctas : 0u;
   const int NT = plan.NT, M = plan.M, K = plan.K, N = plan.N;
   const int slabK = sg.cs * C::BK;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::kStages; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, kConsumerWarps);
-    }
+    for (int w = 0; w < 2; ++w)
+      for (int i = 0; i < C::kStages; ++i) {
+        mbar_init(smem_u32(bars) + w * 16 * C::kStages + 8 * i, 1);                                   // full
+        mbar_init(smem_u32(bars) + w * 16 * C::kStages + 8 * C::kStages + 8 * i, kConsumerWarps);     // empty
+      }
     mbar_init(bar_x, 1);
     mbar_fence_init();
   }
   __syncthreads();
 
-  if (warp == kConsumerWarps) {
-    // =============================== producer ===============================
-    if (lane == 0) {
-      const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-      mbar_arrive_expect_tx(bar_x, (uint32_t)(M * slabK * 2));
-      for (int r = 0; r < M; ++r)
-        bulk_load_1d(smem_u32(xbuf + r * kXRowBytes), x + (size_t)r * K + (size_t)sg.c0 * C::BK, (uint32_t)(slabK * 2),
-                     bar_x);
-      int stage = 0;
-      uint32_t par = 1;
-      int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
-      for (unsigned u = u_begin; u < u_end; ++u) {
-        if (!mbar_wait(bar_empty + 8 * stage, par)) {
-          atomicExch(err, 1);
-          break;
-        }
-        const uint32_t full = bar_full + 8 * stage;
-        const uint32_t dst = smem_u32(stages + stage * C::kStageBytes);
-        mbar_arrive_expect_tx(full, C::kStageBytes);
-#pragma unroll
-        for (int j = 0; j < C::kBoxes; ++j)
-          tma_load_2d(dst + j * (kBN * 128), &tmW, (sg.c0 + kc) * C::kWRowBytes + 128 * j, nt * kBN, full, pol_stream);
-        tma_load_2d(dst + C::kWBytes, &tmS, (sg.c0 + kc) * 8, nt * kBN, full, pol_keep);
-        tma_load_2d(dst + C::kWBytes + C::kSBBytes, &tmB, (sg.c0 + kc) * 8, nt * kBN, full, pol_keep);
-        if (++stage == C::kStages) { stage = 0; par ^= 1; }
-        if (++kc == sg.cs) { kc = 0; ++nt; }
-      }
-    }
-    return;
-  }
-
   // =============================== consumers ===============================
-  const int ctid = threadIdx.x;  // 0..255
+  const int ctid = threadIdx.x & (kConsumers - 1);  // 0..255 inside the worker
   const int g = lane >> 2, c = lane & 3;
   const int rp = row_perm<G>(g);
+  const int bar_id = 1 + worker;
   bool aborted = false;
-  int pend_nt = -1, pend_total = 0;  // a row tile whose ticket has been taken but not yet looked at
-  unsigned pend_ticket = 0;
+  // Row tiles for which this worker has written a partial tile but not yet taken its ticket.  Tickets are
+  // taken in batches (one gpu-scope fence per batch, normally one per kernel at the end of the span, when no
+  // loads are in flight), by a thread that does not issue TMA loads.
+  int npend = 0;
+  auto flush_tickets = [&]() {
+    named_bar_sync(bar_id, kConsumers);  // every pending partial-tile store has been issued
+    if (ctid == 32) {
+      __threadfence();  // cumulative over the worker's stores (observed through the barrier)
+      for (int i0 = 0; i0 < npend; i0 += 8) {  // 8 tickets in flight at a time
+        unsigned t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (i0 + j < npend) t[j] = atomicAdd(&counters[pend[i0 + j]], 1u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (i0 + j < npend) pend[2 * kMaxPend + i0 + j] = (t[j] == (unsigned)(pend[kMaxPend + i0 + j] - 1));
+      }
+      __threadfence();
+    }
+    named_bar_sync(bar_id, kConsumers);
+    for (int i = 0; i < npend; ++i)
+      if (pend[2 * kMaxPend + i]) finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c);
+    named_bar_sync(bar_id, kConsumers);
+  };
 
-  // rows >= M of the activation slab are zeros
+  // ---- TMA issue (thread 0 of the worker): the classic producer sequence, run kStages-1 units ahead ----
+  const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+  int pstage = 0, pnt = (int)(u_begin / sg.cs), pkc = (int)(u_begin % sg.cs);
+  uint32_t ppar = 1;
+  unsigned pu = u_begin;
+  auto issue_one = [&]() {
+    if (pu >= u_end) return;
+    if (!mbar_wait(bar_empty + 8 * pstage, ppar)) { atomicExch(err, 1); pu = u_end; return; }
+    const uint32_t full = bar_full + 8 * pstage;
+    const uint32_t dst = smem_u32(stages + pstage * C::kStageBytes);
+    mbar_arrive_expect_tx(full, C::kStageBytes);
+#pragma unroll
+    for (int j = 0; j < C::kBoxes; ++j)
+      tma_load_2d(dst + j * (kBN * 128), &tmW, (sg.c0 + pkc) * C::kWRowBytes + 128 * j, pnt * kBN, full, pol_stream);
+    tma_load_2d(dst + C::kWBytes, &tmS, (sg.c0 + pkc) * 8, pnt * kBN, full, pol_keep);
+    tma_load_2d(dst + C::kWBytes + C::kSBBytes, &tmB, (sg.c0 + pkc) * 8, pnt * kBN, full, pol_keep);
+    if (++pstage == C::kStages) { pstage = 0; ppar ^= 1; }
+    if (++pkc == sg.cs) { pkc = 0; ++pnt; }
+    ++pu;
+  };
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(bar_x, (uint32_t)(M * slabK * 2));
+    for (int r = 0; r < M; ++r)
+      bulk_load_1d(smem_u32(xbuf + r * C::kXRowBytes), x + (size_t)r * K + (size_t)sg.c0 * C::BK,
+                   (uint32_t)(slabK * 2), bar_x);
+  }
+  if (ctid == 0) {
+#pragma unroll 1
+    for (int j = 0; j < C::kStages - 1; ++j) issue_one();
+  }
+
+  // rows >= M of the activation slab are zeros (all 512 threads take part)
   for (int r = M; r < 16; ++r)
-    for (int i = ctid; i < slabK * 2 / 16; i += kConsumers) ((uint4*)(xbuf + r * kXRowBytes))[i] = make_uint4(0, 0, 0, 0);
-  named_bar_sync(1, kConsumers);
+    for (int i = threadIdx.x; i < slabK * 2 / 16; i += 2 * kConsumers)
+      ((uint4*)(xbuf + r * C::kXRowBytes))[i] = make_uint4(0, 0, 0, 0);
+  named_bar_sync(3, 2 * kConsumers);
+  if (!has_work) return;
   if (!mbar_wait(bar_x, 0)) { aborted = true; atomicExch(err, 2); }
 
   float out[4][2][4];
@@ -234,14 +271,16 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   // position of this warp's group inside a stage row: box, first 16-byte chunk
   constexpr int kGroupBytes = G / 2;
-  const int box = (warp * kGroupBytes) >> 7;
-  const int lbyte = ((warp * kGroupBytes) & 127) + c * 4 * C::WPT;  // logical byte inside the 128-byte box row
-  const int phys = ((((lbyte >> 4) ^ rp) << 4) | (lbyte & 15));     // 128B swizzle: chunk ^= (row & 7)
+  const int box = (wwarp * kGroupBytes) >> 7;
+  const int lbyte = ((wwarp * kGroupBytes) & 127) + c * 4 * C::WPT;  // logical byte inside the 128-byte box row
+  const int phys = ((((lbyte >> 4) ^ rp) << 4) | (lbyte & 15));      // 128B swizzle: chunk ^= (row & 7)
 
   int stage = 0;
   uint32_t par = 0;
   int nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
   for (unsigned u = u_begin; u < u_end; ++u) {
+    if (ctid == 0) issue_one();  // refills the stage that unit u-1 used
+    __syncwarp();
     if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 3); }
     const uint8_t* st = stages + stage * C::kStageBytes;
 
@@ -249,10 +288,10 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     uint32_t xb[2][2 * C::WPT][2];
     float xs[2][4];
     {
-      const uint8_t* xcol = xbuf + (size_t)(kc * C::BK + warp * G + c * 8 * C::WPT) * 2;
+      const uint8_t* xcol = xbuf + (size_t)(kc * C::BK + wwarp * G + c * 8 * C::WPT) * 2;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint4* p = (const uint4*)(xcol + (g + 8 * h) * kXRowBytes);
+        const uint4* p = (const uint4*)(xcol + (g + 8 * h) * C::kXRowBytes);
 #pragma unroll
         for (int i = 0; i < C::WPT; ++i) {
           const uint4 X = p[i];
@@ -262,10 +301,12 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           xb[h][2 * i + 1][1] = prmt(X.y, X.w, 0x7632);  // (k3, k7)
         }
         xs[h][0] = xs[h][1] = xs[h][2] = xs[h][3] = 0.f;
-#pragma unroll
-        for (int m = 0; m < 2 * C::WPT; ++m)
-          TR::mma(xs[h], TR::kOnes, TR::kOnes, TR::kOnes, TR::kOnes, xb[h][m][0], xb[h][m][1]);
       }
+#pragma unroll
+      for (int m = 0; m < 2 * C::WPT; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          TR::mma(xs[h], TR::kOnes, TR::kOnes, TR::kOnes, TR::kOnes, xb[h][m][0], xb[h][m][1]);
     }
 
     const uint16_t* S16 = (const uint16_t*)(st + C::kWBytes);
@@ -288,30 +329,33 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         U[0] = a.x; U[1] = a.y; U[2] = a.z; U[3] = a.w;
         V[0] = b.x; V[1] = b.y; V[2] = b.z; V[3] = b.w;
       }
-      const float s_lo = TR::bits_to_float(S16[r_lo * 8 + warp]), s_hi = TR::bits_to_float(S16[(r_lo + 8) * 8 + warp]);
-      const float b_lo = TR::bits_to_float(B16[r_lo * 8 + warp]), b_hi = TR::bits_to_float(B16[(r_lo + 8) * 8 + warp]);
+      const float s_lo = TR::bits_to_float(S16[r_lo * 8 + wwarp]), s_hi = TR::bits_to_float(S16[(r_lo + 8) * 8 + wwarp]);
+      const float b_lo = TR::bits_to_float(B16[r_lo * 8 + wwarp]), b_hi = TR::bits_to_float(B16[(r_lo + 8) * 8 + wwarp]);
       const float bq_lo = fmaf(-TR::kMagicValue, s_lo, b_lo), bq_hi = fmaf(-TR::kMagicValue, s_hi, b_hi);
 
-      uint32_t PU[C::WPT][4], PV[C::WPT][4];
+      float acc[2][4];
 #pragma unroll
-      for (int i = 0; i < C::WPT; ++i)
+      for (int h = 0; h < 2; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < C::WPT; ++i) {
+        uint32_t PU[4], PV[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          PU[i][q] = lop3_and_or(U[i] >> (4 * q), 0x000F000Fu, TR::kMagic);  // (nib q, nib q+4) as 128+nib
-          PV[i][q] = lop3_and_or(V[i] >> (4 * q), 0x000F000Fu, TR::kMagic);
+          PU[q] = lop3_and_or(U[i] >> (4 * q), 0x000F000Fu, TR::kMagic);  // (nib q, nib q+4) as 128+nib
+          PV[q] = lop3_and_or(V[i] >> (4 * q), 0x000F000Fu, TR::kMagic);
         }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) TR::mma(acc[h], PU[0], PV[0], PU[1], PV[1], xb[h][2 * i][0], xb[h][2 * i][1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          TR::mma(acc[h], PU[2], PV[2], PU[3], PV[3], xb[h][2 * i + 1][0], xb[h][2 * i + 1][1]);
+      }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < C::WPT; ++i) {
-          TR::mma(acc, PU[i][0], PV[i][0], PU[i][1], PV[i][1], xb[h][2 * i][0], xb[h][2 * i][1]);
-          TR::mma(acc, PU[i][2], PV[i][2], PU[i][3], PV[i][3], xb[h][2 * i + 1][0], xb[h][2 * i + 1][1]);
-        }
-        out[t][h][0] = fmaf(s_lo, acc[0], fmaf(bq_lo, xs[h][0], out[t][h][0]));
-        out[t][h][1] = fmaf(s_lo, acc[1], fmaf(bq_lo, xs[h][1], out[t][h][1]));
-        out[t][h][2] = fmaf(s_hi, acc[2], fmaf(bq_hi, xs[h][0], out[t][h][2]));
-        out[t][h][3] = fmaf(s_hi, acc[3], fmaf(bq_hi, xs[h][1], out[t][h][3]));
+        out[t][h][0] = fmaf(s_lo, acc[h][0], fmaf(bq_lo, xs[h][0], out[t][h][0]));
+        out[t][h][1] = fmaf(s_lo, acc[h][1], fmaf(bq_lo, xs[h][1], out[t][h][1]));
+        out[t][h][2] = fmaf(s_hi, acc[h][2], fmaf(bq_hi, xs[h][0], out[t][h][2]));
+        out[t][h][3] = fmaf(s_hi, acc[h][3], fmaf(bq_hi, xs[h][1], out[t][h][3]));
       }
     }
     __syncwarp();
@@ -320,29 +364,42 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
     const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
     if (seg_end) {
-      // A ticket taken at the previous segment end has long since returned: publish whether this CTA was
-      // the last contributor of that tile (the barrier below makes `flag` visible).
-      if (pend_nt >= 0 && ctid == 0) {
-        const int last = (pend_ticket == (unsigned)(pend_total - 1));
-        if (last) __threadfence();
-        *flag = last;
+      // ---- reduce the 8 warps' partial tiles through shared memory, in two rounds of 16 KB ----
+      if (wwarp >= 4) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          red[((wwarp - 4) * 8 + q) * 32 + lane] =
+              make_float4(out[q >> 1][q & 1][0], out[q >> 1][q & 1][1], out[q >> 1][q & 1][2], out[q >> 1][q & 1][3]);
       }
-      // ---- reduce the 8 warps' partial tiles through shared memory ----
+      named_bar_sync(bar_id, kConsumers);
+      if (wwarp < 4) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 a = red[(wwarp * 8 + q) * 32 + lane];
+          out[q >> 1][q & 1][0] += a.x; out[q >> 1][q & 1][1] += a.y;
+          out[q >> 1][q & 1][2] += a.z; out[q >> 1][q & 1][3] += a.w;
+        }
+      }
+      named_bar_sync(bar_id, kConsumers);
+      if (wwarp < 4) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          red[(wwarp * 8 + q) * 32 + lane] =
+              make_float4(out[q >> 1][q & 1][0], out[q >> 1][q & 1][1], out[q >> 1][q & 1][2], out[q >> 1][q & 1][3]);
+      }
 #pragma unroll
       for (int t = 0; t < 4; ++t)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          red[(warp * 8 + t * 2 + h) * 32 + lane] = make_float4(out[t][h][0], out[t][h][1], out[t][h][2], out[t][h][3]);
-          out[t][h][0] = out[t][h][1] = out[t][h][2] = out[t][h][3] = 0.f;
-        }
-      named_bar_sync(1, kConsumers);
-      float4 v = red[(0 * 8 + warp) * 32 + lane];
+        for (int h = 0; h < 2; ++h) out[t][h][0] = out[t][h][1] = out[t][h][2] = out[t][h][3] = 0.f;
+      named_bar_sync(bar_id, kConsumers);
+      // thread (wwarp, lane) finalises quad q = wwarp = (row tile wwarp>>1, token half wwarp&1) of lane `lane`
+      float4 v = red[(0 * 8 + wwarp) * 32 + lane];
 #pragma unroll
-      for (int w2 = 1; w2 < kConsumerWarps; ++w2) {
-        const float4 a = red[(w2 * 8 + warp) * 32 + lane];
+      for (int w2 = 1; w2 < 4; ++w2) {
+        const float4 a = red[(w2 * 8 + wwarp) * 32 + lane];
         v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
       }
-      // pieces this row tile receives in total, and this CTA's piece index inside its slab
+      // pieces this row tile receives in total, and this worker's piece index inside its slab
       int total = 0, first_here = 0;
       for (int s2 = lane; s2 < plan.S; s2 += 32) {
         const SlabGeom g2 = slab_geom(plan, s2);
@@ -355,32 +412,21 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       if (total > 1) {
         pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid] = v;
       } else {
-        store_tile<T>(v, y, bias, nt, warp, rp, c, M, N);
+        store_tile<T>(v, y, bias, nt, wwarp, rp, c, M, N);
       }
-      if (pend_nt >= 0 && *flag) finalize_tile<T>(plan, pieces, counters, y, bias, pend_nt, ctid, warp, rp, c);
-      named_bar_sync(1, kConsumers);  // every piece store is issued; `red` and `flag` are free again
       if (total > 1) {
-        if (ctid == 0) {
-          __threadfence();  // cumulative: orders the whole CTA's piece stores (seen through the barrier) before the ticket
-          pend_ticket = atomicAdd(&counters[nt], 1u);
-        }
-        pend_nt = nt;
-        pend_total = total;
-      } else {
-        pend_nt = -1;
+        if (ctid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
+        ++npend;
+      }
+      named_bar_sync(bar_id, kConsumers);  // `red` is free again
+      if (npend == kMaxPend) {
+        flush_tickets();
+        npend = 0;
       }
     }
     if (++kc == sg.cs) { kc = 0; ++nt; }
   }
-  if (pend_nt >= 0) {
-    if (ctid == 0) {
-      const int last = (pend_ticket == (unsigned)(pend_total - 1));
-      if (last) __threadfence();
-      *flag = last;
-    }
-    named_bar_sync(1, kConsumers);
-    if (*flag) finalize_tile<T>(plan, pieces, counters, y, bias, pend_nt, ctid, warp, rp, c);
-  }
+  if (npend > 0) flush_tickets();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -429,22 +475,24 @@ int g_max_blocks = 0;
 bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
   const int BK = 8 * G;
   const int C = K / BK;
-  const int csmax = kSlabKMax / BK;
+  const int csmax = (G == 128 ? 1024 : 2048) / BK;
   p->M = M; p->K = K; p->N = N;
   p->NT = (N + kBN - 1) / kBN;
   p->S = (C + csmax - 1) / csmax;
   if (p->S > kMaxSlabs || p->NT > kMaxRowTiles) return false;
   for (int i = 0; i <= p->S; ++i) p->slab_chunk0[i] = (int)((long long)i * C / p->S);
   const long long U = (long long)p->NT * C;
-  long long grid = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
-  if (grid > U) grid = U;
-  if (grid < p->S) grid = p->S;
-  for (int i = 0; i <= p->S; ++i) p->slab_cta0[i] = (int)(grid * p->slab_chunk0[i] / C);
+  // Work is dealt to "workers": two per thread block.  A block's two workers share one activation slab,
+  // so every slab starts at an even worker index and gets at least one block.
+  long long blocks = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
+  if (2 * blocks > U + 1) blocks = (U + 1) / 2;
+  if (blocks < p->S) blocks = p->S;
+  for (int i = 0; i <= p->S; ++i) p->slab_cta0[i] = 2 * (int)(blocks * p->slab_chunk0[i] / C);
   for (int i = 1; i <= p->S; ++i)
-    if (p->slab_cta0[i] < p->slab_cta0[i - 1] + 1) p->slab_cta0[i] = p->slab_cta0[i - 1] + 1;
-  p->slab_cta0[p->S] = (int)grid;
+    if (p->slab_cta0[i] < p->slab_cta0[i - 1] + 2) p->slab_cta0[i] = p->slab_cta0[i - 1] + 2;
+  p->slab_cta0[p->S] = 2 * (int)blocks;
   for (int i = p->S - 1; i >= 1; --i)
-    if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 1) p->slab_cta0[i] = p->slab_cta0[i + 1] - 1;
+    if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 2) p->slab_cta0[i] = p->slab_cta0[i + 1] - 2;
   int maxp = 1;
   for (int i = 0; i < p->S; ++i) {
     const int cs = p->slab_chunk0[i + 1] - p->slab_chunk0[i];
@@ -542,7 +590,7 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   cudaError_t e;
   unsigned* counters = (unsigned*)ws;
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
-  const int grid = plan.slab_cta0[plan.S];
+  const int grid = plan.slab_cta0[plan.S] / 2;
   kern<<<grid, kThreads, C::kSmemBytes, st>>>(tw, ts, tb, (const T*)x, (const T*)bias, (T*)y, pieces, counters, plan,
                                               device_error_word(device));
   e = cudaGetLastError();
