@@ -70,6 +70,57 @@ DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
  * returns how many ints were written (<0 on error). */
 DFLASH_API int dflash_verify_qmm_plan(int M, int K, int N, int group_size, int* out, int capacity);
 
+/* ---------------------------------------------------------------------------------------------
+ * GatedDeltaNet forward with innovation tape (tape record).
+ * Replaces `gated_delta_kernel_with_tape` and the Metal kernels `gated_delta_tape[_vec][_mask]`
+ * (dflash_mlx/kernels.py:176-224, 29-105).  Per step t < T, on state S[Dv,Dk] of head hv:
+ *   S *= g_t ; kv = S k_t ; delta_t = (v_t - kv) * beta_t ; S += delta_t (x) k_t ; y_t = S q_t
+ * and, when the state dtype is not f32, S is rounded to it after every step (kernels.py:89-91).
+ *   q,k   in_dtype [B,T,Hk,Dk];  v in_dtype [B,T,Hv,Dv];  beta f32 [B,T,Hv]
+ *   g     f32 [B,T,Hv] (g_is_vector=0) or [B,T,Hv,Dk] (g_is_vector=1): the decay FACTOR in (0,1]
+ *   mask  uint8 [B,T] or NULL; a masked-out step leaves S unchanged and writes delta = 0, y = 0
+ *   state_in/state_out  state_dtype [B,Hv,Dv,Dk], 16-byte aligned (may be the same buffer)
+ *   y     in_dtype [B,T,Hv,Dv];  tape f32 [B,T,Hv,Dv]
+ * Dk in {32,64,128,256}; Hv % Hk == 0 (head hv reads k-head hv / (Hv/Hk), kernels.py:33).
+ */
+DFLASH_API int dflash_gdn_forward_tape(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                       const uint8_t* mask, const void* state_in, void* state_out, void* y, float* tape,
+                                       int B, int T, int Hk, int Hv, int Dk, int Dv, int g_is_vector, int in_dtype,
+                                       int state_dtype, void* stream);
+
+/* Tape replay (rollback): applies the first `steps` tape entries to state_in.
+ * Replaces `tape_replay_kernel` and the Metal kernels `tape_replay[_vec][_mask]`
+ * (dflash_mlx/kernels.py:361-407, 244-294):  S *= g_t ; S += delta_t (x) k_t  for t < steps.
+ *   tape f32 [B,T,Hv,Dv];  k k_dtype [B,T,Hk,Dk];  g f32 as above;  mask uint8 [B,T] or NULL
+ *   T is the length the arrays were recorded with (their stride); 0 <= steps <= T; steps == 0 copies.
+ *   steps_dev, when not NULL, is a device int that overrides `steps` at run time (clamped to 0..T), so
+ *   that a captured CUDA graph can replay a different accepted length every time.
+ * To roll back every layer of a model in one launch, stack the layers' arrays along B.
+ */
+DFLASH_API int dflash_tape_replay(const float* tape, const void* k, const float* g, const uint8_t* mask,
+                                  const void* state_in, void* state_out, int B, int T, int steps, const int* steps_dev,
+                                  int Hk, int Hv, int Dk, int Dv, int g_is_vector, int k_dtype, int state_dtype,
+                                  void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * verify_sdpa: exact softmax attention of 16 query rows per head over N keys (split-KV + combine).
+ * Replaces `batched_sdpa_2pass_exact` and the Metal kernels `batched_sdpa_2pass_partials[_mask]` /
+ * `batched_sdpa_2pass_reduce` (dflash_mlx/kernels.py:658-761, 479-565, 579-638).
+ *   q    dtype [B,Hq,16,D] contiguous;  out likewise
+ *   k,v  dtype [B,Hk,N,D]: element (b,h,n,d) at ((b*Hk+h)*head_stride + n*seq_stride + d); strides in
+ *        elements, multiples of 8 (rows 16-byte aligned).  N counts the 16 new positions (runtime.py:550-555)
+ *   key n is visible to row i iff n <= N-16+i (kernels.py:530); head hq reads KV head hq/(Hq/Hk)
+ *   mask dtype [B,Hq,16,N] additive, or NULL; entries below the dtype's finite minimum hide the key
+ *   D in {128,256};  dtype bf16 or f16;  scale multiplies q.k
+ *   num_splits: 0 = chosen from the SM count; workspace: dflash_verify_sdpa_workspace_bytes() bytes of
+ *   device memory (contents irrelevant), 16-byte aligned; unused when the split count comes out as 1.
+ */
+DFLASH_API size_t dflash_verify_sdpa_workspace_bytes(int B, int Hq, int Hk, int N, int D, int num_splits);
+DFLASH_API int dflash_verify_sdpa(const void* q, const void* k, const void* v, const void* mask, void* out, int B,
+                                  int Hq, int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
+                                  long long v_head_stride, long long v_seq_stride, float scale, int dtype,
+                                  int num_splits, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
