@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the dflash target-verify hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--workload qmm_cfg1|replay|sdpa] [--impl reference]
+
+Prints ONE JSON line (rank 0).  See DESIGN.md ("Measurement") for what every field means.
+Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
+  qmm_cfg1  x bf16 [16,4096] . int4-g64 W [12288,4096]^T.  A step = one pass over a pool of weight
+            matrices larger than L2 (so every launch streams its weights from HBM).
+  replay    GatedDeltaNet tape replay of all 48 layers of the dense model in one launch.
+  sdpa      16-row verify attention at one KV length.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def qmm_bytes(M, K, N, G=64):
+    """Algorithmic bytes of one verify matmul: packed weights + scales + biases + x + y."""
+    return N * K // 2 + 2 * (N * (K // G)) * 2 + M * K * 2 + M * N * 2
+
+
+class QmmWorkload:
+    """Configuration 1 of BASELINE.json.  With R ranks the output columns are split R ways (column-parallel
+    linear: no collective on the data path), so the job's work is fixed: strong scaling."""
+    name = "qmm_cfg1"
+    metric, unit, higher_is_better, scaling, dtype = "m16_int4_verify_qmm_latency", "us", False, "strong", "bf16"
+    M, K, N, G = 16, 4096, 12288, 64
+
+    def __init__(self, rank, world, device):
+        import torch
+        from oracle import qmm as oq
+        self.torch, self.device, self.world = torch, device, world
+        self.n_local = self.N // world
+        per = qmm_bytes(self.M, self.K, self.n_local, self.G)
+        self.pool = max(2, (3 * L2_BYTES) // per + 1)          # pool > 3 x L2: every launch reads HBM
+        self.per_launch_bytes = per
+        self.ws = []
+        for i in range(self.pool):
+            wq, s, b = oq.random_quantized(self.n_local, self.K, seed=0xDF1A + 131 * i + rank, group_size=self.G)
+            self.ws.append((wq.to(device), s.to(device), b.to(device)))
+        gen = torch.Generator().manual_seed(0xDF1A)
+        self.x_host = torch.randn(self.M, self.K, generator=gen).bfloat16().pin_memory()
+        self.x = self.x_host.to(device)
+        self.y_host = torch.empty(self.M, self.n_local, dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = self.pool
+        self.units_per_step = self.pool
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "group_size": self.G,
+                       "columns_per_rank": self.n_local, "weight_pool": self.pool,
+                       "l2": "inputs larger than L2: a step walks a pool of %d weight matrices (%.0f MB)" %
+                             (self.pool, self.pool * per / 1e6), "parallelism": f"column-parallel x{world}"}
+
+    def step(self):
+        from dflash_mlx_b200.verify_qmm import verify_matmul
+        out = None
+        for w in self.ws:
+            out = verify_matmul(self.x, *w, group_size=self.G, bits=4)
+        return out
+
+    def e2e_step(self):
+        """One call through the public API with host buffers: x from pinned host memory, y back to the host."""
+        from dflash_mlx_b200.verify_qmm import verify_matmul
+        self._i = (getattr(self, "_i", -1) + 1) % self.pool
+        x = self.x_host.to(self.device, non_blocking=True)
+        y = verify_matmul(x, *self.ws[self._i], group_size=self.G, bits=4)
+        self.y_host.copy_(y, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return 1
+
+    h2d_bytes = property(lambda self: self.M * self.K * 2)
+    d2h_bytes = property(lambda self: self.M * self.n_local * 2)
+
+    def value_from_ms(self, ms_per_step):
+        return ms_per_step * 1e3 / self.units_per_step      # us per matmul
+
+    def e2e_value(self, seconds, calls):
+        return seconds * 1e6 / calls
+
+    def cpu_baseline(self, budget_s=12.0):
+        """The C restatement of the stock CPU path (oracle/qmm_ref.c) on all host cores, same shape."""
+        import torch
+        from oracle import qmm as oq
+        from oracle.build_ref import load
+        out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "gpurun_out" / "oracle_native")))
+        try:
+            lib, kind_note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
+        except Exception:
+            lib, kind_note = load(native=False), "gcc -O3 -fopenmp"
+        wq, s, b = oq.random_quantized(self.N, self.K, seed=1, group_size=self.G)
+        x = self.x_host.clone()
+        y = torch.empty(self.M, self.N, dtype=torch.float32)
+        args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), self.M, self.K, self.N, self.G)
+        lib.qmm_ref(*args)
+        times, t_end = [], time.perf_counter() + budget_s
+        while len(times) < 30 and (time.perf_counter() < t_end or len(times) < 3):
+            t0 = time.perf_counter()
+            lib.qmm_ref(*args)
+            times.append(time.perf_counter() - t0)
+        times.sort()
+        return {"value": times[len(times) // 2] * 1e6, "unit": "us", "cores": int(lib.qmm_ref_threads()),
+                "kind": "port", "sample": f"{len(times)} full-size calls (M=16,K=4096,N=12288), median; {kind_note}; "
+                                          "MLX unavailable on this box: CPU baseline = C restatement of the stock qmm"}
+
+
+WORKLOADS = {"qmm_cfg1": QmmWorkload}
+DEFAULT_WORKLOAD = "qmm_cfg1"
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    os.environ.setdefault("CUDA_VISIBLE_DEVICES", "")
+    cls = WORKLOADS[args.workload]
+    w = cls.__new__(cls)
+    import torch
+    w.torch = torch
+    gen = torch.Generator().manual_seed(0xDF1A)
+    w.x_host = torch.randn(cls.M, cls.K, generator=gen).bfloat16()
+    w.world, w.n_local = 1, cls.N
+    budget = max(3.0, min(60.0, 2.0 * (args.steps + args.warmup)))
+    cb = w.cpu_baseline(budget_s=budget)
+    line = {"impl": "reference", "metric": cls.metric, "value": cb["value"], "unit": cls.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
+            "higher_is_better": cls.higher_is_better, "scaling": cls.scaling, "vs_baseline": None, "dtype": cls.dtype,
+            "data": "synthetic", "config": {"workload": cls.name, "M": cls.M, "K": cls.K, "N": cls.N,
+                                            "group_size": cls.G},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    os.environ["DFLASH_VERIFY_QMM"] = "1"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    wl = WORKLOADS[args.workload](rank, world, device)
+
+    # ---- device-resident loop: one CUDA graph = one step ----
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        wl.step()                     # untimed: creates workspaces, tensor maps, kernel attributes
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            wl.step()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # ---- end to end through the public API with host buffers ----
+    for _ in range(3):
+        wl.e2e_step()
+    barrier()
+    calls, t0 = 0, time.perf_counter()
+    e2e_iters = max(50, args.steps * 4)
+    for _ in range(e2e_iters):
+        calls += wl.e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    from dflash_mlx_b200 import _lib
+    dev_err = _lib.lib().dflash_device_error(local_rank)
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        us_per_launch = ms_per_step * 1e3 / wl.launches_per_step
+        achieved = wl.per_launch_bytes / us_per_launch / 1e3       # GB/s
+        line = {"metric": wl.metric, "value": wl.value_from_ms(ms_per_step), "unit": wl.unit, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": wl.higher_is_better, "scaling": wl.scaling, "vs_baseline": None,
+                "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                             "kernel": "qmm_stream_kernel", "algorithmic_bytes_per_launch": wl.per_launch_bytes,
+                             "us_per_launch": us_per_launch},
+                "e2e": {"value": wl.e2e_value(e2e_s, calls), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,
+                        "d2h_bytes_per_step": wl.d2h_bytes, "calls": calls},
+                "gpu_launches": wl.launches_per_step * args.steps,
+                "clocks": clocks, "device_error": dev_err}
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = wl.cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
