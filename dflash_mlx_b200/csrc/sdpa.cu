@@ -377,3 +377,42 @@ extern "C" int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
                     : launch<__half, 256>(a, workspace, workspace_bytes, num_splits, st);
   return fail(DFLASH_ERR_BAD_ARG, "verify_sdpa: dtype %d (want bf16 or f16)", dtype);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate: the split-KV partials live in a fixed array inside the library.
+namespace {
+constexpr size_t kStaticScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_sdpa_static_scratch[kStaticScratchBytes];
+void* g_static_scratch_ptr[64] = {};  // device address of the array, per device (host code cannot use the symbol itself)
+}  // namespace
+
+extern "C" size_t dflash_verify_sdpa_static_capacity(void) { return kStaticScratchBytes; }
+
+extern "C" int dflash_verify_sdpa_static(const void* q, const void* k, const void* v, const void* mask, void* out, int B,
+                                         int Hq, int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
+                                         long long v_head_stride, long long v_seq_stride, float scale, int dtype,
+                                         int num_splits, void* stream) {
+  if (B < 1 || Hq < 1 || Hk < 1 || Hq % Hk != 0 || N < 16 || (D != 128 && D != 256))
+    return fail(DFLASH_ERR_BAD_SHAPE, "verify_sdpa_static: unsupported shape");
+  const size_t need = dflash_verify_sdpa_workspace_bytes(B, Hq, Hk, N, D, num_splits);
+  if (need > kStaticScratchBytes)
+    return fail(DFLASH_ERR_WORKSPACE,
+                "verify_sdpa_static: this shape needs %zu bytes of split-KV scratch but the built-in array holds %zu; "
+                "pass a smaller num_splits or use dflash_verify_sdpa with a caller workspace",
+                need, (size_t)kStaticScratchBytes);
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= 64) return fail(DFLASH_ERR_UNSUPPORTED, "verify_sdpa_static: device index %d", device);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    // one-time set-up on this device (it is current): resolve the array's device address
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sdpa_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(DFLASH_ERR_LAUNCH, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_scratch_ptr[device] = p;
+  }
+  return dflash_verify_sdpa(q, k, v, mask, out, B, Hq, Hk, N, D, k_head_stride, k_seq_stride, v_head_stride,
+                            v_seq_stride, scale, dtype, num_splits, g_static_scratch_ptr[device], kStaticScratchBytes,
+                            stream);
+}

@@ -121,6 +121,27 @@ DFLASH_API int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
                                   long long v_head_stride, long long v_seq_stride, float scale, int dtype,
                                   int num_splits, void* workspace, size_t workspace_bytes, void* stream);
 
+/* verify_sdpa for callers that cannot allocate device memory.  (No counterpart in the reference.)
+ * Some hosts of this library - a serving loop that has handed all device memory to its own pool, code
+ * running inside a CUDA-graph capture, a plugin slot that forbids allocator calls - cannot obtain the
+ * split-KV workspace dflash_verify_sdpa asks for.  This entry point computes exactly the same result with the
+ * partial-softmax scratch kept in an array built into the library (dflash_verify_sdpa_static_capacity()
+ * bytes, 32 MiB, held on every GPU that loads the library until the process exits).  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine; inputs and the output are still the caller's.
+ *   - Same arguments as dflash_verify_sdpa, minus the workspace.  Shapes whose scratch need
+ *     (dflash_verify_sdpa_workspace_bytes) exceeds the capacity are refused with DFLASH_ERR_WORKSPACE.
+ *   - The first call on each device resolves the array's device address (that device must be current); make
+ *     that first call before any stream capture.
+ *   - The array is shared by every call and keeps the previous call's contents.  Nothing in it has to start
+ *     at zero (pass 1 writes every slot pass 2 reads), but two calls that overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it: serialise them.
+ */
+DFLASH_API size_t dflash_verify_sdpa_static_capacity(void);
+DFLASH_API int dflash_verify_sdpa_static(const void* q, const void* k, const void* v, const void* mask, void* out, int B,
+                                         int Hq, int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
+                                         long long v_head_stride, long long v_seq_stride, float scale, int dtype,
+                                         int num_splits, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
