@@ -1,0 +1,351 @@
+// Small fused kernels between the matmuls of a 16-token verify step (sm_100a).
+//
+// They restate the per-layer dataflow of the reference's target-model hooks: the GatedDeltaNet layer
+// (dflash_mlx/runtime.py:351-452), the gated full-attention layer (runtime.py:515-613) and the step driver
+// (runtime.py:779-821, 90-108).  Activations are bf16 (or fp16), all arithmetic is fp32.  Every kernel works on
+// T <= 64 token rows; they are latency-sized, one CTA (or warp) per row or per (row, head).
+#include "common.cuh"
+
+namespace dflash {
+namespace {
+
+template <typename T> __device__ __forceinline__ float tof(T v);
+template <> __device__ __forceinline__ float tof<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float tof<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T fromf(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 fromf<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half fromf<__half>(float v) { return __float2half_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Block-wide sum for blockDim.x <= 1024 (every thread gets the result).
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// h_out = h_in (+ delta);  x = rmsnorm(h_out) * w.  One CTA per token row.
+template <typename T>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* __restrict__ h_in, const T* __restrict__ delta,
+                                                          const T* __restrict__ w, T* __restrict__ h_out,
+                                                          T* __restrict__ x, int H, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = tof<T>(h_in[row + i]);
+    if (delta != nullptr) v = tof<T>(fromf<T>(v + tof<T>(delta[row + i])));  // the residual stream is stored in T
+    if (h_out != nullptr) h_out[row + i] = fromf<T>(v);
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = tof<T>(h_in[row + i]);
+    if (delta != nullptr) v = tof<T>(fromf<T>(v + tof<T>(delta[row + i])));
+    x[row + i] = fromf<T>(v * inv * tof<T>(w[i]));
+  }
+}
+
+// y[t, i] = silu(gu[t, i]) * gu[t, I + i]   (SwiGLU on a fused gate|up projection)
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T* __restrict__ y, int I, int rows) {
+  const size_t n = (size_t)rows * I;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / I, c = i % I;
+    const float g = tof<T>(gu[t * 2 * I + c]), u = tof<T>(gu[t * 2 * I + I + c]);
+    y[i] = fromf<T>(silu(g) * u);
+  }
+}
+
+// h[t, :] = table[ids[t], :]
+template <typename T>
+__global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                                    T* __restrict__ h, int H, int V) {
+  int id = ids[blockIdx.x];
+  id = min(max(id, 0), V - 1);
+  const uint4* src = (const uint4*)(table + (size_t)id * H);
+  uint4* dst = (uint4*)(h + (size_t)blockIdx.x * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[t] = index of the first maximum of logits[t, :]  (greedy tokens, runtime.py:90-98)
+template <typename T>
+__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int V) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const T* row = logits + (size_t)blockIdx.x * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = tof<T>(row[i]);
+    if (v > best) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+  }
+}
+
+// GatedDeltaNet layer, everything between the input projections and the recurrence (runtime.py:368-403):
+// depthwise causal conv over [conv_state ; qkv] + SiLU, split into q/k/v heads, q = Dk^-1 rms_norm(q),
+// k = Dk^-1/2 rms_norm(k), g = exp(-exp(A_log) softplus(a + dt_bias)), beta = sigmoid(b); also emits the new
+// conv window (last Kc-1 rows of the concatenation) and a contiguous copy of qkv for the rollback tape.
+// grid (T, 2*Hk + Hv), block = max(Dk, Dv) threads: one thread per channel of one head.
+struct GdnPrepArgs {
+  const void* proj; long long ld; int z_off, b_off, a_off;
+  const void* conv_state; const void* conv_w; const void* conv_b;
+  const float* A_log; const float* dt_bias;
+  void* q; void* k; void* v; float* g; float* beta; void* new_conv_state; void* qkv_tape;
+  int T, Hk, Hv, Dk, Dv, Kc;
+  float eps;
+};
+template <typename T>
+__global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, hb = blockIdx.y, d = threadIdx.x;
+  const int key_dim = a.Hk * a.Dk, conv_dim = 2 * key_dim + a.Hv * a.Dv;
+  const bool is_v = hb >= 2 * a.Hk;
+  const int D = is_v ? a.Dv : a.Dk;
+  const int c = is_v ? 2 * key_dim + (hb - 2 * a.Hk) * a.Dv + d : hb * a.Dk + d;
+  const bool live = d < D;
+  const T* proj = (const T*)a.proj;
+  const T* cs = (const T*)a.conv_state;
+  const int keep = a.Kc - 1;
+  float val = 0.f;
+  if (live) {
+    float acc = a.conv_b ? tof<T>(((const T*)a.conv_b)[c]) : 0.f;
+    for (int j = 0; j < a.Kc; ++j) {
+      const int r = t + j;  // row of [conv_state ; qkv]
+      const float in = r < keep ? tof<T>(cs[(size_t)r * conv_dim + c]) : tof<T>(proj[(size_t)(r - keep) * a.ld + c]);
+      acc = fmaf(tof<T>(((const T*)a.conv_w)[(size_t)c * a.Kc + j]), in, acc);
+    }
+    val = tof<T>(fromf<T>(acc));
+    val = tof<T>(fromf<T>(silu(val)));
+    ((T*)a.qkv_tape)[(size_t)t * conv_dim + c] = proj[(size_t)t * a.ld + c];
+    for (int r = t; r < keep; r += a.T) {  // new conv window = rows T .. T+keep-1 of the concatenation
+      const int src = a.T + r;
+      ((T*)a.new_conv_state)[(size_t)r * conv_dim + c] =
+          src < keep ? cs[(size_t)src * conv_dim + c] : proj[(size_t)(src - keep) * a.ld + c];
+    }
+  }
+  if (is_v) {
+    if (live) ((T*)a.v)[((size_t)t * a.Hv + (hb - 2 * a.Hk)) * a.Dv + d] = fromf<T>(val);
+    // one v-head block per head also produces that head's gate and beta
+    if (d == 0) {
+      const int hv = hb - 2 * a.Hk;
+      const float av = tof<T>(proj[(size_t)t * a.ld + a.a_off + hv]), bv = tof<T>(proj[(size_t)t * a.ld + a.b_off + hv]);
+      const float xs = tof<T>(fromf<T>(av + a.dt_bias[hv]));
+      const float sp = xs > 20.f ? xs : log1pf(expf(xs));
+      a.g[(size_t)t * a.Hv + hv] = expf(-expf(a.A_log[hv]) * sp);
+      a.beta[(size_t)t * a.Hv + hv] = tof<T>(fromf<T>(sigmoidf(bv)));
+    }
+    return;
+  }
+  const float ss = block_sum(live ? val * val : 0.f, scratch);
+  if (!live) return;
+  const float inv = rsqrtf(ss / (float)a.Dk + a.eps);
+  const float normed = tof<T>(fromf<T>(val * inv));
+  const float isc = rsqrtf((float)a.Dk);
+  if (hb < a.Hk) ((T*)a.q)[((size_t)t * a.Hk + hb) * a.Dk + d] = fromf<T>(normed * isc * isc);
+  else ((T*)a.k)[((size_t)t * a.Hk + (hb - a.Hk)) * a.Dk + d] = fromf<T>(normed * isc);
+}
+
+// out[t, hv*Dv + d] = rms_norm(y[t,hv,:])[d] * w[d] * silu(z[t, z_off + hv*Dv + d])   (runtime.py:445)
+template <typename T>
+__global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ proj,
+                                                            long long ld, int z_off, const T* __restrict__ w,
+                                                            T* __restrict__ out, int rows_heads, int Hv, int Dv, float eps) {
+  const int rh = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (rh >= rows_heads) return;
+  const int t = rh / Hv, hv = rh % Hv;
+  const T* yr = y + (size_t)rh * Dv;
+  float ss = 0.f;
+  for (int d = lane; d < Dv; d += 32) { const float v = tof<T>(yr[d]); ss += v * v; }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)Dv + eps);
+  for (int d = lane; d < Dv; d += 32) {
+    const float n = tof<T>(fromf<T>(tof<T>(yr[d]) * inv * tof<T>(w[d])));
+    const float z = tof<T>(proj[(size_t)t * ld + z_off + hv * Dv + d]);
+    out[(size_t)t * Hv * Dv + hv * Dv + d] = fromf<T>(n * silu(z));
+  }
+}
+
+// Full-attention layer between the projections and the attention kernel (runtime.py:527-555):
+// per-head RMSNorm of q and k (with weights), rotary embedding of the first `rope_dims` channels at position
+// offset + t, q written as [Hq, T, D], k and v appended to the cache at row offset + t.
+// proj row: [ (query D | gate D) x Hq | k (Hk*D) | v (Hk*D) ].  One warp per (token, head).
+struct AttnPrepArgs {
+  const void* proj; long long ld; int k_off, v_off;
+  const void* q_norm_w; const void* k_norm_w;
+  void* q; void* kcache; void* vcache; long long cache_head_stride;
+  int T, Hq, Hk, D, rope_dims, offset;
+  float eps, rope_base;
+};
+template <typename T>
+__global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
+  const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int heads = a.Hq + 2 * a.Hk;
+  if (idx >= a.T * heads) return;
+  const int t = idx / heads, h = idx % heads;
+  const T* row = (const T*)a.proj + (size_t)t * a.ld;
+  const int pos = a.offset + t;
+  if (h >= a.Hq + a.Hk) {  // value head: plain copy into the cache
+    const int hk = h - a.Hq - a.Hk;
+    T* dst = (T*)a.vcache + (size_t)hk * a.cache_head_stride + (size_t)pos * a.D;
+    for (int d = lane; d < a.D; d += 32) dst[d] = row[a.v_off + hk * a.D + d];
+    return;
+  }
+  const bool is_q = h < a.Hq;
+  const T* src = is_q ? row + (size_t)h * 2 * a.D : row + a.k_off + (h - a.Hq) * a.D;
+  const T* w = (const T*)(is_q ? a.q_norm_w : a.k_norm_w);
+  T* dst = is_q ? (T*)a.q + ((size_t)h * a.T + t) * a.D
+                : (T*)a.kcache + (size_t)(h - a.Hq) * a.cache_head_stride + (size_t)pos * a.D;
+  float ss = 0.f;
+  for (int d = lane; d < a.D; d += 32) { const float v = tof<T>(src[d]); ss += v * v; }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)a.D + a.eps);
+  const int half = a.rope_dims / 2;
+  for (int d = lane; d < a.D; d += 32) {
+    const float x = tof<T>(fromf<T>(tof<T>(src[d]) * inv * tof<T>(w[d])));
+    float o = x;
+    if (d < a.rope_dims) {
+      const int i = d < half ? d : d - half;
+      const int pd = d < half ? d + half : d - half;
+      const float xp = tof<T>(fromf<T>(tof<T>(src[pd]) * inv * tof<T>(w[pd])));
+      const double theta = (double)pos * pow((double)a.rope_base, -2.0 * (double)i / (double)a.rope_dims);
+      double sn, cs;
+      sincos(theta, &sn, &cs);
+      o = d < half ? x * (float)cs - xp * (float)sn : xp * (float)sn + x * (float)cs;
+    }
+    dst[d] = fromf<T>(o);
+  }
+}
+
+// out[t, hq*D + d] = o[hq, t, d] * sigmoid(gate[t, hq, d])   (runtime.py:611-612)
+template <typename T>
+__global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o, const T* __restrict__ proj, long long ld,
+                                                        T* __restrict__ out, int Tn, int Hq, int D) {
+  const size_t n = (size_t)Tn * Hq * D;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D), hq = (int)((i / D) % Hq), t = (int)(i / ((size_t)D * Hq));
+    const float gate = tof<T>(proj[(size_t)t * ld + (size_t)hq * 2 * D + D + d]);
+    out[i] = fromf<T>(tof<T>(o[((size_t)hq * Tn + t) * D + d]) * sigmoidf(gate));
+  }
+}
+
+}  // namespace
+}  // namespace dflash
+
+using namespace dflash;
+
+#define DFLASH_DISPATCH(dtype, CALL)                                                  \
+  do {                                                                                \
+    if ((dtype) == DFLASH_BF16) { using T = __nv_bfloat16; CALL; }                    \
+    else if ((dtype) == DFLASH_F16) { using T = __half; CALL; }                       \
+    else return fail(DFLASH_ERR_BAD_ARG, "%s: dtype %d (want bf16 or f16)", __func__, (int)(dtype)); \
+    cudaError_t e_ = cudaGetLastError();                                              \
+    if (e_ != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "%s: %s", __func__, cudaGetErrorString(e_)); \
+    return DFLASH_OK;                                                                 \
+  } while (0)
+
+extern "C" int dflash_add_rmsnorm(const void* h_in, const void* delta, const void* w, void* h_out, void* x, int T_rows,
+                                  int H, float eps, int dtype, void* stream) {
+  if (!h_in || !w || !x || T_rows < 1 || H < 1) return fail(DFLASH_ERR_BAD_ARG, "add_rmsnorm: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (add_rmsnorm_kernel<T><<<T_rows, 256, 0, st>>>((const T*)h_in, (const T*)delta, (const T*)w,
+                                                                          (T*)h_out, (T*)x, H, eps)));
+}
+
+extern "C" int dflash_swiglu(const void* gate_up, void* y, int T_rows, int I, int dtype, void* stream) {
+  if (!gate_up || !y || T_rows < 1 || I < 1) return fail(DFLASH_ERR_BAD_ARG, "swiglu: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (int)(((size_t)T_rows * I + 255) / 256);
+  DFLASH_DISPATCH(dtype, (swiglu_kernel<T><<<blocks < 2048 ? blocks : 2048, 256, 0, st>>>((const T*)gate_up, (T*)y, I, T_rows)));
+}
+
+extern "C" int dflash_embed(const int* ids, const void* table, void* h, int T_rows, int H, int V, int dtype, void* stream) {
+  if (!ids || !table || !h || T_rows < 1 || H % 8 != 0) return fail(DFLASH_ERR_BAD_ARG, "embed: bad argument (H %% 8 == 0)");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (embed_kernel<T><<<T_rows, 256, 0, st>>>(ids, (const T*)table, (T*)h, H, V)));
+}
+
+extern "C" int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream) {
+  if (!logits || !out || T_rows < 1 || V < 1) return fail(DFLASH_ERR_BAD_ARG, "argmax: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (argmax_kernel<T><<<T_rows, 1024, 0, st>>>((const T*)logits, out, V)));
+}
+
+extern "C" int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_off, int a_off, const void* conv_state,
+                               const void* conv_w, const void* conv_b, const float* A_log, const float* dt_bias, void* q,
+                               void* k, void* v, float* g, float* beta, void* new_conv_state, void* qkv_tape, int T_rows,
+                               int Hk, int Hv, int Dk, int Dv, int conv_kernel, float eps, int dtype, void* stream) {
+  if (!proj || !conv_state || !conv_w || !A_log || !dt_bias || !q || !k || !v || !g || !beta || !new_conv_state || !qkv_tape)
+    return fail(DFLASH_ERR_BAD_ARG, "gdn_prep: null operand");
+  if (T_rows < 1 || Dk > 256 || Dv > 256 || conv_kernel < 1 || conv_kernel > 8 || new_conv_state == conv_state)
+    return fail(DFLASH_ERR_BAD_SHAPE, "gdn_prep: unsupported shape (Dk,Dv <= 256; conv kernel 1..8; separate conv buffers)");
+  GdnPrepArgs a{proj, ld, z_off, b_off, a_off, conv_state, conv_w, conv_b, A_log, dt_bias, q, k, v, g, beta,
+                new_conv_state, qkv_tape, T_rows, Hk, Hv, Dk, Dv, conv_kernel, eps};
+  const int D = Dk > Dv ? Dk : Dv;
+  const int threads = (D + 31) / 32 * 32;
+  dim3 grid(T_rows, 2 * Hk + Hv);
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (gdn_prep_kernel<T><<<grid, threads, 0, st>>>(a)));
+}
+
+extern "C" int dflash_gated_rmsnorm(const void* y, const void* proj, long long ld, int z_off, const void* w, void* out,
+                                    int T_rows, int Hv, int Dv, float eps, int dtype, void* stream) {
+  if (!y || !proj || !w || !out || T_rows < 1) return fail(DFLASH_ERR_BAD_ARG, "gated_rmsnorm: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rh = T_rows * Hv;
+  DFLASH_DISPATCH(dtype, (gated_rmsnorm_kernel<T><<<(rh + 3) / 4, 128, 0, st>>>((const T*)y, (const T*)proj, ld, z_off,
+                                                                                 (const T*)w, (T*)out, rh, Hv, Dv, eps)));
+}
+
+extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                                const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
+                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
+                                int dtype, void* stream) {
+  if (!proj || !q_norm_w || !k_norm_w || !q || !kcache || !vcache) return fail(DFLASH_ERR_BAD_ARG, "attn_prep: null operand");
+  if (T_rows < 1 || rope_dims < 0 || rope_dims > D || rope_dims % 2 != 0 || offset < 0)
+    return fail(DFLASH_ERR_BAD_SHAPE, "attn_prep: bad rope_dims/offset");
+  AttnPrepArgs a{proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride,
+                 T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base};
+  const int n = T_rows * (Hq + 2 * Hk);
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (attn_prep_kernel<T><<<(n + 3) / 4, 128, 0, st>>>(a)));
+}
+
+extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, int T_rows, int Hq, int D,
+                                int dtype, void* stream) {
+  if (!o || !proj || !out || T_rows < 1) return fail(DFLASH_ERR_BAD_ARG, "attn_post: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (int)(((size_t)T_rows * Hq * D + 255) / 256);
+  DFLASH_DISPATCH(dtype, (attn_post_kernel<T><<<blocks, 256, 0, st>>>((const T*)o, (const T*)proj, ld, (T*)out, T_rows, Hq, D)));
+}

@@ -1,0 +1,343 @@
+"""The 16-token target verify step of a hybrid (GatedDeltaNet : full-attention = 3 : 1) model, with rollback.
+
+Restates, over this package's CUDA kernels, what the reference's hooks make one verify pass do:
+``target_forward_with_hidden_states`` / ``_verify_target_block`` (dflash_mlx/runtime.py:779-951), the
+GatedDeltaNet layer hook (runtime.py:351-452), the gated full-attention hook (runtime.py:515-613), greedy
+acceptance (runtime.py:90-108) and ``_restore_target_cache_after_acceptance`` (runtime.py:878-907).
+
+B200-first choices: projections that read the same activations are fused into one int4 matmul (qkv|z|b|a,
+q|k|v, gate|up); all buffers are preallocated, so a whole step is a fixed sequence of launches that can be
+captured in one CUDA graph; GDN states are ping-pong buffers stacked over layers, so the rollback of every
+layer is ONE tape-replay launch with the accepted length read on the device.
+Weights are random-initialised (there are no checkpoints here): this module is the step driver, not a loader.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+
+_c = ctypes
+_vp, _i32, _f32, _ll = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong
+_declared = False
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    from . import kernels
+    kernels._ensure_declared()
+    kernels._ensure_sdpa_declared()
+    d = _lib.declare
+    d("dflash_add_rmsnorm", _i32, [_vp] * 5 + [_i32, _i32, _f32, _i32, _vp])
+    d("dflash_swiglu", _i32, [_vp, _vp, _i32, _i32, _i32, _vp])
+    d("dflash_embed", _i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp])
+    d("dflash_argmax", _i32, [_vp, _vp, _i32, _i32, _i32, _vp])
+    d("dflash_gdn_prep", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 12 + [_i32] * 6 + [_f32, _i32, _vp])
+    d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
+    d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_f32, _f32, _i32, _vp])
+    d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _i32, _i32, _i32, _i32, _vp])
+    _declared = True
+
+
+@dataclass
+class HybridConfig:
+    """Shapes of the dense hybrid model of the benchmark's 4th configuration (defaults) - GDN dimensions are
+    not fixed there and are taken from its 2nd configuration (16 key / 32 value heads of 128)."""
+    layers: int = 64
+    attn_every: int = 4                # layers i with (i + 1) % attn_every == 0 are full attention
+    hidden: int = 5120
+    intermediate: int = 17408
+    q_heads: int = 24
+    kv_heads: int = 4
+    head_dim: int = 256
+    rope_dims: int = 64
+    rope_base: float = 10000000.0
+    gdn_k_heads: int = 16
+    gdn_v_heads: int = 32
+    gdn_dk: int = 128
+    gdn_dv: int = 128
+    conv_kernel: int = 4
+    vocab: int = 151936
+    group_size: int = 64
+    eps: float = 1e-6
+    block: int = 16                    # tokens per verify step
+    max_context: int = 4096 + 64
+
+    def is_attention(self, i: int) -> bool:
+        return (i + 1) % self.attn_every == 0
+
+    @property
+    def conv_dim(self) -> int:
+        return 2 * self.gdn_k_heads * self.gdn_dk + self.gdn_v_heads * self.gdn_dv
+
+    @property
+    def gdn_proj_n(self) -> int:        # qkv | z | b | a
+        return self.conv_dim + self.gdn_v_heads * self.gdn_dv + 2 * self.gdn_v_heads
+
+    @property
+    def attn_proj_n(self) -> int:       # (query | gate) per head | k | v
+        return 2 * self.q_heads * self.head_dim + 2 * self.kv_heads * self.head_dim
+
+
+def _rand_quantized(n: int, k: int, gen: torch.Generator, device, group_size: int, w_std: float = 0.02):
+    """Random int4 codes plus scales/biases with the statistics of affine-quantised N(0, w_std) weights."""
+    w_q = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, device=device, dtype=torch.int64).to(torch.int32)
+    s = (w_std * 6.0 / 15.0) * (1.0 + 0.1 * torch.randn(n, k // group_size, generator=gen, device=device))
+    b = -7.5 * s + 0.1 * w_std * torch.randn(n, k // group_size, generator=gen, device=device)
+    return {"w": w_q, "s": s.to(torch.bfloat16), "b": b.to(torch.bfloat16)}
+
+
+def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
+    """Random-init weights of the architecture (bf16 norms/embedding, int4 group-64 linears)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    bf = torch.bfloat16
+    rn = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=gen, device=device))  # noqa: E731
+    H, I, G = cfg.hidden, cfg.intermediate, cfg.group_size
+    layers: List[Dict] = []
+    for i in range(cfg.layers):
+        L: Dict = {"in_norm": (1.0 + 0.1 * rn(H)).to(bf), "post_norm": (1.0 + 0.1 * rn(H)).to(bf),
+                   "gate_up": _rand_quantized(2 * I, H, gen, device, G), "down": _rand_quantized(H, I, gen, device, G)}
+        if cfg.is_attention(i):
+            L["proj"] = _rand_quantized(cfg.attn_proj_n, H, gen, device, G)
+            L["q_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
+            L["k_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
+            L["o_proj"] = _rand_quantized(H, cfg.q_heads * cfg.head_dim, gen, device, G)
+        else:
+            L["proj"] = _rand_quantized(cfg.gdn_proj_n, H, gen, device, G)
+            L["conv_w"] = rn(cfg.conv_dim, cfg.conv_kernel, std=0.5).to(bf)
+            L["A_log"] = torch.log(0.5 + 4.0 * torch.rand(cfg.gdn_v_heads, generator=gen, device=device)).float()
+            L["dt_bias"] = rn(cfg.gdn_v_heads, std=0.5).float()
+            L["g_norm"] = (1.0 + 0.1 * rn(cfg.gdn_dv)).to(bf)
+            L["out_proj"] = _rand_quantized(H, cfg.gdn_v_heads * cfg.gdn_dv, gen, device, G)
+        layers.append(L)
+    return {"layers": layers, "embed": rn(cfg.vocab, H, std=1.0).to(bf), "norm": (1.0 + 0.1 * rn(H)).to(bf),
+            "lm_head": _rand_quantized(cfg.vocab, H, gen, device, G)}
+
+
+def weights_to(weights, device):
+    if isinstance(weights, dict):
+        return {k: weights_to(v, device) for k, v in weights.items()}
+    if isinstance(weights, list):
+        return [weights_to(v, device) for v in weights]
+    return weights.to(device)
+
+
+class HybridVerifyModel:
+    """Preallocated verify-step engine.  ``tp_world`` > 1 runs one tensor-parallel shard (heads, the MLP's
+    intermediate dimension and the vocabulary are split; ``all_reduce`` sums the row-parallel outputs)."""
+
+    def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None):
+        _declare()
+        self.cfg, self.w, self.dev = cfg, weights, torch.device(device)
+        self.lib = _lib.lib()
+        self.all_reduce, self.all_gather = all_reduce, all_gather
+        T, H, bf = cfg.block, cfg.hidden, torch.bfloat16
+        dev = self.dev
+        z = lambda *s, dt=bf: torch.zeros(*s, dtype=dt, device=dev)  # noqa: E731
+        self.gdn_layers = [i for i in range(cfg.layers) if not cfg.is_attention(i)]
+        self.attn_layers = [i for i in range(cfg.layers) if cfg.is_attention(i)]
+        Lg, La = max(1, len(self.gdn_layers)), max(1, len(self.attn_layers))
+        self.h, self.x, self.delta = z(T, H), z(T, H), z(T, H)
+        self.proj = z(T, max(cfg.gdn_proj_n, cfg.attn_proj_n))
+        self.mix = z(T, max(cfg.q_heads * cfg.head_dim, cfg.gdn_v_heads * cfg.gdn_dv))
+        self.gu, self.act = z(T, 2 * cfg.intermediate), z(T, cfg.intermediate)
+        self.logits = z(T, cfg.vocab)
+        self.tokens = z(T, dt=torch.int32)
+        # GatedDeltaNet: per-layer step inputs double as the rollback tape (recurrent_rollback_cache.py:116-127)
+        self.gq = z(T, cfg.gdn_k_heads, cfg.gdn_dk)
+        self.gv = z(T, cfg.gdn_v_heads, cfg.gdn_dv)
+        self.gbeta = z(T, cfg.gdn_v_heads, dt=torch.float32)
+        self.gy = z(T, cfg.gdn_v_heads, cfg.gdn_dv)
+        self.tape = z(Lg, T, cfg.gdn_v_heads, cfg.gdn_dv, dt=torch.float32)
+        self.tape_k = z(Lg, T, cfg.gdn_k_heads, cfg.gdn_dk)
+        self.tape_g = z(Lg, T, cfg.gdn_v_heads, dt=torch.float32)
+        self.tape_qkv = z(Lg, T, cfg.conv_dim)
+        self.state = [z(Lg, cfg.gdn_v_heads, cfg.gdn_dv, cfg.gdn_dk, dt=torch.float32) for _ in range(2)]
+        self.conv = [z(Lg, cfg.conv_kernel - 1, cfg.conv_dim) for _ in range(2)]
+        self.cur = 0                 # index of the committed state / conv window
+        self._armed = False
+        # full attention
+        self.kcache = z(La, cfg.kv_heads, cfg.max_context, cfg.head_dim)
+        self.vcache = z(La, cfg.kv_heads, cfg.max_context, cfg.head_dim)
+        self.aq = z(cfg.q_heads, T, cfg.head_dim)
+        self.ao = z(cfg.q_heads, T, cfg.head_dim)
+        self.offset = 0
+        self.steps_dev = z(1, dt=torch.int32)
+        with torch.cuda.device(dev):
+            need = 256
+            for L in weights["layers"]:
+                for name in ("proj", "o_proj", "out_proj", "gate_up", "down"):
+                    if name in L:
+                        need = max(need, self.lib.dflash_verify_qmm_workspace_bytes(T, L[name]["w"].shape[1] * 8,
+                                                                                    L[name]["w"].shape[0], cfg.group_size))
+            need = max(need, self.lib.dflash_verify_qmm_workspace_bytes(T, H, weights["lm_head"]["w"].shape[0], cfg.group_size))
+            self.qmm_ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+            sdpa_need = self.lib.dflash_verify_sdpa_workspace_bytes(1, cfg.q_heads, cfg.kv_heads, cfg.max_context,
+                                                                    cfg.head_dim, 0)
+            self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
+        self.launches_per_step = 0
+
+    # ---- helpers -------------------------------------------------------------------------------------
+    def _st(self):
+        return torch.cuda.current_stream(self.dev).cuda_stream
+
+    def _chk(self, st, what):
+        self.launches_per_step += 1
+        _lib.check(st, what)
+
+    def _qmm(self, x, W, out):
+        n, k = W["w"].shape[0], W["w"].shape[1] * 8
+        # `out` is flat storage: the result is written as a contiguous [T, n] array at its start
+        st = self.lib.dflash_verify_qmm(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
+                                        out.data_ptr(), self.cfg.block, k, n, self.cfg.group_size, _lib.BF16,
+                                        self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
+        self._chk(st, "dflash_verify_qmm")
+
+    def _add_rmsnorm(self, delta, w):
+        st = self.lib.dflash_add_rmsnorm(self.h.data_ptr(), _lib.ptr(delta), w.data_ptr(), self.h.data_ptr(),
+                                         self.x.data_ptr(), self.cfg.block, self.cfg.hidden, self.cfg.eps, _lib.BF16, self._st())
+        self._chk(st, "dflash_add_rmsnorm")
+
+    def prefill_synthetic(self, context_len: int, seed: int) -> None:
+        """Stands in for a prefill: fills the KV caches (N(0,1)), GDN states (N(0,0.1)) and conv windows."""
+        gen = torch.Generator(device=self.dev).manual_seed(seed)
+        if context_len + self.cfg.block > self.cfg.max_context:
+            raise ValueError("context does not fit max_context")
+        self.kcache[:, :, :context_len].copy_(torch.randn(self.kcache[:, :, :context_len].shape, generator=gen, device=self.dev))
+        self.vcache[:, :, :context_len].copy_(torch.randn(self.vcache[:, :, :context_len].shape, generator=gen, device=self.dev))
+        self.state[self.cur].copy_(0.1 * torch.randn(self.state[0].shape, generator=gen, device=self.dev))
+        self.conv[self.cur].copy_(torch.randn(self.conv[0].shape, generator=gen, device=self.dev))
+        self.offset = context_len
+
+    # ---- one verify pass (runtime.py:779-821 with the hooks of :351-452 and :515-613) ---------------------
+    def arm_rollback(self, prefix_len: int = 0) -> None:
+        """O(1): the committed buffers (index ``cur``) are the snapshot; a verify pass only writes the others."""
+        del prefix_len
+        self._armed = True
+
+    def verify(self, ids: torch.Tensor) -> torch.Tensor:
+        """Enqueues the whole step for ``ids`` (int32 CUDA, ``block`` tokens); returns the logits buffer
+        ``[block, vocab]``.  Greedy tokens are left in ``self.tokens``."""
+        cfg, lib, T = self.cfg, self.lib, self.cfg.block
+        if ids.dtype != torch.int32 or not ids.is_cuda or ids.numel() != T:
+            raise ValueError(f"ids must be {T} int32 tokens on the CUDA device")
+        if self.offset + T > cfg.max_context:
+            raise ValueError("KV cache capacity exceeded")
+        self.launches_per_step = 0
+        st, BF = self._st(), _lib.BF16
+        cur, nxt = self.cur, self.cur ^ 1
+        self._chk(lib.dflash_embed(ids.data_ptr(), self.w["embed"].data_ptr(), self.h.data_ptr(), T, cfg.hidden,
+                                   cfg.vocab, BF, st), "dflash_embed")
+        delta = None
+        ig = ia = 0
+        N = self.offset + T
+        for i, L in enumerate(self.w["layers"]):
+            self._add_rmsnorm(delta, L["in_norm"])
+            self._qmm(self.x, L["proj"], self.proj)
+            if cfg.is_attention(i):
+                ld = L["proj"]["w"].shape[0]
+                k_off = 2 * cfg.q_heads * cfg.head_dim
+                v_off = k_off + cfg.kv_heads * cfg.head_dim
+                hs = cfg.max_context * cfg.head_dim
+                self._chk(lib.dflash_attn_prep(self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(),
+                                               L["k_norm"].data_ptr(), self.aq.data_ptr(), self.kcache[ia].data_ptr(),
+                                               self.vcache[ia].data_ptr(), hs, T, cfg.q_heads, cfg.kv_heads, cfg.head_dim,
+                                               cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st), "dflash_attn_prep")
+                self._chk(lib.dflash_verify_sdpa(self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(),
+                                                 None, self.ao.data_ptr(), 1, cfg.q_heads, cfg.kv_heads, N, cfg.head_dim,
+                                                 hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
+                                                 self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st), "dflash_verify_sdpa")
+                self.launches_per_step += 1      # partials + combine
+                self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix.data_ptr(), T,
+                                               cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
+                self._qmm(self.mix, L["o_proj"], self.delta)
+                ia += 1
+            else:
+                ld = L["proj"]["w"].shape[0]
+                z_off = cfg.conv_dim
+                b_off = z_off + cfg.gdn_v_heads * cfg.gdn_dv
+                a_off = b_off + cfg.gdn_v_heads
+                self._chk(lib.dflash_gdn_prep(self.proj.data_ptr(), ld, z_off, b_off, a_off, self.conv[cur][ig].data_ptr(),
+                                              L["conv_w"].data_ptr(), None, L["A_log"].data_ptr(), L["dt_bias"].data_ptr(),
+                                              self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
+                                              self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), self.conv[nxt][ig].data_ptr(),
+                                              self.tape_qkv[ig].data_ptr(), T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
+                                              cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, st), "dflash_gdn_prep")
+                self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
+                                                      self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
+                                                      self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
+                                                      self.gy.data_ptr(), self.tape[ig].data_ptr(), 1, T, cfg.gdn_k_heads,
+                                                      cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF, _lib.F32, st),
+                          "dflash_gdn_forward_tape")
+                self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
+                                                   self.mix.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
+                          "dflash_gated_rmsnorm")
+                self._qmm(self.mix, L["out_proj"], self.delta)
+                ig += 1
+            if self.all_reduce is not None:
+                self.all_reduce(self.delta)
+            self._add_rmsnorm(self.delta, L["post_norm"])
+            self._qmm(self.x, L["gate_up"], self.gu)
+            self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
+                      "dflash_swiglu")
+            self._qmm(self.act, L["down"], self.delta)
+            if self.all_reduce is not None:
+                self.all_reduce(self.delta)
+            delta = self.delta
+        self._add_rmsnorm(delta, self.w["norm"])
+        self._qmm(self.x, self.w["lm_head"], self.logits)
+        v_local = self.w["lm_head"]["w"].shape[0]
+        self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
+        return self.logits[:, :v_local] if v_local == self.logits.shape[1] else self.logits.view(-1)[: T * v_local].view(T, v_local)
+
+    # ---- acceptance and rollback (runtime.py:101-108, 878-907; recurrent_rollback_cache.py:148-171) -------
+    @staticmethod
+    def match_acceptance_length(drafted: torch.Tensor, posterior: torch.Tensor) -> torch.Tensor:
+        """Number of leading positions where the drafted tokens equal the target's greedy tokens."""
+        if drafted.numel() == 0:
+            return torch.zeros((), dtype=torch.int32, device=posterior.device)
+        m = (drafted == posterior[: drafted.numel()]).to(torch.int32)
+        return torch.cumprod(m, dim=0).sum().to(torch.int32)
+
+    def rollback(self, n_accepted, drafted_tokens: int = 0) -> None:
+        """Commits ``n_accepted + 1`` positions of the last verify pass.  ``n_accepted`` is a host int, or a
+        1-element int32 CUDA tensor (then nothing synchronises and the replay reads it on the device; the KV
+        offset must then be advanced by the caller with the same number once it reaches the host)."""
+        cfg, T = self.cfg, self.cfg.block
+        cur, nxt = self.cur, self.cur ^ 1
+        on_device = isinstance(n_accepted, torch.Tensor)
+        if not on_device and drafted_tokens > 0 and int(n_accepted) == drafted_tokens:
+            # fully accepted: keep the forward state, nothing to replay (runtime.py:886-891)
+            self.cur = nxt
+            self.offset += T
+            self._armed = False
+            return
+        Lg = len(self.gdn_layers)
+        if Lg:
+            if on_device:
+                self.steps_dev.copy_((n_accepted.to(torch.int32) + 1).clamp_(0, T).reshape(1))
+                steps_host, steps_dev = T, self.steps_dev
+            else:
+                steps_host, steps_dev = min(int(n_accepted) + 1, T), None
+            st = self.lib.dflash_tape_replay(self.tape.data_ptr(), self.tape_k.data_ptr(), self.tape_g.data_ptr(), None,
+                                             self.state[cur].data_ptr(), self.state[nxt].data_ptr(), Lg, T, steps_host,
+                                             _lib.ptr(steps_dev), cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv,
+                                             0, _lib.BF16, _lib.F32, self._st())
+            _lib.check(st, "dflash_tape_replay")
+            keep = cfg.conv_kernel - 1
+            conv_in = torch.cat([self.conv[cur], self.tape_qkv], dim=1)          # [Lg, keep + T, conv_dim]
+            if on_device:
+                idx = (self.steps_dev.long() + torch.arange(keep, device=self.dev)).clamp_(max=keep + T - 1)
+                self.conv[nxt].copy_(conv_in.index_select(1, idx))
+            else:
+                self.conv[nxt].copy_(conv_in[:, steps_host: steps_host + keep])
+        self.cur = nxt
+        if not on_device:
+            self.offset += int(n_accepted) + 1
+        self._armed = False

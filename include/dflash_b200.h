@@ -142,6 +142,45 @@ DFLASH_API int dflash_verify_sdpa_static(const void* q, const void* k, const voi
                                          long long v_head_stride, long long v_seq_stride, float scale, int dtype,
                                          int num_splits, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Fused element-wise / normalisation kernels between the matmuls of a verify step.  They restate the
+ * layer dataflow of the reference's model hooks; dtype is bf16 or f16, arithmetic fp32, T_rows token rows.
+ */
+/* h_out = h_in + delta (delta may be NULL; h_out may be NULL or alias h_in); x = rms_norm(h_out) * w.
+ * The residual add and the layer norms around every mixer / MLP (mlx-lm decoder layer called at runtime.py:802-809). */
+DFLASH_API int dflash_add_rmsnorm(const void* h_in, const void* delta, const void* w, void* h_out, void* x, int T_rows,
+                                  int H, float eps, int dtype, void* stream);
+/* y[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]: SwiGLU on a fused [gate | up] projection (mlx-lm MLP). */
+DFLASH_API int dflash_swiglu(const void* gate_up, void* y, int T_rows, int I, int dtype, void* stream);
+/* h[t,:] = table[ids[t],:]  (embed_tokens, runtime.py:788). */
+DFLASH_API int dflash_embed(const int* ids, const void* table, void* h, int T_rows, int H, int V, int dtype, void* stream);
+/* out[t] = first index of the maximum of logits[t,:]  (greedy_tokens_with_mask, runtime.py:90-98). */
+DFLASH_API int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream);
+/* GatedDeltaNet layer between its input projections and the recurrence (runtime.py:368-403).
+ * proj[t, 0:conv_dim] = qkv (q heads | k heads | v heads), z at z_off, b and a (Hv columns each) at b_off, a_off;
+ * ld = row stride of proj in elements.  conv_state [Kc-1, conv_dim], conv_w [conv_dim, Kc] (tap j multiplies row t+j
+ * of [conv_state ; qkv]), conv_b [conv_dim] or NULL.  Outputs: q,k [T,Hk,Dk] (q = Dk^-1 rms_norm, k = Dk^-1/2 rms_norm),
+ * v [T,Hv,Dv], g f32 [T,Hv] = exp(-exp(A_log) softplus(a + dt_bias)), beta f32 [T,Hv] = sigmoid(b),
+ * new_conv_state [Kc-1, conv_dim] (must not alias conv_state), qkv_tape [T, conv_dim] (copy kept for the rollback). */
+DFLASH_API int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_off, int a_off, const void* conv_state,
+                               const void* conv_w, const void* conv_b, const float* A_log, const float* dt_bias, void* q,
+                               void* k, void* v, float* g, float* beta, void* new_conv_state, void* qkv_tape, int T_rows,
+                               int Hk, int Hv, int Dk, int Dv, int conv_kernel, float eps, int dtype, void* stream);
+/* out[t, hv*Dv+d] = rms_norm(y[t,hv,:])[d] * w[d] * silu(z[t,hv,d]), z read from proj at z_off (runtime.py:445). */
+DFLASH_API int dflash_gated_rmsnorm(const void* y, const void* proj, long long ld, int z_off, const void* w, void* out,
+                                    int T_rows, int Hv, int Dv, float eps, int dtype, void* stream);
+/* Gated attention layer between its projections and the attention kernel (runtime.py:527-555).
+ * proj row = [(query D | gate D) x Hq | k Hk*D at k_off | v Hk*D at v_off].  q,k get a per-head RMSNorm with weights
+ * and a rotary embedding of the first rope_dims channels (half-split pairing) at position offset + t; q is written as
+ * [Hq,T,D]; k and v are appended to the caches [Hk, capacity, D] (cache_head_stride elements per head) at row offset+t. */
+DFLASH_API int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                                const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
+                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
+                                int dtype, void* stream);
+/* out[t, hq*D+d] = o[hq,t,d] * sigmoid(gate[t,hq,d])  (runtime.py:611-612). */
+DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, int T_rows, int Hq, int D,
+                                int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

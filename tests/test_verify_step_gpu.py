@@ -1,0 +1,97 @@
+"""GPU parity of the whole 16-token verify step + rollback against the CPU oracle on a small hybrid model
+(3 GatedDeltaNet layers + 1 full-attention layer).  Tolerances: logits max-rel <= 3e-2 (bf16 activations through
+four layers), greedy tokens identical wherever the oracle's top-2 margin exceeds that bound, fp32 GDN state
+after rollback <= 1e-2 relative (its inputs are bf16 activations), first-layer state <= 1e-4."""
+import pytest
+import torch
+
+from oracle import gdn as og
+from oracle import model as om
+from tests.test_verify_step import small_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.detach().cpu().float(), b.detach().cpu().float()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-6))
+
+
+@pytest.fixture(scope="module")
+def setup():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import HybridVerifyModel, weights_to
+    cfg, W, caches, ids, ctx = small_case()
+    m = HybridVerifyModel(cfg, weights_to(W, "cuda"), "cuda")
+    for l in range(len(caches["state"])):
+        m.state[m.cur][l].copy_(caches["state"][l])
+        m.conv[m.cur][l].copy_(caches["conv"][l])
+    for l in range(len(caches["k"])):
+        m.kcache[l].copy_(caches["k"][l])
+        m.vcache[l].copy_(caches["v"][l])
+    m.offset = ctx
+    return cfg, W, caches, ids, ctx, m
+
+
+def test_logits_tokens_and_rollback(setup):
+    cfg, W, caches, ids, ctx, m = setup
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
+    m.arm_rollback()
+    logits = m.verify(ids.cuda())
+    torch.cuda.synchronize()
+    assert m.launches_per_step > 20
+    assert _rel(logits, ref_logits) <= 3e-2
+    # greedy argmax where the oracle's margin is larger than the error bound
+    rl = ref_logits.float()
+    top2 = rl.topk(2, dim=-1).values
+    sure = (top2[:, 0] - top2[:, 1]) > 3e-2 * rl.abs().max()
+    assert int(sure.sum()) >= 1
+    assert torch.equal(m.tokens.cpu()[sure], ref_toks[sure])
+    # per-layer tape and forward state
+    for l, tp in enumerate(tapes):
+        tol = 1e-4 if l == 0 else 2e-2
+        assert _rel(m.tape[l], tp["tape"]) <= tol, l
+        assert _rel(m.state[m.cur ^ 1][l], ref_new["state"][l]) <= tol, l
+    assert torch.equal(m.tape_qkv[0].cpu(), tapes[0]["qkv"])
+    # rollback to 5 accepted drafts (6 committed positions), host int
+    n_acc = 5
+    snap_cur = m.cur
+    m.rollback(n_acc, drafted_tokens=15)
+    torch.cuda.synchronize()
+    assert m.cur == snap_cur ^ 1 and m.offset == ctx + n_acc + 1 and not m._armed
+    for l, tp in enumerate(tapes):
+        want = og.tape_replay_ref(tp["tape"][None], tp["k"][None], tp["g"][None], caches["state"][l][None], steps=n_acc + 1)[0]
+        assert _rel(m.state[m.cur][l], want) <= (1e-4 if l == 0 else 2e-2), l
+        conv = og.rebuild_conv_state(caches["conv"][l][None], tp["qkv"][None], n_acc + 1, cfg.conv_kernel)[0]
+        if l == 0:
+            assert torch.equal(m.conv[m.cur][l].cpu(), conv)
+
+
+def test_device_side_accept_length_and_full_accept(setup):
+    cfg, W, caches, ids, ctx, m = setup
+    # restore the committed buffers, run again, roll back with the accepted length living on the device
+    for l in range(len(caches["state"])):
+        m.state[m.cur][l].copy_(caches["state"][l])
+        m.conv[m.cur][l].copy_(caches["conv"][l])
+    m.offset = ctx
+    m.arm_rollback()
+    m.verify(ids.cuda())
+    tape0 = m.tape[0].clone()
+    k0, g0 = m.tape_k[0].clone(), m.tape_g[0].clone()
+    n_dev = torch.tensor([8], dtype=torch.int32, device="cuda")
+    m.rollback(n_dev)
+    torch.cuda.synchronize()
+    want = og.tape_replay_ref(tape0.cpu()[None], k0.cpu()[None], g0.cpu()[None], caches["state"][0][None], steps=9)[0]
+    assert _rel(m.state[m.cur][0], want) <= 1e-4
+    # fully accepted block: the forward state is kept, no replay
+    for l in range(len(caches["state"])):
+        m.state[m.cur][l].copy_(caches["state"][l])
+        m.conv[m.cur][l].copy_(caches["conv"][l])
+    m.offset = ctx
+    m.arm_rollback()
+    m.verify(ids.cuda())
+    fwd = m.state[m.cur ^ 1].clone()
+    m.rollback(15, drafted_tokens=15)
+    assert torch.equal(m.state[m.cur], fwd) and m.offset == ctx + 16
