@@ -36,8 +36,8 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(
 
 // h_out = h_in (+ delta);  x = rmsnorm(h_out) * w.  One CTA per token row.
 template <typename T>
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* __restrict__ h_in, const T* __restrict__ delta,
-                                                          const T* __restrict__ w, T* __restrict__ h_out,
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* h_in, const T* __restrict__ delta,
+                                                          const T* __restrict__ w, T* h_out,
                                                           T* __restrict__ x, int H, float eps) {
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;
@@ -51,8 +51,13 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* __restrict__ 
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)H + eps);
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = tof<T>(h_in[row + i]);
-    if (delta != nullptr) v = tof<T>(fromf<T>(v + tof<T>(delta[row + i])));
+    float v;
+    if (h_out != nullptr) {
+      v = tof<T>(h_out[row + i]);  // written by this same thread above (h_out may alias h_in)
+    } else {
+      v = tof<T>(h_in[row + i]);
+      if (delta != nullptr) v = tof<T>(fromf<T>(v + tof<T>(delta[row + i])));
+    }
     x[row + i] = fromf<T>(v * inv * tof<T>(w[i]));
   }
 }

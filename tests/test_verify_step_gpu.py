@@ -54,7 +54,7 @@ def test_logits_tokens_and_rollback(setup):
         tol = 1e-4 if l == 0 else 2e-2
         assert _rel(m.tape[l], tp["tape"]) <= tol, l
         assert _rel(m.state[m.cur ^ 1][l], ref_new["state"][l]) <= tol, l
-    assert torch.equal(m.tape_qkv[0].cpu(), tapes[0]["qkv"])
+    assert _rel(m.tape_qkv[0], tapes[0]["qkv"]) <= 1e-2          # a bf16 matmul output: ulp-level differences
     # rollback to 5 accepted drafts (6 committed positions), host int
     n_acc = 5
     snap_cur = m.cur
@@ -66,7 +66,7 @@ def test_logits_tokens_and_rollback(setup):
         assert _rel(m.state[m.cur][l], want) <= (1e-4 if l == 0 else 2e-2), l
         conv = og.rebuild_conv_state(caches["conv"][l][None], tp["qkv"][None], n_acc + 1, cfg.conv_kernel)[0]
         if l == 0:
-            assert torch.equal(m.conv[m.cur][l].cpu(), conv)
+            assert _rel(m.conv[m.cur][l], conv) <= 1e-2
 
 
 def test_device_side_accept_length_and_full_accept(setup):
