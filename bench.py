@@ -154,6 +154,13 @@ class QmmWorkload:
     def e2e_value(self, seconds, calls):
         return seconds * 1e6 / calls
 
+    def roofline(self, ms_per_step, aux_ms, peak, peak_src):
+        us_per_launch = ms_per_step * 1e3 / self.launches_per_step
+        achieved = self.per_launch_bytes / us_per_launch / 1e3
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": 28.50e6 if self.world == 1 else None, "peak_source": peak_src, "kernel": "qmm_stream_kernel",
+                "algorithmic_bytes_per_launch": self.per_launch_bytes, "us_per_launch": us_per_launch}
+
     def cpu_baseline(self, budget_s=12.0):
         """The C restatement of the stock CPU path (oracle/qmm_ref.c) on all host cores, same shape."""
         import torch
@@ -180,30 +187,167 @@ class QmmWorkload:
                                           "MLX unavailable on this box: CPU baseline = C restatement of the stock qmm"}
 
 
-WORKLOADS = {"qmm_cfg1": QmmWorkload}
-DEFAULT_WORKLOAD = "qmm_cfg1"
+class DenseStepWorkload:
+    """Configuration 4 of BASELINE.json: one 16-token verify step of the dense hybrid model (64 layers, 3 GDN : 1
+    attention, hidden 5120, SwiGLU 17408, 24 q / 4 KV heads of 256, int4 g64 linears, vocab 151936) at context
+    4096, random-init weights.  GDN dimensions come from configuration 2 (16 key / 32 value heads of 128).
+    With R ranks the step is tensor-parallel (heads, MLP intermediate and vocabulary split R ways, one
+    all-reduce after each row-parallel matmul): strong scaling."""
+    name = "dense_step_cfg4"
+    metric, unit, higher_is_better, scaling, dtype = "m16_int4_verify_step_latency", "us", False, "strong", "bf16"
+    CONTEXT = 4096
+
+    def __init__(self, rank, world, device, layers=None):
+        import torch
+        from dflash_mlx_b200.verify_step import HybridConfig, HybridVerifyModel, init_weights
+        from dflash_mlx_b200.parallel import shard_config, make_collectives
+        self.torch, self.device, self.world, self.rank = torch, device, world, rank
+        full = HybridConfig(max_context=self.CONTEXT + 64)
+        if layers:
+            full.layers = layers
+        self.full_cfg = full
+        cfg = shard_config(full, world)
+        self.cfg = cfg
+        with torch.cuda.device(device):
+            weights = init_weights(cfg, 0xDF1D + rank, device)
+        ar, ag = make_collectives(world)
+        self.model = HybridVerifyModel(cfg, weights, device, all_reduce=ar, all_gather=ag)
+        self.model.prefill_synthetic(self.CONTEXT, 0xDF1D)
+        gen = torch.Generator().manual_seed(0xDF1D)
+        self.ids_host = torch.randint(0, full.vocab, (cfg.block,), generator=gen, dtype=torch.int32).pin_memory()
+        self.ids = self.ids_host.to(device)
+        self.tok_host = torch.empty(cfg.block, dtype=torch.int32).pin_memory()
+        self.model.verify(self.ids)
+        self.launches_per_step = self.model.launches_per_step
+        self.units_per_step = 1
+        self.bytes = self.model.algorithmic_bytes()
+        self.n_qmm = len(self.model.qmm_launch_list())
+        self.config = {"workload": self.name, "layers": cfg.layers, "hidden": cfg.hidden, "context": self.CONTEXT,
+                       "block": cfg.block, "vocab": full.vocab, "gdn_dims": "Hk16/Hv32/128x128 (from config 2)",
+                       "algorithmic_bytes_per_step_per_rank": self.bytes,
+                       "l2": "inputs larger than L2: one step streams %.1f GB of weights" % (self.bytes["qmm"] / 1e9),
+                       "parallelism": f"tp{world}"}
+
+    def step(self):
+        self.model.verify(self.ids)
+
+    def aux_step(self):
+        self.model.run_qmm_only()
+
+    def e2e_step(self):
+        self.model.verify_captured(self.ids_host)        # pinned host ids -> device inside the call
+        self.tok_host.copy_(self.model.tokens, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return 1
+
+    h2d_bytes = property(lambda self: self.cfg.block * 4)
+    d2h_bytes = property(lambda self: self.cfg.block * 4)
+
+    def value_from_ms(self, ms_per_step):
+        return ms_per_step * 1e3
+
+    def e2e_value(self, seconds, calls):
+        return seconds * 1e6 / calls
+
+    def roofline(self, ms_per_step, aux_ms, peak, peak_src):
+        """Dominant kernel = the int4 matmul: its launches alone are replayed as a second CUDA graph."""
+        us_per_launch = aux_ms * 1e3 / self.n_qmm
+        per_launch = self.bytes["qmm"] / self.n_qmm
+        achieved = per_launch / us_per_launch / 1e3
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": peak_src, "kernel": "qmm_stream_kernel",
+                "launches_per_step": self.n_qmm, "algorithmic_bytes_per_launch": per_launch,
+                "us_per_launch": us_per_launch, "matmul_share_of_step": aux_ms / ms_per_step,
+                "whole_step_gbps": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9}
+
+    def cpu_baseline(self, budget_s=25.0):
+        return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s)
+
+
+def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
+    """CPU path of one dense verify step on all host cores, from a bounded sample: every distinct linear shape
+    is timed with the C restatement of the stock qmm (oracle/qmm_ref.c), the GDN recurrence and the attention
+    with the torch oracle on one layer each; the step time is sum(count x time).  Element-wise glue is left out
+    (it favours the CPU number)."""
+    import torch
+    from oracle import gdn as og
+    from oracle import qmm as oq
+    from oracle import sdpa as osd
+    from oracle.build_ref import load
+    torch.set_num_threads(os.cpu_count() or 1)
+    out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "gpurun_out" / "oracle_native")))
+    try:
+        lib, note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
+    except Exception:
+        lib, note = load(native=False), "gcc -O3 -fopenmp"
+    n_attn = sum(cfg.is_attention(i) for i in range(cfg.layers))
+    n_gdn = cfg.layers - n_attn
+    H, I, G, T = cfg.hidden, cfg.intermediate, cfg.group_size, cfg.block
+    shapes = [("gdn_proj", cfg.gdn_proj_n, H, n_gdn), ("gdn_out", H, cfg.gdn_v_heads * cfg.gdn_dv, n_gdn),
+              ("attn_proj", cfg.attn_proj_n, H, n_attn), ("attn_o", H, cfg.q_heads * cfg.head_dim, n_attn),
+              ("gate_up", 2 * I, H, cfg.layers), ("down", H, I, cfg.layers), ("lm_head", cfg.vocab, H, 1)]
+    total, parts = 0.0, {}
+    reps = 3 if budget_s >= 20 else 2
+    for name, n, k, count in shapes:
+        if count == 0:
+            continue
+        wq, s, b = oq.random_quantized(n, k, seed=7, group_size=G)
+        x = torch.randn(T, k).bfloat16()
+        y = torch.empty(T, n, dtype=torch.float32)
+        args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), T, k, n, G)
+        lib.qmm_ref(*args)
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            lib.qmm_ref(*args)
+            ts.append(time.perf_counter() - t0)
+        parts[name] = min(ts)
+        total += count * min(ts)
+    c = og.make_gdn_case(seed=1, T=T, Hk=cfg.gdn_k_heads, Hv=cfg.gdn_v_heads, Dk=cfg.gdn_dk, Dv=cfg.gdn_dv)
+    t0 = time.perf_counter()
+    og.gated_delta_with_tape_ref(c["q"], c["k"], c["v"], c["g"], c["beta"], c["state"])
+    parts["gdn_recurrence"] = time.perf_counter() - t0
+    total += n_gdn * parts["gdn_recurrence"]
+    q, k_, v, sc = osd.make_sdpa_case(context + T, seed=2, Hq=cfg.q_heads, Hk=cfg.kv_heads, D=cfg.head_dim)
+    t0 = time.perf_counter()
+    osd.sdpa_ref(q, k_, v, sc)
+    parts["attention"] = time.perf_counter() - t0
+    total += n_attn * parts["attention"]
+    return {"value": total * 1e6, "unit": "us", "cores": int(lib.qmm_ref_threads()), "kind": "port",
+            "sample": "sum over the step of count x time of each distinct op (7 linear shapes with the C qmm, best of "
+                      f"{reps}; one GDN recurrence and one attention with the torch oracle); {note}; MLX unavailable on "
+                      "this box: CPU baseline = restatement of the stock path",
+            "parts_ms": {k2: round(v2 * 1e3, 3) for k2, v2 in parts.items()}}
+
+
+WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload}
+DEFAULT_WORKLOAD = "dense_step_cfg4"
 
 
 def run_reference_arm(args, rank, world):
     """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
     if rank != 0:
         return
-    os.environ.setdefault("CUDA_VISIBLE_DEVICES", "")
     cls = WORKLOADS[args.workload]
-    w = cls.__new__(cls)
-    import torch
-    w.torch = torch
-    gen = torch.Generator().manual_seed(0xDF1A)
-    w.x_host = torch.randn(cls.M, cls.K, generator=gen).bfloat16()
-    w.world, w.n_local = 1, cls.N
-    budget = max(3.0, min(60.0, 2.0 * (args.steps + args.warmup)))
-    cb = w.cpu_baseline(budget_s=budget)
+    budget = max(6.0, min(60.0, 2.0 * (args.steps + args.warmup)))
+    if cls is QmmWorkload:
+        import torch
+        w = cls.__new__(cls)
+        w.torch = torch
+        w.x_host = torch.randn(cls.M, cls.K, generator=torch.Generator().manual_seed(0xDF1A)).bfloat16()
+        w.world, w.n_local = 1, cls.N
+        cb = w.cpu_baseline(budget_s=budget)
+        config = {"workload": cls.name, "M": cls.M, "K": cls.K, "N": cls.N, "group_size": cls.G}
+    else:
+        from dflash_mlx_b200.verify_step import HybridConfig
+        cfg = HybridConfig(max_context=cls.CONTEXT + 64)
+        cb = dense_step_cpu_baseline(cfg, cls.CONTEXT, budget)
+        config = {"workload": cls.name, "layers": cfg.layers, "hidden": cfg.hidden, "context": cls.CONTEXT,
+                  "block": cfg.block, "vocab": cfg.vocab}
     line = {"impl": "reference", "metric": cls.metric, "value": cb["value"], "unit": cls.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
             "higher_is_better": cls.higher_is_better, "scaling": cls.scaling, "vs_baseline": None, "dtype": cls.dtype,
-            "data": "synthetic", "config": {"workload": cls.name, "M": cls.M, "K": cls.K, "N": cls.N,
-                                            "group_size": cls.G},
-            "cpu_baseline": cb,
+            "data": "synthetic", "config": config, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -244,34 +388,38 @@ def main():
     wl = WORKLOADS[args.workload](rank, world, device)
 
     # ---- device-resident loop: one CUDA graph = one step ----
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        wl.step()                     # untimed: creates workspaces, tensor maps, kernel attributes
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            wl.step()
-    torch.cuda.current_stream().wait_stream(side)
-    for _ in range(args.warmup):
-        graph.replay()
-    barrier()
+    def time_graph(fn, steps, warmup, sample=False):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()                      # untimed: creates workspaces, tensor maps, kernel attributes
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        if sample and rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
     sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+    ms_per_step = time_graph(wl.step, args.steps, args.warmup, sample=True)
+    aux_ms = time_graph(wl.aux_step, args.steps, args.warmup) if hasattr(wl, "aux_step") else None
 
     # ---- end to end through the public API with host buffers ----
     for _ in range(3):
@@ -294,16 +442,11 @@ def main():
 
     if rank == 0:
         peak, peak_src = measured_peaks()
-        us_per_launch = ms_per_step * 1e3 / wl.launches_per_step
-        achieved = wl.per_launch_bytes / us_per_launch / 1e3       # GB/s
         line = {"metric": wl.metric, "value": wl.value_from_ms(ms_per_step), "unit": wl.unit, "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": wl.higher_is_better, "scaling": wl.scaling, "vs_baseline": None,
                 "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                             "kernel": "qmm_stream_kernel", "algorithmic_bytes_per_launch": wl.per_launch_bytes,
-                             "us_per_launch": us_per_launch},
+                "roofline": wl.roofline(ms_per_step, aux_ms, peak, peak_src),
                 "e2e": {"value": wl.e2e_value(e2e_s, calls), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,
                         "d2h_bytes_per_step": wl.d2h_bytes, "calls": calls},
                 "gpu_launches": wl.launches_per_step * args.steps,

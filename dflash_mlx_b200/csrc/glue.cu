@@ -256,12 +256,12 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
 // out[t, hq*D + d] = o[hq, t, d] * sigmoid(gate[t, hq, d])   (runtime.py:611-612)
 template <typename T>
 __global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o, const T* __restrict__ proj, long long ld,
-                                                        T* __restrict__ out, int Tn, int Hq, int D) {
+                                                        T* __restrict__ out, long long out_ld, int Tn, int Hq, int D) {
   const size_t n = (size_t)Tn * Hq * D;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const int d = (int)(i % D), hq = (int)((i / D) % Hq), t = (int)(i / ((size_t)D * Hq));
     const float gate = tof<T>(proj[(size_t)t * ld + (size_t)hq * 2 * D + D + d]);
-    out[i] = fromf<T>(tof<T>(o[((size_t)hq * Tn + t) * D + d]) * sigmoidf(gate));
+    out[(size_t)t * out_ld + (size_t)hq * D + d] = fromf<T>(tof<T>(o[((size_t)hq * Tn + t) * D + d]) * sigmoidf(gate));
   }
 }
 
@@ -347,10 +347,10 @@ extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v
   DFLASH_DISPATCH(dtype, (attn_prep_kernel<T><<<(n + 3) / 4, 128, 0, st>>>(a)));
 }
 
-extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, int T_rows, int Hq, int D,
-                                int dtype, void* stream) {
-  if (!o || !proj || !out || T_rows < 1) return fail(DFLASH_ERR_BAD_ARG, "attn_post: bad argument");
+extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,
+                                int Hq, int D, int dtype, void* stream) {
+  if (!o || !proj || !out || T_rows < 1 || out_ld < (long long)Hq * D) return fail(DFLASH_ERR_BAD_ARG, "attn_post: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = (int)(((size_t)T_rows * Hq * D + 255) / 256);
-  DFLASH_DISPATCH(dtype, (attn_post_kernel<T><<<blocks, 256, 0, st>>>((const T*)o, (const T*)proj, ld, (T*)out, T_rows, Hq, D)));
+  DFLASH_DISPATCH(dtype, (attn_post_kernel<T><<<blocks, 256, 0, st>>>((const T*)o, (const T*)proj, ld, (T*)out, out_ld, T_rows, Hq, D)));
 }

@@ -41,7 +41,7 @@ def _declare():
     d("dflash_gdn_prep", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 12 + [_i32] * 6 + [_f32, _i32, _vp])
     d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
     d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_f32, _f32, _i32, _vp])
-    d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _i32, _i32, _i32, _i32, _vp])
+    d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _ll, _i32, _i32, _i32, _i32, _vp])
     _declared = True
 
 
@@ -107,7 +107,10 @@ def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
             L["proj"] = _rand_quantized(cfg.attn_proj_n, H, gen, device, G)
             L["q_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
             L["k_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
-            L["o_proj"] = _rand_quantized(H, cfg.q_heads * cfg.head_dim, gen, device, G)
+            ko = cfg.q_heads * cfg.head_dim
+            if getattr(cfg, "tp_world", 1) > 1:          # a shard's row-parallel K is padded to 8 groups
+                ko = (ko + 8 * G - 1) // (8 * G) * (8 * G)
+            L["o_proj"] = _rand_quantized(H, ko, gen, device, G)
         else:
             L["proj"] = _rand_quantized(cfg.gdn_proj_n, H, gen, device, G)
             L["conv_w"] = rn(cfg.conv_dim, cfg.conv_kernel, std=0.5).to(bf)
@@ -116,7 +119,7 @@ def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
             L["g_norm"] = (1.0 + 0.1 * rn(cfg.gdn_dv)).to(bf)
             L["out_proj"] = _rand_quantized(H, cfg.gdn_v_heads * cfg.gdn_dv, gen, device, G)
         layers.append(L)
-    return {"layers": layers, "embed": rn(cfg.vocab, H, std=1.0).to(bf), "norm": (1.0 + 0.1 * rn(H)).to(bf),
+    return {"layers": layers, "embed": rn(getattr(cfg, "embed_rows", cfg.vocab), H, std=1.0).to(bf), "norm": (1.0 + 0.1 * rn(H)).to(bf),
             "lm_head": _rand_quantized(cfg.vocab, H, gen, device, G)}
 
 
@@ -145,7 +148,9 @@ class HybridVerifyModel:
         Lg, La = max(1, len(self.gdn_layers)), max(1, len(self.attn_layers))
         self.h, self.x, self.delta = z(T, H), z(T, H), z(T, H)
         self.proj = z(T, max(cfg.gdn_proj_n, cfg.attn_proj_n))
-        self.mix = z(T, max(cfg.q_heads * cfg.head_dim, cfg.gdn_v_heads * cfg.gdn_dv))
+        # inputs of the row-parallel output projections (zero-filled: a shard's K may be padded up)
+        self.mix_attn = z(T, self._k_of("o_proj", cfg.q_heads * cfg.head_dim))
+        self.mix_gdn = z(T, self._k_of("out_proj", cfg.gdn_v_heads * cfg.gdn_dv))
         self.gu, self.act = z(T, 2 * cfg.intermediate), z(T, cfg.intermediate)
         self.logits = z(T, cfg.vocab)
         self.tokens = z(T, dt=torch.int32)
@@ -184,6 +189,12 @@ class HybridVerifyModel:
         self.launches_per_step = 0
 
     # ---- helpers -------------------------------------------------------------------------------------
+    def _k_of(self, name, default):
+        for L in self.w["layers"]:
+            if name in L:
+                return L[name]["w"].shape[1] * 8
+        return default
+
     def _st(self):
         return torch.cuda.current_stream(self.dev).cuda_stream
 
@@ -233,7 +244,7 @@ class HybridVerifyModel:
         st, BF = self._st(), _lib.BF16
         cur, nxt = self.cur, self.cur ^ 1
         self._chk(lib.dflash_embed(ids.data_ptr(), self.w["embed"].data_ptr(), self.h.data_ptr(), T, cfg.hidden,
-                                   cfg.vocab, BF, st), "dflash_embed")
+                                   self.w["embed"].shape[0], BF, st), "dflash_embed")
         delta = None
         ig = ia = 0
         N = self.offset + T
@@ -254,9 +265,9 @@ class HybridVerifyModel:
                                                  hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
                                                  self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st), "dflash_verify_sdpa")
                 self.launches_per_step += 1      # partials + combine
-                self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix.data_ptr(), T,
-                                               cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
-                self._qmm(self.mix, L["o_proj"], self.delta)
+                self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix_attn.data_ptr(),
+                                               self.mix_attn.shape[1], T, cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
+                self._qmm(self.mix_attn, L["o_proj"], self.delta)
                 ia += 1
             else:
                 ld = L["proj"]["w"].shape[0]
@@ -276,9 +287,9 @@ class HybridVerifyModel:
                                                       cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF, _lib.F32, st),
                           "dflash_gdn_forward_tape")
                 self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
-                                                   self.mix.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
+                                                   self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
                           "dflash_gated_rmsnorm")
-                self._qmm(self.mix, L["out_proj"], self.delta)
+                self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
@@ -294,7 +305,70 @@ class HybridVerifyModel:
         self._qmm(self.x, self.w["lm_head"], self.logits)
         v_local = self.w["lm_head"]["w"].shape[0]
         self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
+        if self.all_gather is not None:
+            # vocabulary-parallel greedy token: every rank contributes (best logit, global index) per row
+            world = getattr(cfg, "tp_world", 1)
+            lg = self.logits.view(-1)[: T * v_local].view(T, v_local)
+            vals = lg.gather(1, self.tokens.long()[:, None])[:, 0].float()
+            rank = torch.distributed.get_rank()
+            pair = torch.stack([vals, (self.tokens + rank * v_local).float()], dim=1).contiguous()
+            allp = torch.empty(world * T, 2, dtype=torch.float32, device=self.dev)
+            self.all_gather(allp, pair)
+            allp = allp.view(world, T, 2)
+            best = allp[..., 0].max(dim=0).values
+            idx = torch.where(allp[..., 0] == best[None], allp[..., 1], torch.full_like(allp[..., 1], 3e8)).min(dim=0).values
+            self.tokens.copy_(idx.to(torch.int32))
         return self.logits[:, :v_local] if v_local == self.logits.shape[1] else self.logits.view(-1)[: T * v_local].view(T, v_local)
+
+    def capture(self) -> None:
+        """Captures one verify pass at the current KV offset into a CUDA graph (replayed by verify_captured)."""
+        self.ids_static = torch.zeros(self.cfg.block, dtype=torch.int32, device=self.dev)
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            self.verify(self.ids_static)
+            torch.cuda.synchronize(self.dev)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self.verify(self.ids_static)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        self.graph_offset = self.offset
+
+    def verify_captured(self, ids: torch.Tensor) -> torch.Tensor:
+        """``verify`` as one graph launch; ``ids`` may be a pinned host tensor (copied asynchronously)."""
+        if getattr(self, "graph", None) is None or self.graph_offset != self.offset:
+            self.capture()
+        self.ids_static.copy_(ids, non_blocking=True)
+        self.graph.replay()
+        return self.logits
+
+    def qmm_launch_list(self):
+        """(x, W, out) of every matmul of a step, in launch order (used to time the matmuls alone)."""
+        out = []
+        for i, L in enumerate(self.w["layers"]):
+            out.append((self.x, L["proj"], self.proj))
+            out.append((self.mix_attn, L["o_proj"], self.delta) if self.cfg.is_attention(i) else (self.mix_gdn, L["out_proj"], self.delta))
+            out.append((self.x, L["gate_up"], self.gu))
+            out.append((self.act, L["down"], self.delta))
+        out.append((self.x, self.w["lm_head"], self.logits))
+        return out
+
+    def run_qmm_only(self):
+        for x, W, o in self.qmm_launch_list():
+            self._qmm(x, W, o)
+
+    def algorithmic_bytes(self):
+        """Algorithmic HBM bytes of one step: every matmul's operands, KV read, GDN state read+write, tapes."""
+        cfg, T, G = self.cfg, self.cfg.block, self.cfg.group_size
+        qmm = 0
+        for x, W, o in self.qmm_launch_list():
+            n, k = W["w"].shape[0], W["w"].shape[1] * 8
+            qmm += n * k // 2 + 2 * n * (k // G) * 2 + T * k * 2 + T * n * 2
+        N = self.offset + T
+        kv = len(self.attn_layers) * (2 * cfg.kv_heads * N * cfg.head_dim * 2 + 2 * cfg.q_heads * T * cfg.head_dim * 2)
+        st = len(self.gdn_layers) * (2 * cfg.gdn_v_heads * cfg.gdn_dv * cfg.gdn_dk * 4
+                                     + T * (cfg.gdn_v_heads * cfg.gdn_dv * (4 + 2 + 2) + 2 * cfg.gdn_k_heads * cfg.gdn_dk * 2))
+        return {"qmm": qmm, "kv": kv, "gdn": st, "total": qmm + kv + st}
 
     # ---- acceptance and rollback (runtime.py:101-108, 878-907; recurrent_rollback_cache.py:148-171) -------
     @staticmethod

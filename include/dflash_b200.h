@@ -177,9 +177,9 @@ DFLASH_API int dflash_attn_prep(const void* proj, long long ld, int k_off, int v
                                 const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
                                 int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
                                 int dtype, void* stream);
-/* out[t, hq*D+d] = o[hq,t,d] * sigmoid(gate[t,hq,d])  (runtime.py:611-612). */
-DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, int T_rows, int Hq, int D,
-                                int dtype, void* stream);
+/* out[t*out_ld + hq*D+d] = o[hq,t,d] * sigmoid(gate[t,hq,d])  (runtime.py:611-612); out_ld >= Hq*D. */
+DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,
+                                int Hq, int D, int dtype, void* stream);
 
 #ifdef __cplusplus
 }
