@@ -63,3 +63,103 @@ def shard_ranges(n: int, world: int):
         out.append((s, e))
         s = e
     return out
+
+
+def _rows(Wq, idx):
+    """Column-parallel slice of a quantised linear: output rows ``idx``."""
+    return {"w": Wq["w"][idx].contiguous(), "s": Wq["s"][idx].contiguous(), "b": Wq["b"][idx].contiguous()}
+
+
+def _cols(Wq, k0, k1, group_size, pad_to=None):
+    """Row-parallel slice of a quantised linear: input columns [k0, k1) (multiples of the group size), optionally
+    zero-padded on the right to ``pad_to`` columns (zero codes, zero scale and bias)."""
+    assert k0 % group_size == 0 and k1 % group_size == 0
+    w = Wq["w"][:, k0 // 8:k1 // 8]
+    s = Wq["s"][:, k0 // group_size:k1 // group_size]
+    b = Wq["b"][:, k0 // group_size:k1 // group_size]
+    if pad_to is not None and pad_to > k1 - k0:
+        extra = pad_to - (k1 - k0)
+        w = torch.cat([w, torch.zeros(w.shape[0], extra // 8, dtype=w.dtype, device=w.device)], dim=1)
+        s = torch.cat([s, torch.zeros(s.shape[0], extra // group_size, dtype=s.dtype, device=s.device)], dim=1)
+        b = torch.cat([b, torch.zeros(b.shape[0], extra // group_size, dtype=b.dtype, device=b.device)], dim=1)
+    return {"w": w.contiguous(), "s": s.contiguous(), "b": b.contiguous()}
+
+
+def _arange(a, b, device):
+    return torch.arange(a, b, device=device)
+
+
+def shard_weights(cfg, W, rank: int, world: int):
+    """Cuts rank ``rank``'s tensor-parallel shard out of a full set of weights (the dict ``init_weights`` makes).
+    Returns ``(local_cfg, local_weights)``.  Requires head counts divisible by ``world`` and an MLP intermediate
+    whose per-rank share is a multiple of 8 quantisation groups."""
+    lc = shard_config(cfg, world)
+    if world == 1:
+        return lc, W
+    G, dev = cfg.group_size, W["norm"].device
+    if cfg.intermediate % world != 0 or (cfg.intermediate // world) % (8 * G) != 0:
+        raise ValueError("shard_weights needs intermediate/world to be a multiple of 8 groups")
+    I, Il = cfg.intermediate, cfg.intermediate // world
+    lc.intermediate = Il
+    D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
+    hq0, hq1 = rank * lc.q_heads, (rank + 1) * lc.q_heads
+    kv0 = (rank * Hkv) // world if Hkv >= world else hq0 // (Hq // Hkv)
+    kv1 = kv0 + lc.kv_heads
+    Hk, Hv, Dk, Dv = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv
+    gk0, gk1 = rank * lc.gdn_k_heads, (rank + 1) * lc.gdn_k_heads
+    gv0, gv1 = rank * lc.gdn_v_heads, (rank + 1) * lc.gdn_v_heads
+    layers = []
+    for i, L in enumerate(W["layers"]):
+        gu_idx = torch.cat([_arange(rank * Il, (rank + 1) * Il, dev), _arange(I + rank * Il, I + (rank + 1) * Il, dev)])
+        o = {"in_norm": L["in_norm"], "post_norm": L["post_norm"], "gate_up": _rows(L["gate_up"], gu_idx),
+             "down": _cols(L["down"], rank * Il, (rank + 1) * Il, G)}
+        if cfg.is_attention(i):
+            idx = torch.cat([_arange(hq0 * 2 * D, hq1 * 2 * D, dev),
+                             _arange(2 * Hq * D + kv0 * D, 2 * Hq * D + kv1 * D, dev),
+                             _arange(2 * Hq * D + Hkv * D + kv0 * D, 2 * Hq * D + Hkv * D + kv1 * D, dev)])
+            ko = lc.q_heads * D
+            o.update(proj=_rows(L["proj"], idx), q_norm=L["q_norm"], k_norm=L["k_norm"],
+                     o_proj=_cols(L["o_proj"], hq0 * D, hq1 * D, G, pad_to=_round_up(ko, 8 * G)))
+        else:
+            kd = Hk * Dk
+            cd = cfg.conv_dim
+            zo = cd
+            bo = zo + Hv * Dv
+            ao = bo + Hv
+            ch = torch.cat([_arange(gk0 * Dk, gk1 * Dk, dev), _arange(kd + gk0 * Dk, kd + gk1 * Dk, dev),
+                            _arange(2 * kd + gv0 * Dv, 2 * kd + gv1 * Dv, dev)])
+            idx = torch.cat([ch, _arange(zo + gv0 * Dv, zo + gv1 * Dv, dev), _arange(bo + gv0, bo + gv1, dev),
+                             _arange(ao + gv0, ao + gv1, dev)])
+            o.update(proj=_rows(L["proj"], idx), conv_w=L["conv_w"][ch].contiguous(), A_log=L["A_log"][gv0:gv1].contiguous(),
+                     dt_bias=L["dt_bias"][gv0:gv1].contiguous(), g_norm=L["g_norm"],
+                     out_proj=_cols(L["out_proj"], gv0 * Dv, gv1 * Dv, G))
+        layers.append(o)
+    v0 = rank * lc.vocab
+    v1 = min(cfg.vocab, v0 + lc.vocab)
+    lm = _rows(W["lm_head"], _arange(v0, v1, dev))
+    return lc, {"layers": layers, "embed": W["embed"], "norm": W["norm"], "lm_head": lm}
+
+
+def shard_caches(cfg, caches, rank: int, world: int):
+    """The matching slice of the recurrent / KV caches (oracle-style dict of per-layer tensors)."""
+    if world == 1:
+        return caches
+    lc = shard_config(cfg, world)
+    Hk, Hv, Dk, Dv = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv
+    gk0, gk1 = rank * lc.gdn_k_heads, (rank + 1) * lc.gdn_k_heads
+    gv0, gv1 = rank * lc.gdn_v_heads, (rank + 1) * lc.gdn_v_heads
+    kd = Hk * Dk
+    dev = caches["conv"][0].device if caches["conv"] else None
+    kv0 = (rank * cfg.kv_heads) // world if cfg.kv_heads >= world else (rank * lc.q_heads) // (cfg.q_heads // cfg.kv_heads)
+    out = {"conv": [], "state": [], "k": [], "v": []}
+    for c in caches["conv"]:
+        ch = torch.cat([_arange(gk0 * Dk, gk1 * Dk, dev), _arange(kd + gk0 * Dk, kd + gk1 * Dk, dev),
+                        _arange(2 * kd + gv0 * Dv, 2 * kd + gv1 * Dv, dev)])
+        out["conv"].append(c[:, ch].contiguous())
+    for s in caches["state"]:
+        out["state"].append(s[gv0:gv1].contiguous())
+    for k in caches["k"]:
+        out["k"].append(k[kv0:kv0 + lc.kv_heads].contiguous())
+    for v in caches["v"]:
+        out["v"].append(v[kv0:kv0 + lc.kv_heads].contiguous())
+    return out

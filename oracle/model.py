@@ -101,12 +101,17 @@ def attn_layer(cfg, L, x, kcache, vcache, offset):
     o = osd.sdpa_ref(queries.transpose(0, 1)[None], kcache[None, :, :N], vcache[None, :, :N], D ** -0.5, out_dtype=BF)[0]
     o = o.transpose(0, 1).reshape(T, Hq * D)
     gated = (o.float() * torch.sigmoid(gate.float())).to(BF)
+    k_in = L["o_proj"]["w"].shape[1] * 8
+    if k_in > gated.shape[1]:                      # a tensor-parallel shard may carry zero pad columns
+        gated = torch.cat([gated, torch.zeros(T, k_in - gated.shape[1], dtype=BF)], dim=1)
     return _lin(gated, L["o_proj"], cfg.group_size)
 
 
-def verify_step_ref(cfg, W, ids, caches, offset):
+def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None):
     """caches: {"conv": [Lg][keep,cd] bf16, "state": [Lg][Hv,Dv,Dk] f32, "k"/"v": [La][Hk,cap,D] bf16}.
-    Returns (logits bf16 [T,V], greedy tokens, new_caches, tapes) without touching the input GDN caches."""
+    Returns (logits bf16 [T,V], greedy tokens, new_caches, tapes) without touching the input GDN caches.
+    For a tensor-parallel shard, ``reduce(t)`` must return the sum of ``t`` over the ranks (applied to the output of
+    every row-parallel projection) and ``gather_tokens(best_value, local_index)`` the global greedy tokens."""
     h = W["embed"][ids.long()].to(BF)
     ig = ia = 0
     new = {"conv": [], "state": [], "k": caches["k"], "v": caches["v"]}
@@ -122,15 +127,23 @@ def verify_step_ref(cfg, W, ids, caches, offset):
             new["state"].append(ns)
             tapes.append(tp)
             ig += 1
+        if reduce is not None:
+            out = reduce(out)
         h = (h.float() + out.float()).to(BF)
         x = _rms(h, L["post_norm"], cfg.eps)
         gu = _lin(x, L["gate_up"], cfg.group_size)
         I = gu.shape[1] // 2
         act = (torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()).to(BF)
-        h = (h.float() + _lin(act, L["down"], cfg.group_size).float()).to(BF)
+        mlp = _lin(act, L["down"], cfg.group_size)
+        if reduce is not None:
+            mlp = reduce(mlp)
+        h = (h.float() + mlp.float()).to(BF)
     x = _rms(h, W["norm"], cfg.eps)
     logits = _lin(x, W["lm_head"], cfg.group_size)
-    return logits, torch.argmax(logits.float(), dim=-1).to(torch.int32), new, tapes
+    toks = torch.argmax(logits.float(), dim=-1).to(torch.int32)
+    if gather_tokens is not None:
+        toks = gather_tokens(logits.float().gather(1, toks.long()[:, None])[:, 0], toks)
+    return logits, toks, new, tapes
 
 
 def match_acceptance_length(drafted, posterior):
