@@ -360,6 +360,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense step with fewer layers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -385,7 +386,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    wl = WORKLOADS[args.workload](rank, world, device)
+    wl = (WORKLOADS[args.workload](rank, world, device, layers=args.layers) if args.layers and args.workload == "dense_step_cfg4"
+          else WORKLOADS[args.workload](rank, world, device))
 
     # ---- device-resident loop: one CUDA graph = one step ----
     def time_graph(fn, steps, warmup, sample=False):
@@ -455,7 +457,11 @@ def main():
             line["cpu_baseline"] = wl.cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # CUDA graphs that captured NCCL kernels are still alive here; tearing the process group down under them can
+        # block.  All ranks have finished their work: synchronise, then leave without the teardown.
+        sys.stdout.flush()
+        barrier()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -62,6 +62,48 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* h_in, const T
   }
 }
 
+// Vectorised form for H % 8 == 0: one 16-byte load per thread and operand, values stay in registers.
+template <typename T>
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(const uint4* h_in, const uint4* __restrict__ delta,
+                                                               const uint4* __restrict__ w, uint4* h_out,
+                                                               uint4* __restrict__ x, int H8, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = (size_t)blockIdx.x * H8;
+  constexpr int kMaxV = 4;  // vectors per thread (H <= 8 * 4 * blockDim)
+  float v[kMaxV][8];
+  float ss = 0.f;
+  int nv = 0;
+  for (int i = threadIdx.x; i < H8 && nv < kMaxV; i += blockDim.x, ++nv) {
+    uint4 a = h_in[row + i];
+    const T* ap = (const T*)&a;
+    if (delta != nullptr) {
+      const uint4 d = delta[row + i];
+      const T* dp = (const T*)&d;
+      T o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j] = fromf<T>(tof<T>(ap[j]) + tof<T>(dp[j])); v[nv][j] = tof<T>(o[j]); }
+      if (h_out != nullptr) h_out[row + i] = *(const uint4*)o;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[nv][j] = tof<T>(ap[j]);
+      if (h_out != nullptr && h_out != h_in) h_out[row + i] = a;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[nv][j] * v[nv][j];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)(H8 * 8) + eps);
+  int k = 0;
+  for (int i = threadIdx.x; i < H8 && k < kMaxV; i += blockDim.x, ++k) {
+    const uint4 ww = w[i];
+    const T* wp = (const T*)&ww;
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = fromf<T>(v[k][j] * inv * tof<T>(wp[j]));
+    x[row + i] = *(const uint4*)o;
+  }
+}
+
 // y[t, i] = silu(gu[t, i]) * gu[t, I + i]   (SwiGLU on a fused gate|up projection)
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T* __restrict__ y, int I, int rows) {
@@ -92,9 +134,28 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
   const T* row = logits + (size_t)blockIdx.x * V;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  // 16-byte loads over the aligned middle of the row, scalar head and tail
+  const int head = (int)((((16 - ((uintptr_t)row & 15)) & 15)) / sizeof(T));
+  const int h0 = head < V ? head : V;
+  const int nvec = (V - h0) / 8;
+  for (int i = threadIdx.x; i < h0; i += blockDim.x) {
     const float v = tof<T>(row[i]);
-    if (v > best) { best = v; bi = i; }
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  const uint4* rv = (const uint4*)(row + h0);
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 a = rv[i];
+    const T* ap = (const T*)&a;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = tof<T>(ap[j]);
+      const int idx = h0 + 8 * i + j;
+      if (v > best || (v == best && idx < bi)) { best = v; bi = idx; }
+    }
+  }
+  for (int i = h0 + 8 * nvec + threadIdx.x; i < V; i += blockDim.x) {
+    const float v = tof<T>(row[i]);
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -284,6 +345,13 @@ extern "C" int dflash_add_rmsnorm(const void* h_in, const void* delta, const voi
                                   int H, float eps, int dtype, void* stream) {
   if (!h_in || !w || !x || T_rows < 1 || H < 1) return fail(DFLASH_ERR_BAD_ARG, "add_rmsnorm: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (H % 8 == 0 && H <= 8 * 4 * 1024 && al(h_in) && al(delta) && al(w) && al(h_out) && al(x)) {
+    int threads = (H / 8 + 31) / 32 * 32;
+    if (threads > 1024) threads = 1024;
+    DFLASH_DISPATCH(dtype, (add_rmsnorm_vec_kernel<T><<<T_rows, threads, 0, st>>>(
+                               (const uint4*)h_in, (const uint4*)delta, (const uint4*)w, (uint4*)h_out, (uint4*)x, H / 8, eps)));
+  }
   DFLASH_DISPATCH(dtype, (add_rmsnorm_kernel<T><<<T_rows, 256, 0, st>>>((const T*)h_in, (const T*)delta, (const T*)w,
                                                                           (T*)h_out, (T*)x, H, eps)));
 }
