@@ -26,6 +26,13 @@ tensormap_encode_fn get_tensormap_encoder();
 
 int sm_count(int device);
 
+// tcgen05 implementation of the bf16 / group-64 verify matmul (qmm_tc.cu)
+namespace tc {
+size_t workspace_bytes(int M, int K, int N, int device, int max_blocks);
+int launch(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K, int N,
+           void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks);
+}  // namespace tc
+
 #ifdef __CUDACC__
 // ---- device helpers -----------------------------------------------------------------------
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait gives up (a fraction of a second)

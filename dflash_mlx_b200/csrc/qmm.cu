@@ -24,6 +24,7 @@
 //     as an fp32 piece to the workspace and the LAST contributor (atomic ticket) sums all pieces in a
 //     fixed order - deterministic, no inter-CTA waiting.
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -471,6 +472,8 @@ __global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ 
 
 // ------------------------------------------------------------------------------------------
 int g_max_blocks = 0;
+int g_impl = 0;  // 0 = tcgen05 kernel where it applies, 1 = mma.sync kernel only
+thread_local int g_last_impl = 0;  // 1 = mma.sync streaming kernel, 2 = tcgen05 kernel, 3 = general kernel
 
 bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
   const int BK = 8 * G;
@@ -603,18 +606,25 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
                int N, int G, void* ws, size_t ws_bytes, cudaStream_t st) {
   int device = 0;
   cudaGetDevice(&device);
+  if (g_impl == 0 && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
+      ((uintptr_t)ws & 255) == 0) {
+    const int rc = tc::launch(x, wq, sc, bi, bias, y, M, K, N, ws, ws_bytes, st, device, g_max_blocks);
+    if (rc <= 0) { g_last_impl = 2; return rc; }
+  }
   QmmPlan plan;
   if (fast_path_ok(x, wq, sc, bi, K, G) && make_plan(M, K, N, G, device, &plan)) {
     const size_t need = plan_workspace(plan);
     if (ws == nullptr || ws_bytes < need)
       return fail(DFLASH_ERR_WORKSPACE, "verify_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
     if (((uintptr_t)ws & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+    g_last_impl = 1;
     switch (G) {
       case 32: return launch_stream<T, 32>(x, wq, sc, bi, bias, y, plan, ws, st, device);
       case 64: return launch_stream<T, 64>(x, wq, sc, bi, bias, y, plan, ws, st, device);
       default: return launch_stream<T, 128>(x, wq, sc, bi, bias, y, plan, ws, st, device);
     }
   }
+  g_last_impl = 3;
   qmm_general_kernel<T><<<(N + 7) / 8, 256, 0, st>>>((const T*)x, (const uint32_t*)wq, (const T*)sc, (const T*)bi,
                                                      (const T*)bias, (T*)y, M, K, N, G);
   cudaError_t e = cudaGetLastError();
@@ -636,8 +646,16 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
   cudaGetDevice(&device);
   QmmPlan plan;
   if (!make_plan(M, K, N, group_size, device, &plan)) return 256;
-  return plan_workspace(plan);
+  size_t need = plan_workspace(plan);
+  if (group_size == 64) {
+    const size_t t = tc::workspace_bytes(M, K, N, device, g_max_blocks);
+    if (t > need) need = t;
+  }
+  return need;
 }
+
+extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = impl == 1 ? 1 : 0; }
+extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
 
 extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,
                                  const void* bias, void* y, int M, int K, int N, int group_size, int dtype,

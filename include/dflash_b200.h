@@ -65,6 +65,11 @@ DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* sca
                       size_t workspace_bytes, void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
+/* Kernel choice for bf16 / group-64 shapes: 0 (default) = tcgen05 kernel (dequantised operand in tensor memory),
+ * 1 = the mma.sync kernel only.  Other dtypes / group sizes always use the mma.sync kernel. */
+DFLASH_API void dflash_verify_qmm_set_impl(int impl);
+/* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
+DFLASH_API int dflash_verify_qmm_last_impl(void);
 /* Introspection for host-side tests (needs no GPU): writes the streaming kernel's work partition for a
  * shape as ints {row_tiles, slabs, max_pieces, blocks, slab_chunk0[slabs+1], slab_block0[slabs+1]} and
  * returns how many ints were written (<0 on error). */

@@ -103,6 +103,27 @@ def test_block_count_does_not_change_the_answer(vq, blocks):
     assert lib.dflash_device_error(0) == 0
 
 
+@pytest.mark.parametrize("impl,want", [(0, 2), (1, 1)])
+def test_both_kernels_on_config1(vq, impl, want):
+    """bf16 / group 64: the tcgen05 kernel by default, the mma.sync kernel on request; both within tolerance and
+    within fp32-rounding of each other."""
+    from dflash_mlx_b200 import _lib
+    lib = _lib.lib()
+    lib.dflash_verify_qmm_set_impl(impl)
+    try:
+        err, y = _run(vq, 16, 4096, 12288)
+        assert lib.dflash_verify_qmm_last_impl() == want
+        assert err <= REL_TOL, err
+        err2, y2 = _run(vq, 16, 4096, 12288)
+        assert torch.equal(y, y2)
+        for K, N, M in [(5120, 1024, 16), (17408, 5120, 16), (2048, 200, 5), (512, 128, 16), (6144, 5120, 16)]:
+            e, _ = _run(vq, M, K, N, x_std=8.0 / K ** 0.5, w_std=0.05)
+            assert e <= REL_TOL, (K, N, M, e)
+    finally:
+        lib.dflash_verify_qmm_set_impl(0)
+    assert lib.dflash_device_error(0) == 0
+
+
 def test_bad_arguments_raise(vq):
     x, wq, s, b = oq.make_qmm_case(16, 512, 64, seed=1)
     with pytest.raises(ValueError):
