@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ 
 
 // ------------------------------------------------------------------------------------------
 int g_max_blocks = 0;
-int g_impl = 0;  // 0 = tcgen05 kernel where it applies, 1 = mma.sync kernel only
+int g_impl = 0;  // 0/1 = mma.sync streaming kernel (measured faster today), 2 = tcgen05 kernel where it applies
 thread_local int g_last_impl = 0;  // 1 = mma.sync streaming kernel, 2 = tcgen05 kernel, 3 = general kernel
 
 bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
@@ -606,7 +606,7 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
                int N, int G, void* ws, size_t ws_bytes, cudaStream_t st) {
   int device = 0;
   cudaGetDevice(&device);
-  if (g_impl == 0 && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
+  if (g_impl == 2 && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
       ((uintptr_t)ws & 255) == 0) {
     const int rc = tc::launch(x, wq, sc, bi, bias, y, M, K, N, ws, ws_bytes, st, device, g_max_blocks);
     if (rc <= 0) { g_last_impl = 2; return rc; }
@@ -654,7 +654,7 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
   return need;
 }
 
-extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = impl == 1 ? 1 : 0; }
+extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }
 extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
 
 extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,

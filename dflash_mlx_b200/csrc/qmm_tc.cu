@@ -13,9 +13,11 @@
 // Structure of a CTA (1 per SM, persistent over a span of work units):
 //   warps 0-15  : 4 sets x 4 warps.  Warp w may touch TMEM lanes 32*(w%4)..+31, so a set covers the 128 rows;
 //                 set j handles quantisation groups 2j and 2j+1 of every stage.
-//   warp 16     : TMA producer (weights: 128B-swizzled boxes; scales, biases; activation slab as a 3-D map that
-//                 lands directly in the K-major core-matrix layout the MMA wants).
-//   warp 17     : TMEM allocation and MMA issue.
+//   warp 16     : TMEM allocation and TMA producer (weights: 128B-swizzled boxes; scales, biases; activation slab
+//                 as a 3-D map that lands directly in the K-major core-matrix layout the MMA wants).
+//   MMA issue   : no dedicated warp.  When a set has finished writing a group's operand, the LAST of its four warps
+//                 to get there (a shared-memory ticket) issues that group's four MMAs and the commit, so nothing
+//                 waits for a polling thread.
 // Work unit = 128 rows x 8 groups (one 36 KB stage); K slabs, stream-K spans, fp32 partial tiles, batched
 // tickets and the deterministic last-arriver reduction are those of qmm.cu.
 #include <mutex>
@@ -32,7 +34,7 @@ constexpr int kBK = 8 * kG;              // k per stage
 constexpr int kSets = 4;
 constexpr int kDequantWarps = 16;
 constexpr int kDequant = kDequantWarps * 32;  // 512
-constexpr int kThreads = kDequant + 64;
+constexpr int kThreads = kDequant + 32;
 constexpr int kStages = 3;
 constexpr int kWBytes = kRows * (kBK / 2);    // 32 KB
 constexpr int kSBBytes = kRows * 16;          // 2 KB
@@ -44,9 +46,9 @@ constexpr int kRedBytes = kSets * kRows * 16 * 4;
 constexpr int kMaxSlabs = 64;
 constexpr int kMaxPend = 32;
 constexpr int kMaxRowTiles = 16384;
-constexpr int kNumBars = 2 * kStages + 1 + 4 * kSets;  // full, empty, x, a_full[set][2], mma_done[set][2]
+constexpr int kNumBars = 2 * kStages + 1 + 2 * kSets;  // full, empty, x, mma_done[set][2]
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kXsBytes + kRedBytes + 8 * kNumBars +
-                              3 * kMaxPend * 4 + 64;
+                              3 * kMaxPend * 4 + 2 * kSets * 4 + 64;
 constexpr uint32_t kTmemCols = 512;
 // TMEM columns: set j owns [96 j, 96 j + 96): A buffers at +0 and +32 (32 columns = 64 k), D buffers at +64, +80.
 constexpr uint32_t kSetCols = 96;
@@ -111,17 +113,22 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&d)[16]) {
-  uint32_t r[16];
+// Asynchronous TMEM load of 16 columns; the registers may only be read after tc_ld16_wait on the same array.
+__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
-  tc_wait_ld();
-#pragma unroll
-  for (int i = 0; i < 16; ++i) d[i] = __uint_as_float(r[i]);
+}
+// The in/out operands tie every later use of the registers to this wait (the compiler cannot hoist them above it).
+__device__ __forceinline__ void tc_ld16_wait(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
 }
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored as 128 contiguous
 // bytes; lbo = byte distance between core matrices along K, sbo = along the row (N) direction.
@@ -164,7 +171,7 @@ __device__ __noinline__ void finalize_tile(const Plan& plan, const float4* piece
 
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-              const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmX,
+              const __grid_constant__ CUtensorMap tmB, const __nv_bfloat16* __restrict__ x,
               const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, float4* __restrict__ pieces,
               unsigned* __restrict__ counters, const __grid_constant__ Plan plan, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
@@ -175,10 +182,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   float4* red = (float4*)((uint8_t*)xs + kXsBytes);
   uint64_t* bars = (uint64_t*)((uint8_t*)red + kRedBytes);
   volatile int* pend = (volatile int*)(bars + kNumBars);
-  uint32_t* tmem_holder = (uint32_t*)(pend + 3 * kMaxPend);
+  int* tickets = (int*)(pend + 3 * kMaxPend);  // [set][buf]: warps of the set that have written the operand
+  uint32_t* tmem_holder = (uint32_t*)(tickets + 2 * kSets);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_full = bar0, bar_empty = bar0 + 8 * kStages, bar_x = bar0 + 16 * kStages;
-  const uint32_t bar_afull = bar_x + 8, bar_done = bar_afull + 8 * 2 * kSets;  // [set][buf]
+  const uint32_t bar_done = bar_x + 8;  // [set][buf]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -197,12 +205,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     }
     mbar_init(bar_x, 1);
     for (int i = 0; i < 2 * kSets; ++i) {
-      mbar_init(bar_afull + 8 * i, 4);  // one arrival per warp of the set
-      mbar_init(bar_done + 8 * i, 1);   // tcgen05.commit
+      mbar_init(bar_done + 8 * i, 1);  // tcgen05.commit
+      tickets[i] = 0;
     }
     mbar_fence_init();
   }
-  if (warp == kDequantWarps + 1) tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+  if (warp == kDequantWarps) tmem_alloc(smem_u32(tmem_holder), kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -212,12 +220,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // ======================= TMA producer =======================
     if (lane == 0) {
       const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-      mbar_arrive_expect_tx(bar_x, kXBytes);
-      asm volatile(
-          "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
-          " [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(smem_u32(xbuf)),
-          "l"(&tmX), "r"(0), "r"(0), "r"(sg.c0 * (kBK / 8)), "r"(bar_x), "l"(pol_keep)
-          : "memory");
       int stage = 0, nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
       uint32_t par = 1;
       for (unsigned u = u_begin; u < u_end; ++u) {
@@ -232,44 +234,43 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (++kc == sg.cs) { kc = 0; ++nt; }
       }
     }
-  } else if (warp == kDequantWarps + 1) {
-    // ======================= MMA issuer =======================
-    if (lane == 0) {
-      const uint32_t xaddr = smem_u32(xbuf);
-      unsigned n = 0;
-      int kc = (int)(u_begin % sg.cs);
-      bool dead = false;
-      for (unsigned u = u_begin; u < u_end && !dead; ++u) {
-        for (int g2 = 0; g2 < 2 && !dead; ++g2, ++n) {
-          const uint32_t buf = n & 1, par = (n >> 1) & 1;
-          for (int set = 0; set < kSets; ++set) {
-            if (!mbar_wait(bar_afull + 8 * (set * 2 + buf), par)) { atomicExch(err, 12); dead = true; break; }
-            tc_fence_after();
-            const int gs = kc * 8 + 2 * set + g2;  // group index inside the slab
-            const uint32_t d = tmem + set * kSetCols + 64 + 16 * buf, a = tmem + set * kSetCols + 32 * buf;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              tc_mma(d, a + 8 * i, smem_desc(xaddr + (uint32_t)(gs * 8 + 2 * i) * 256u, 256u, 128u), kIdesc, i > 0);
-            tc_commit(bar_done + 8 * (set * 2 + buf));
-          }
-        }
-        if (++kc == sg.cs) kc = 0;
-      }
-    }
   } else {
     // ======================= dequant / epilogue warps =======================
     const int set = warp >> 2, r = ((warp & 3) << 5) | lane;  // TMEM lane = weight row inside the tile
     const uint32_t lane_base = (uint32_t)((warp & 3) << 5) << 16;
+    const uint32_t xaddr = smem_u32(xbuf);
     bool aborted = false;
-    if (!mbar_wait(bar_x, 0)) { aborted = true; atomicExch(err, 13); }
+    // Activation slab: read straight from global memory (it is L2 resident), re-tiled to the K-major core-matrix
+    // layout [k/8][16 tokens][8] with the k order inside every 8-block permuted to (0,4,1,5,2,6,3,7) - the order in
+    // which LOP3 yields nibble pairs.  A warp covers 16 tokens x 2 k-blocks: full 32-byte sectors from global
+    // memory, consecutive 16-byte chunks in shared memory.
+    {
+      const int kb_lim = (plan.K - sg.c0 * kBK) / 8;  // k-blocks that exist from the slab start
+      uint4 v[kXBytes / 16 / kDequant];
+#pragma unroll
+      for (int j = 0; j < kXBytes / 16 / kDequant; ++j) {
+        const int ci = tid + j * kDequant, tok = ci & 15, kb = ci >> 4;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (tok < M && kb < kb_lim) v[j] = *(const uint4*)(x + (size_t)tok * plan.K + (size_t)sg.c0 * kBK + kb * 8);
+      }
+#pragma unroll
+      for (int j = 0; j < kXBytes / 16 / kDequant; ++j) {
+        uint4 o;
+        o.x = prmt(v[j].x, v[j].z, 0x5410); o.y = prmt(v[j].x, v[j].z, 0x7632);
+        o.z = prmt(v[j].y, v[j].w, 0x5410); o.w = prmt(v[j].y, v[j].w, 0x7632);
+        ((uint4*)xbuf)[tid + j * kDequant] = o;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    named_bar_sync(1, kDequant);
     // group sums of x: thread (g, tok) adds the 64 activations of group g for token tok
     {
       const int g = tid >> 4, tok = tid & 15;
       float acc = 0.f;
 #pragma unroll
       for (int kb = 0; kb < 8; ++kb) {
-        const uint4 v = *(const uint4*)(xbuf + ((size_t)(g * 8 + kb) * 16 + tok) * 16);
-        const __nv_bfloat162* p = (const __nv_bfloat162*)&v;
+        const uint4 vv = *(const uint4*)(xbuf + ((size_t)(g * 8 + kb) * 16 + tok) * 16);
+        const __nv_bfloat162* p = (const __nv_bfloat162*)&vv;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = __bfloat1622float2(p[j]);
@@ -278,16 +279,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
       xs[g * 16 + tok] = acc;
     }
-    named_bar_sync(1, kDequant);
-    // k order inside every 8-block becomes (0,4,1,5,2,6,3,7): the order in which LOP3 yields nibble pairs
-    for (int ci = tid; ci < kXBytes / 16; ci += kDequant) {
-      uint4 v = ((const uint4*)xbuf)[ci];
-      uint4 o;
-      o.x = prmt(v.x, v.z, 0x5410); o.y = prmt(v.x, v.z, 0x7632);
-      o.z = prmt(v.y, v.w, 0x5410); o.w = prmt(v.y, v.w, 0x7632);
-      ((uint4*)xbuf)[ci] = o;
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     named_bar_sync(1, kDequant);
 
     float out[16];
@@ -300,21 +291,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     bool primed = false;       // two groups are in flight
     int npend = 0;
 
-    auto collect = [&](const int buf) {  // folds group `ncol` (which used buffer `buf`) into `out`
+    // collect = wait for the MMAs of group `ncol` (buffer `buf`), start the TMEM load of its accumulator ...
+    auto collect_begin = [&](const int buf, uint32_t (&dr)[16]) {
       const uint32_t par = (ncol >> 1) & 1;
       if (!aborted && !mbar_wait(bar_done + 8 * (set * 2 + buf), par)) { aborted = true; atomicExch(err, 14); }
       tc_fence_after();
-      float d[16];
-      tc_ld16(tmem + lane_base + set * kSetCols + 64 + 16 * buf, d);
+      tc_ld16_issue(tmem + lane_base + set * kSetCols + 64 + 16 * buf, dr);
+    };
+    // ... and fold it into `out` with that group's scale and bias.
+    auto collect_end = [&](const int buf, uint32_t (&dr)[16]) {
+      tc_ld16_wait(dr);
       const float sc = ps[buf], bq = pb[buf];
       const float4* xr = (const float4*)(xs + pg[buf] * 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float4 xv = xr[i];
-        out[4 * i + 0] = fmaf(sc, d[4 * i + 0], fmaf(bq, xv.x, out[4 * i + 0]));
-        out[4 * i + 1] = fmaf(sc, d[4 * i + 1], fmaf(bq, xv.y, out[4 * i + 1]));
-        out[4 * i + 2] = fmaf(sc, d[4 * i + 2], fmaf(bq, xv.z, out[4 * i + 2]));
-        out[4 * i + 3] = fmaf(sc, d[4 * i + 3], fmaf(bq, xv.w, out[4 * i + 3]));
+        out[4 * i + 0] = fmaf(sc, __uint_as_float(dr[4 * i + 0]), fmaf(bq, xv.x, out[4 * i + 0]));
+        out[4 * i + 1] = fmaf(sc, __uint_as_float(dr[4 * i + 1]), fmaf(bq, xv.y, out[4 * i + 1]));
+        out[4 * i + 2] = fmaf(sc, __uint_as_float(dr[4 * i + 2]), fmaf(bq, xv.z, out[4 * i + 2]));
+        out[4 * i + 3] = fmaf(sc, __uint_as_float(dr[4 * i + 3]), fmaf(bq, xv.w, out[4 * i + 3]));
       }
       ++ncol;
     };
@@ -349,12 +344,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
       for (int g2 = 0; g2 < 2; ++g2, ++n) {
         const int buf = g2;
-        if (primed) collect(g2);  // frees A[buf] and D[buf]
         const int gi = 2 * set + g2;
         const uint8_t* wrow = st + (gi >> 2) * (kRows * 128) + r * 128;
         const int c0 = 2 * (gi & 3);
+        // long-latency operations are issued back to back and their waits pushed behind independent work:
+        // weights (shared memory) -> previous accumulator (TMEM load) -> dequantise -> TMEM store -> fold -> publish
         const uint4 w0 = *(const uint4*)(wrow + (((c0) ^ (r & 7)) << 4));
         const uint4 w1 = *(const uint4*)(wrow + (((c0 + 1) ^ (r & 7)) << 4));
+        uint32_t dr[16];
+        if (primed) collect_begin(buf, dr);  // also means A[buf] and D[buf] are free again
         const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         const uint32_t a_addr = tmem + lane_base + set * kSetCols + 32 * buf;
 #pragma unroll
@@ -367,10 +365,24 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               regs[4 * w + p] = lop3_and_or(words[4 * half + w] >> (4 * p), 0x000F000Fu, 0x43004300u);
           tc_st16(a_addr + 16 * half, regs);
         }
+        if (primed) collect_end(buf, dr);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_afull + 8 * (set * 2 + buf));
+        if (lane == 0) {
+          __threadfence_block();
+          const int old = atomicAdd(&tickets[set * 2 + buf], 1);
+          if ((old & 3) == 3) {  // the set's operand for this group is complete: issue its MMAs
+            __threadfence_block();
+            tc_fence_after();
+            const int gs = kc * 8 + gi;  // group index inside the slab
+            const uint32_t d = tmem + set * kSetCols + 64 + 16 * buf, a = tmem + set * kSetCols + 32 * buf;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              tc_mma(d, a + 8 * i, smem_desc(xaddr + (uint32_t)(gs * 8 + 2 * i) * 256u, 256u, 128u), kIdesc, i > 0);
+            tc_commit(bar_done + 8 * (set * 2 + buf));
+          }
+        }
         const float sc = __uint_as_float((g2 ? (s2 >> 16) : (s2 & 0xFFFFu)) << 16);
         const float bi = __uint_as_float((g2 ? (b2 >> 16) : (b2 & 0xFFFFu)) << 16);
         ps[buf] = sc;
@@ -384,8 +396,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
       const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
       if (seg_end) {
-        collect(0);
-        collect(1);
+        {
+          uint32_t d0[16], d1[16];
+          collect_begin(0, d0);
+          ++ncol;              // the parity of buffer 1's barrier belongs to the next group
+          collect_begin(1, d1);
+          --ncol;
+          collect_end(0, d0);
+          collect_end(1, d1);
+        }
         primed = false;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -425,7 +444,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   // every warp ends here: the accumulator memory goes back before the CTA exits
   tc_fence_before();
   __syncthreads();
-  if (warp == kDequantWarps + 1) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kDequantWarps) tmem_dealloc(tmem, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -540,10 +559,8 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   if (K % kBK != 0) return 1;
   Plan plan;
   if (!make_plan(M, K, N, device, max_blocks, &plan)) return 1;
-  CUtensorMap tw, ts, tb, tx;
-  if (!get_map(wq, N, K / 2, 0, &tw) || !get_map(sc, N, K / kG, 1, &ts) || !get_map(bi, N, K / kG, 1, &tb) ||
-      !get_map(x, M, K, 2, &tx))
-    return 1;
+  CUtensorMap tw, ts, tb;
+  if (!get_map(wq, N, K / 2, 0, &tw) || !get_map(sc, N, K / kG, 1, &ts) || !get_map(bi, N, K / kG, 1, &tb)) return 1;
   const size_t need = plan_workspace(plan);
   if (ws == nullptr || ws_bytes < need)
     return fail(DFLASH_ERR_WORKSPACE, "verify_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
@@ -555,7 +572,7 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   }
   unsigned* counters = (unsigned*)ws;
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
-  qmm_tc_kernel<<<plan.slab_cta0[plan.S], kThreads, kSmemBytes, st>>>(tw, ts, tb, tx, (const __nv_bfloat16*)bias,
+  qmm_tc_kernel<<<plan.slab_cta0[plan.S], kThreads, kSmemBytes, st>>>(tw, ts, tb, (const __nv_bfloat16*)x, (const __nv_bfloat16*)bias,
                                                                       (__nv_bfloat16*)y, pieces, counters, plan,
                                                                       device_error_word(device));
   cudaError_t e = cudaGetLastError();

@@ -65,8 +65,9 @@ DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* sca
                       size_t workspace_bytes, void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
-/* Kernel choice for bf16 / group-64 shapes: 0 (default) = tcgen05 kernel (dequantised operand in tensor memory),
- * 1 = the mma.sync kernel only.  Other dtypes / group sizes always use the mma.sync kernel. */
+/* Kernel choice for bf16 / group-64 shapes: 0 (default) or 1 = the mma.sync streaming kernel (the faster one in
+ * today's measurements), 2 = the tcgen05 kernel (dequantised operand in tensor memory, accumulator in TMEM).
+ * Other dtypes / group sizes always use the mma.sync kernel. */
 DFLASH_API void dflash_verify_qmm_set_impl(int impl);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
 DFLASH_API int dflash_verify_qmm_last_impl(void);
