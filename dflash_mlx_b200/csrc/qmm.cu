@@ -129,15 +129,36 @@ template <typename T>
 __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pieces, unsigned* counters,
                                            T* __restrict__ y, const T* __restrict__ bias, int nt, int ctid, int warp,
                                            int rp, int c) {
+  // First the slot list (integer divisions only), then the loads eight at a time so that their latencies overlap,
+  // then the sum in slot order (fixed order: deterministic).
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s2 = 0; s2 < plan.S; ++s2) {
-    const SlabGeom g2 = slab_geom(plan, s2);
+  int s2 = 0, p = 0, np = 0;
+  {
     int f;
-    const int np = tile_pieces(g2, nt, &f);
-    for (int p = 0; p < np; ++p) {
-      const float4 a = ld_cg_f4(&pieces[((size_t)(s2 * plan.maxp + p) * plan.NT + nt) * kConsumers + ctid]);
-      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    np = tile_pieces(slab_geom(plan, 0), nt, &f);
+  }
+  bool more = true;
+  while (more) {
+    const float4* src[8];
+    int n = 0;
+    while (n < 8) {
+      if (p >= np) {
+        if (++s2 >= plan.S) { more = false; break; }
+        int f;
+        np = tile_pieces(slab_geom(plan, s2), nt, &f);
+        p = 0;
+        continue;
+      }
+      src[n++] = &pieces[((size_t)(s2 * plan.maxp + p) * plan.NT + nt) * kConsumers + ctid];
+      ++p;
     }
+    float4 a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < n) a[i] = ld_cg_f4(src[i]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < n) { v.x += a[i].x; v.y += a[i].y; v.z += a[i].z; v.w += a[i].w; }
   }
   if (ctid == 0) counters[nt] = 0;  // ready for the next launch
   store_tile<T>(v, y, bias, nt, warp, rp, c, plan.M, plan.N);
@@ -373,20 +394,14 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               make_float4(out[q >> 1][q & 1][0], out[q >> 1][q & 1][1], out[q >> 1][q & 1][2], out[q >> 1][q & 1][3]);
       }
       named_bar_sync(bar_id, kConsumers);
-      if (wwarp < 4) {
+      if (wwarp < 4) {  // warp w folds warp w+4's tile into its own and puts the sum back in the same slots
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           const float4 a = red[(wwarp * 8 + q) * 32 + lane];
-          out[q >> 1][q & 1][0] += a.x; out[q >> 1][q & 1][1] += a.y;
-          out[q >> 1][q & 1][2] += a.z; out[q >> 1][q & 1][3] += a.w;
-        }
-      }
-      named_bar_sync(bar_id, kConsumers);
-      if (wwarp < 4) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
           red[(wwarp * 8 + q) * 32 + lane] =
-              make_float4(out[q >> 1][q & 1][0], out[q >> 1][q & 1][1], out[q >> 1][q & 1][2], out[q >> 1][q & 1][3]);
+              make_float4(out[q >> 1][q & 1][0] + a.x, out[q >> 1][q & 1][1] + a.y, out[q >> 1][q & 1][2] + a.z,
+                          out[q >> 1][q & 1][3] + a.w);
+        }
       }
 #pragma unroll
       for (int t = 0; t < 4; ++t)
