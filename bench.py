@@ -264,6 +264,162 @@ class DenseStepWorkload:
         return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s)
 
 
+class ReplayWorkload:
+    """Configuration 2 of BASELINE.json, per speculative cycle: tape replay of ALL 48 GatedDeltaNet layers of the dense
+    model (stacked along the batch axis) in one launch; 32 value / 16 key heads, 128x128 fp32 state, 16-step tape.
+    A step walks a pool of independent state sets larger than L2.  Ranks shard the value heads."""
+    name = "gdn_replay_cfg2"
+    metric, unit, higher_is_better, scaling, dtype = "gdn_tape_replay_latency_per_cycle", "us", False, "strong", "f32"
+    LAYERS, T, STEPS = 48, 16, 16
+
+    def __init__(self, rank, world, device):
+        import torch
+        self.torch, self.device, self.world = torch, device, world
+        Hk, Hv, D = 16 // world, 32 // world, 128
+        self.shape = (Hk, Hv, D)
+        L = self.LAYERS
+        per = L * (2 * Hv * D * D * 4 + self.STEPS * (Hv * D * 4 + Hk * D * 2 + Hv * 4))
+        self.per_launch_bytes = per
+        self.pool = max(2, (3 * L2_BYTES) // per + 1)
+        g = torch.Generator(device=device).manual_seed(0xDF1B + rank)
+        rn = lambda *s: torch.randn(*s, generator=g, device=device)  # noqa: E731
+        self.sets = []
+        for _ in range(self.pool):
+            k = rn(L, self.T, Hk, D)
+            k = (k / k.norm(dim=-1, keepdim=True)).bfloat16()
+            self.sets.append(dict(tape=rn(L, self.T, Hv, D), k=k,
+                                  g=torch.exp(-torch.nn.functional.softplus(rn(L, self.T, Hv))),
+                                  state=0.1 * rn(L, Hv, D, D), out=torch.empty(L, Hv, D, D, device=device)))
+        self.steps_host = torch.tensor([self.STEPS], dtype=torch.int32).pin_memory()
+        self.steps_dev = self.steps_host.to(device)
+        self.flag_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        self.launches_per_step = self.pool
+        self.units_per_step = self.pool
+        self.config = {"workload": self.name, "layers": L, "tape_steps": self.T, "replayed_steps": self.STEPS,
+                       "value_heads_per_rank": Hv, "state": "fp32 [48,Hv,128,128]", "pool": self.pool,
+                       "l2": "inputs larger than L2: a step walks %d independent state sets (%.0f MB)" % (self.pool, self.pool * per / 1e6),
+                       "parallelism": f"value heads x{world}"}
+
+    def _one(self, s, steps):
+        from dflash_mlx_b200.kernels import tape_replay_kernel
+        return tape_replay_kernel(s["tape"], s["k"], s["g"], s["state"], steps=steps, out=s["out"])
+
+    def step(self):
+        for s in self.sets:
+            self._one(s, self.steps_dev)
+
+    def e2e_step(self):
+        self._i = (getattr(self, "_i", -1) + 1) % self.pool
+        self.steps_dev.copy_(self.steps_host, non_blocking=True)       # the accepted length arrives from the host
+        out = self._one(self.sets[self._i], self.steps_dev)
+        self.flag_host.copy_(out.view(-1)[:1], non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return 1
+
+    h2d_bytes = property(lambda self: 4)
+    d2h_bytes = property(lambda self: 4)
+
+    def value_from_ms(self, ms):
+        return ms * 1e3 / self.units_per_step
+
+    def e2e_value(self, seconds, calls):
+        return seconds * 1e6 / calls
+
+    def roofline(self, ms_per_step, aux_ms, peak, peak_src):
+        us = ms_per_step * 1e3 / self.launches_per_step
+        ach = self.per_launch_bytes / us / 1e3
+        return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                "peak_source": peak_src, "kernel": "gdn_kernel<RECORD=false>", "algorithmic_bytes_per_launch": self.per_launch_bytes,
+                "us_per_launch": us}
+
+    def cpu_baseline(self, budget_s=10.0):
+        import torch
+        from oracle import gdn as og
+        torch.set_num_threads(os.cpu_count() or 1)
+        c = og.make_gdn_case(seed=1)
+        tape = torch.randn(1, 16, 32, 128)
+        ts = []
+        for _ in range(4):
+            t0 = time.perf_counter()
+            og.tape_replay_ref(tape, c["k"], c["g"], c["state"], steps=self.STEPS)
+            ts.append(time.perf_counter() - t0)
+        return {"value": min(ts[1:]) * self.LAYERS * 1e6, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": "one layer with the torch restatement of _tape_replay_ops (best of 3) x 48 layers; "
+                          "MLX unavailable on this box"}
+
+
+class SdpaWorkload:
+    """Configuration 3 of BASELINE.json: 16 query heads / 2 KV heads of 256, 16 query rows, KV length 8192 (bf16).
+    A step walks a pool of KV caches larger than L2.  Ranks shard the KV heads (with their query heads)."""
+    name = "verify_sdpa_cfg3"
+    metric, unit, higher_is_better, scaling, dtype = "verify_sdpa_latency", "us", False, "strong", "bf16"
+    N = 8192
+
+    def __init__(self, rank, world, device):
+        import torch
+        self.torch, self.device, self.world = torch, device, world
+        Hk = max(1, 2 // world)
+        Hq = 16 // world
+        self.Hq, self.Hk, D = Hq, Hk, 256
+        per = 2 * Hk * self.N * D * 2 + 2 * Hq * 16 * D * 2
+        self.per_launch_bytes = per
+        self.pool = max(2, (3 * L2_BYTES) // per + 1)
+        g = torch.Generator(device=device).manual_seed(0xDF1C + rank)
+        self.kv = [(torch.randn(1, Hk, self.N, D, generator=g, device=device).bfloat16(),
+                    torch.randn(1, Hk, self.N, D, generator=g, device=device).bfloat16()) for _ in range(self.pool)]
+        self.q_host = torch.randn(1, Hq, 16, D).bfloat16().pin_memory()
+        self.q = self.q_host.to(device)
+        self.o_host = torch.empty(1, Hq, 16, D, dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = 2 * self.pool
+        self.units_per_step = self.pool
+        self.config = {"workload": self.name, "q_heads": Hq, "kv_heads": Hk, "head_dim": D, "kv_len": self.N, "pool": self.pool,
+                       "l2": "inputs larger than L2: a step walks %d KV caches (%.0f MB)" % (self.pool, self.pool * per / 1e6),
+                       "parallelism": f"kv heads x{world}"}
+
+    def step(self):
+        from dflash_mlx_b200.kernels import batched_sdpa_2pass_exact
+        for k, v in self.kv:
+            batched_sdpa_2pass_exact(self.q, k, v, 1.0 / 16.0)
+
+    def e2e_step(self):
+        from dflash_mlx_b200.kernels import batched_sdpa_2pass_exact
+        self._i = (getattr(self, "_i", -1) + 1) % self.pool
+        q = self.q_host.to(self.device, non_blocking=True)
+        o = batched_sdpa_2pass_exact(q, *self.kv[self._i], 1.0 / 16.0)
+        self.o_host.copy_(o, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return 1
+
+    h2d_bytes = property(lambda self: self.Hq * 16 * 256 * 2)
+    d2h_bytes = property(lambda self: self.Hq * 16 * 256 * 2)
+
+    def value_from_ms(self, ms):
+        return ms * 1e3 / self.units_per_step
+
+    def e2e_value(self, seconds, calls):
+        return seconds * 1e6 / calls
+
+    def roofline(self, ms_per_step, aux_ms, peak, peak_src):
+        us = ms_per_step * 1e3 / self.units_per_step
+        ach = self.per_launch_bytes / us / 1e3
+        return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                "peak_source": peak_src, "kernel": "sdpa_partials_kernel (+ combine)",
+                "algorithmic_bytes_per_launch": self.per_launch_bytes, "us_per_launch": us}
+
+    def cpu_baseline(self, budget_s=10.0):
+        import torch
+        from oracle import sdpa as osd
+        torch.set_num_threads(os.cpu_count() or 1)
+        q, k, v, sc = osd.make_sdpa_case(self.N, seed=1)
+        ts = []
+        for _ in range(4):
+            t0 = time.perf_counter()
+            osd.sdpa_ref(q, k, v, sc)
+            ts.append(time.perf_counter() - t0)
+        return {"value": min(ts[1:]) * 1e6, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": "dense-softmax torch restatement, best of 3; MLX unavailable on this box"}
+
+
 def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
     """CPU path of one dense verify step on all host cores, from a bounded sample: every distinct linear shape
     is timed with the C restatement of the stock qmm (oracle/qmm_ref.c), the GDN recurrence and the attention
@@ -320,7 +476,8 @@ def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
             "parts_ms": {k2: round(v2 * 1e3, 3) for k2, v2 in parts.items()}}
 
 
-WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload}
+WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload, "gdn_replay_cfg2": ReplayWorkload,
+             "verify_sdpa_cfg3": SdpaWorkload}
 DEFAULT_WORKLOAD = "dense_step_cfg4"
 
 
@@ -338,6 +495,9 @@ def run_reference_arm(args, rank, world):
         w.world, w.n_local = 1, cls.N
         cb = w.cpu_baseline(budget_s=budget)
         config = {"workload": cls.name, "M": cls.M, "K": cls.K, "N": cls.N, "group_size": cls.G}
+    elif cls in (ReplayWorkload, SdpaWorkload):
+        cb = cls.__new__(cls).cpu_baseline(budget_s=budget)
+        config = {"workload": cls.name}
     else:
         from dflash_mlx_b200.verify_step import HybridConfig
         cfg = HybridConfig(max_context=cls.CONTEXT + 64)
