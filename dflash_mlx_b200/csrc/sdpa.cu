@@ -253,40 +253,56 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
   }
 }
 
-// One warp per (head, row): out = sum_s w_s O_s / sum_s w_s l_s with w_s = exp2(m_s - max_s m_s).
+// One CTA per (head, row), one thread per output channel: out = sum_s w_s O_s / sum_s w_s l_s with
+// w_s = exp2(m_s - max_s m_s).  The weights are computed once into shared memory; the channel loop then reads the
+// partials with fully coalesced, independent loads.
 template <typename T, int D>
-__global__ void __launch_bounds__(128) sdpa_combine_kernel(const SdpaArgs a, int rows) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
+__global__ void __launch_bounds__(D) sdpa_combine_kernel(const SdpaArgs a, int rows) {
+  __shared__ float sw[1024];
+  __shared__ float sred[D / 32];
+  __shared__ float sden;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* pm = a.part_m + (size_t)row * a.splits;
   const float* pl = a.part_l + (size_t)row * a.splits;
   float mx = -INFINITY;
-  for (int s = lane; s < a.splits; s += 32) mx = fmaxf(mx, pm[s]);
+  for (int s = tid; s < a.splits; s += D) mx = fmaxf(mx, pm[s]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) sred[warp] = mx;
+  __syncthreads();
+  mx = sred[0];
+#pragma unroll
+  for (int i = 1; i < D / 32; ++i) mx = fmaxf(mx, sred[i]);
   const float ref = (mx == -INFINITY) ? 0.f : mx;
+  __syncthreads();
   float den = 0.f;
-  for (int s = lane; s < a.splits; s += 32) den += exp2f(pm[s] - ref) * pl[s];
+  for (int s = tid; s < a.splits; s += D) {
+    const float w = exp2f(pm[s] - ref);
+    sw[s] = w;
+    den += w * pl[s];
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-  constexpr int VPL = D / 32;  // values per lane
-  float acc[VPL];
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
-  const float* po = a.part_o + (size_t)row * a.splits * D + lane * VPL;
-  for (int s = 0; s < a.splits; ++s) {
-    const float w = exp2f(pm[s] - ref);
-#pragma unroll
-    for (int i = 0; i < VPL; i += 4) {
-      const float4 v = *(const float4*)(po + (size_t)s * D + i);
-      acc[i] = fmaf(w, v.x, acc[i]); acc[i + 1] = fmaf(w, v.y, acc[i + 1]);
-      acc[i + 2] = fmaf(w, v.z, acc[i + 2]); acc[i + 3] = fmaf(w, v.w, acc[i + 3]);
-    }
+  if (lane == 0) sred[warp] = den;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int i = 0; i < D / 32; ++i) t += sred[i];
+    sden = t;
   }
-  const float inv = den == 0.f ? 1.f : 1.f / den;  // a row with no visible key yields zeros (kernels.py:630)
-  T* out = (T*)a.out + (size_t)row * D + lane * VPL;
-#pragma unroll
-  for (int i = 0; i < VPL; i += 2) *(uint32_t*)(out + i) = pack2<T>(acc[i] * inv, acc[i + 1] * inv);
+  __syncthreads();
+  const float* po = a.part_o + (size_t)row * a.splits * D + tid;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  int s = 0;
+  for (; s + 4 <= a.splits; s += 4) {
+    const float v0 = po[(size_t)s * D], v1 = po[(size_t)(s + 1) * D], v2 = po[(size_t)(s + 2) * D], v3 = po[(size_t)(s + 3) * D];
+    acc0 = fmaf(sw[s], v0, acc0); acc1 = fmaf(sw[s + 1], v1, acc1);
+    acc2 = fmaf(sw[s + 2], v2, acc2); acc3 = fmaf(sw[s + 3], v3, acc3);
+  }
+  for (; s < a.splits; ++s) acc0 = fmaf(sw[s], po[(size_t)s * D], acc0);
+  const float den_all = sden;
+  const float inv = den_all == 0.f ? 1.f : 1.f / den_all;  // a row with no visible key yields zeros (kernels.py:630)
+  ((T*)a.out)[(size_t)row * D + tid] = MmaTraits<T>::from_float(((acc0 + acc1) + (acc2 + acc3)) * inv);
 }
 
 int choose_splits(int N, int ctas_per_split_unit, int device, int requested, int* blocks_per_split) {
@@ -294,6 +310,7 @@ int choose_splits(int N, int ctas_per_split_unit, int device, int requested, int
   int splits = requested > 0 ? requested : sm_count(device) / (ctas_per_split_unit > 0 ? ctas_per_split_unit : 1);
   if (splits < 1) splits = 1;
   if (splits > nblk) splits = nblk;
+  if (splits > 1024) splits = 1024;
   const int bps = (nblk + splits - 1) / splits;
   *blocks_per_split = bps;
   return (nblk + bps - 1) / bps;
@@ -328,7 +345,7 @@ int launch(SdpaArgs a, void* ws, size_t ws_bytes, int requested_splits, cudaStre
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa partials launch: %s", cudaGetErrorString(e));
   if (a.splits > 1) {
-    sdpa_combine_kernel<T, D><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(a, (int)rows);
+    sdpa_combine_kernel<T, D><<<(unsigned)rows, D, 0, st>>>(a, (int)rows);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa combine launch: %s", cudaGetErrorString(e));
   }
