@@ -39,6 +39,9 @@ def _declare(lib) -> None:
         "dflash_version": (i32, []),
         "dflash_last_error_string": (c.c_char_p, []),
         "dflash_device_error": (i32, [i32]),
+        "dflash_set_pdl": (None, [i32]),
+        "dflash_get_pdl": (i32, []),
+        "dflash_pdl_plain_next": (None, [i32]),
         "dflash_verify_qmm_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "dflash_verify_qmm": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, sz, vp]),
         "dflash_verify_qmm_set_max_blocks": (None, [i32]),

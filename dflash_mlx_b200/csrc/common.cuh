@@ -26,6 +26,11 @@ tensormap_encode_fn get_tensormap_encoder();
 
 int sm_count(int device);
 
+// Programmatic dependent launch: when on, every kernel of this library is launched with the stream-serialisation
+// attribute, so its blocks may start (prologue, loads of data no earlier kernel writes) while the previous kernel of
+// the stream drains; every kernel executes pdl_wait() before it touches anything an earlier kernel may write or read.
+bool pdl_enabled_for_next_launch();
+
 // tcgen05 implementation of the bf16 / group-64 verify matmul (qmm_tc.cu)
 namespace tc {
 size_t workspace_bytes(int M, int K, int N, int device, int max_blocks);
@@ -34,8 +39,34 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
 }  // namespace tc
 
 #ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_as(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+  return launch_kernel_as(pdl_enabled_for_next_launch(), kernel, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+
 // ---- device helpers -----------------------------------------------------------------------
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait gives up (a fraction of a second)
+
+// Blocks until every kernel this one depends on has completed and its writes are visible (no-op for a plain launch).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the stream start its blocks as soon as every block of this one has got here (or exited).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -75,6 +75,8 @@ template <typename IT, typename ST, int NPT, bool RECORD>
 __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
   constexpr int Dk = NPT * 32;
   constexpr int kStepChunk = (NPT == 8) ? 8 : 16;  // keeps the static shared memory under 48 KB
+  pdl_wait();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y, b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
   const int row0 = blockIdx.x * kRowsPerCta + warp * kRowsPerWarp;
@@ -216,14 +218,15 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
 template <typename IT, typename ST, bool RECORD>
 int launch_npt(const GdnArgs& a, cudaStream_t st) {
   dim3 grid((a.Dv + kRowsPerCta - 1) / kRowsPerCta, a.B * a.Hv);
+  cudaError_t e = cudaSuccess;
   switch (a.Dk / 32) {
-    case 1: gdn_kernel<IT, ST, 1, RECORD><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 2: gdn_kernel<IT, ST, 2, RECORD><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 4: gdn_kernel<IT, ST, 4, RECORD><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 8: gdn_kernel<IT, ST, 8, RECORD><<<grid, kWarps * 32, 0, st>>>(a); break;
+    case 1: e = launch_kernel(gdn_kernel<IT, ST, 1, RECORD>, grid, dim3(kWarps * 32), 0, st, a); break;
+    case 2: e = launch_kernel(gdn_kernel<IT, ST, 2, RECORD>, grid, dim3(kWarps * 32), 0, st, a); break;
+    case 4: e = launch_kernel(gdn_kernel<IT, ST, 4, RECORD>, grid, dim3(kWarps * 32), 0, st, a); break;
+    case 8: e = launch_kernel(gdn_kernel<IT, ST, 8, RECORD>, grid, dim3(kWarps * 32), 0, st, a); break;
     default: return fail(DFLASH_ERR_BAD_SHAPE, "gdn: Dk=%d not in {32,64,128,256}", a.Dk);
   }
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "gdn launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
 }

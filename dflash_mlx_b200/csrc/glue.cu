@@ -39,6 +39,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* h_in, const T* __restrict__ delta,
                                                           const T* __restrict__ w, T* h_out,
                                                           T* __restrict__ x, int H, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -67,6 +69,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(const uint4* h_in, const uint4* __restrict__ delta,
                                                                const uint4* __restrict__ w, uint4* h_out,
                                                                uint4* __restrict__ x, int H8, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H8;
   constexpr int kMaxV = 4;  // vectors per thread (H <= 8 * 4 * blockDim)
@@ -107,6 +111,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(const uint4* h_in
 // y[t, i] = silu(gu[t, i]) * gu[t, I + i]   (SwiGLU on a fused gate|up projection)
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T* __restrict__ y, int I, int rows) {
+  pdl_wait();
+  pdl_trigger();
   const size_t n = (size_t)rows * I;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / I, c = i % I;
@@ -119,6 +125,8 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T
 template <typename T>
 __global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                                     T* __restrict__ h, int H, int V) {
+  pdl_wait();
+  pdl_trigger();
   int id = ids[blockIdx.x];
   id = min(max(id, 0), V - 1);
   const uint4* src = (const uint4*)(table + (size_t)id * H);
@@ -129,6 +137,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ ids,
 // out[t] = index of the first maximum of logits[t, :]  (greedy tokens, runtime.py:90-98)
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int V) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sv[32];
   __shared__ int si[32];
   const T* row = logits + (size_t)blockIdx.x * V;
@@ -194,6 +204,8 @@ struct GdnPrepArgs {
 };
 template <typename T>
 __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[32];
   const int t = blockIdx.x, hb = blockIdx.y, d = threadIdx.x;
   const int key_dim = a.Hk * a.Dk, conv_dim = 2 * key_dim + a.Hv * a.Dv;
@@ -248,6 +260,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ proj,
                                                             long long ld, int z_off, const T* __restrict__ w,
                                                             T* __restrict__ out, int rows_heads, int Hv, int Dv, float eps) {
+  pdl_wait();
+  pdl_trigger();
   const int rh = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (rh >= rows_heads) return;
   const int t = rh / Hv, hv = rh % Hv;
@@ -276,6 +290,8 @@ struct AttnPrepArgs {
 };
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
+  pdl_wait();
+  pdl_trigger();
   const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int heads = a.Hq + 2 * a.Hk;
   if (idx >= a.T * heads) return;
@@ -318,6 +334,8 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o, const T* __restrict__ proj, long long ld,
                                                         T* __restrict__ out, long long out_ld, int Tn, int Hq, int D) {
+  pdl_wait();
+  pdl_trigger();
   const size_t n = (size_t)Tn * Hq * D;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const int d = (int)(i % D), hq = (int)((i / D) % Hq), t = (int)(i / ((size_t)D * Hq));
@@ -349,10 +367,9 @@ extern "C" int dflash_add_rmsnorm(const void* h_in, const void* delta, const voi
   if (H % 8 == 0 && H <= 8 * 4 * 1024 && al(h_in) && al(delta) && al(w) && al(h_out) && al(x)) {
     int threads = (H / 8 + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
-    DFLASH_DISPATCH(dtype, (add_rmsnorm_vec_kernel<T><<<T_rows, threads, 0, st>>>(
-                               (const uint4*)h_in, (const uint4*)delta, (const uint4*)w, (uint4*)h_out, (uint4*)x, H / 8, eps)));
+    DFLASH_DISPATCH(dtype, (launch_kernel(add_rmsnorm_vec_kernel<T>, dim3(T_rows), dim3(threads), 0, st, (const uint4*)h_in, (const uint4*)delta, (const uint4*)w, (uint4*)h_out, (uint4*)x, H / 8, eps)));
   }
-  DFLASH_DISPATCH(dtype, (add_rmsnorm_kernel<T><<<T_rows, 256, 0, st>>>((const T*)h_in, (const T*)delta, (const T*)w,
+  DFLASH_DISPATCH(dtype, (launch_kernel(add_rmsnorm_kernel<T>, dim3(T_rows), dim3(256), 0, st, (const T*)h_in, (const T*)delta, (const T*)w,
                                                                           (T*)h_out, (T*)x, H, eps)));
 }
 
@@ -360,19 +377,19 @@ extern "C" int dflash_swiglu(const void* gate_up, void* y, int T_rows, int I, in
   if (!gate_up || !y || T_rows < 1 || I < 1) return fail(DFLASH_ERR_BAD_ARG, "swiglu: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = (int)(((size_t)T_rows * I + 255) / 256);
-  DFLASH_DISPATCH(dtype, (swiglu_kernel<T><<<blocks < 2048 ? blocks : 2048, 256, 0, st>>>((const T*)gate_up, (T*)y, I, T_rows)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(swiglu_kernel<T>, dim3(blocks < 2048 ? blocks : 2048), dim3(256), 0, st, (const T*)gate_up, (T*)y, I, T_rows)));
 }
 
 extern "C" int dflash_embed(const int* ids, const void* table, void* h, int T_rows, int H, int V, int dtype, void* stream) {
   if (!ids || !table || !h || T_rows < 1 || H % 8 != 0) return fail(DFLASH_ERR_BAD_ARG, "embed: bad argument (H %% 8 == 0)");
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (embed_kernel<T><<<T_rows, 256, 0, st>>>(ids, (const T*)table, (T*)h, H, V)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(embed_kernel<T>, dim3(T_rows), dim3(256), 0, st, ids, (const T*)table, (T*)h, H, V)));
 }
 
 extern "C" int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream) {
   if (!logits || !out || T_rows < 1 || V < 1) return fail(DFLASH_ERR_BAD_ARG, "argmax: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (argmax_kernel<T><<<T_rows, 1024, 0, st>>>((const T*)logits, out, V)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(argmax_kernel<T>, dim3(T_rows), dim3(1024), 0, st, (const T*)logits, out, V)));
 }
 
 extern "C" int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_off, int a_off, const void* conv_state,
@@ -389,7 +406,7 @@ extern "C" int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_
   const int threads = (D + 31) / 32 * 32;
   dim3 grid(T_rows, 2 * Hk + Hv);
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (gdn_prep_kernel<T><<<grid, threads, 0, st>>>(a)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(gdn_prep_kernel<T>, dim3(grid), dim3(threads), 0, st, a)));
 }
 
 extern "C" int dflash_gated_rmsnorm(const void* y, const void* proj, long long ld, int z_off, const void* w, void* out,
@@ -397,7 +414,7 @@ extern "C" int dflash_gated_rmsnorm(const void* y, const void* proj, long long l
   if (!y || !proj || !w || !out || T_rows < 1) return fail(DFLASH_ERR_BAD_ARG, "gated_rmsnorm: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
   const int rh = T_rows * Hv;
-  DFLASH_DISPATCH(dtype, (gated_rmsnorm_kernel<T><<<(rh + 3) / 4, 128, 0, st>>>((const T*)y, (const T*)proj, ld, z_off,
+  DFLASH_DISPATCH(dtype, (launch_kernel(gated_rmsnorm_kernel<T>, dim3((rh + 3) / 4), dim3(128), 0, st, (const T*)y, (const T*)proj, ld, z_off,
                                                                                  (const T*)w, (T*)out, rh, Hv, Dv, eps)));
 }
 
@@ -412,7 +429,7 @@ extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v
                  T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base};
   const int n = T_rows * (Hq + 2 * Hk);
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (attn_prep_kernel<T><<<(n + 3) / 4, 128, 0, st>>>(a)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(attn_prep_kernel<T>, dim3((n + 3) / 4), dim3(128), 0, st, a)));
 }
 
 extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,
@@ -420,5 +437,5 @@ extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, v
   if (!o || !proj || !out || T_rows < 1 || out_ld < (long long)Hq * D) return fail(DFLASH_ERR_BAD_ARG, "attn_post: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = (int)(((size_t)T_rows * Hq * D + 255) / 256);
-  DFLASH_DISPATCH(dtype, (attn_post_kernel<T><<<blocks, 256, 0, st>>>((const T*)o, (const T*)proj, ld, (T*)out, out_ld, T_rows, Hq, D)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(attn_post_kernel<T>, dim3(blocks), dim3(256), 0, st, (const T*)o, (const T*)proj, ld, (T*)out, out_ld, T_rows, Hq, D)));
 }

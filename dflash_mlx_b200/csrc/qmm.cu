@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                   const __grid_constant__ CUtensorMap tmB, const T* __restrict__ x, const T* __restrict__ bias,
                   T* __restrict__ y, float4* __restrict__ pieces, unsigned* __restrict__ counters,
-                  const __grid_constant__ QmmPlan plan, int* __restrict__ err) {
+                  const __grid_constant__ QmmPlan plan, int* __restrict__ err, const int dependent) {
   using C = Cfg<G>;
   using TR = MmaTraits<T>;
   extern __shared__ uint8_t smem_raw[];
@@ -264,15 +264,25 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     if (++pkc == sg.cs) { pkc = 0; ++pnt; }
     ++pu;
   };
-  if (threadIdx.x == 0) {
+  // A dependent launch (blocks may start while the previous kernel of the stream drains) requests its first weight
+  // stages - written by no kernel - before it waits for that kernel, and the activations (its output) after; every
+  // store of this kernel comes after the wait too.  An ordinary launch asks for the small, L2-resident activation
+  // slab first so that it does not queue behind the weight stages.
+  auto issue_x = [&]() {
     mbar_arrive_expect_tx(bar_x, (uint32_t)(M * slabK * 2));
     for (int r = 0; r < M; ++r)
       bulk_load_1d(smem_u32(xbuf + r * C::kXRowBytes), x + (size_t)r * K + (size_t)sg.c0 * C::BK,
                    (uint32_t)(slabK * 2), bar_x);
-  }
+  };
+  if (!dependent && threadIdx.x == 0) issue_x();
   if (ctid == 0) {
 #pragma unroll 1
     for (int j = 0; j < C::kStages - 1; ++j) issue_one();
+  }
+  if (dependent) {
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x == 0) issue_x();
   }
 
   // rows >= M of the activation slab are zeros (all 512 threads take part)
@@ -454,6 +464,8 @@ __global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ 
                                                           const T* __restrict__ bias, T* __restrict__ y, int M, int K,
                                                           int N, int G) {
   using TR = MmaTraits<T>;
+  pdl_wait();
+  pdl_trigger();
   const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (n >= N) return;
   float acc[16];
@@ -609,9 +621,10 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   unsigned* counters = (unsigned*)ws;
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
   const int grid = plan.slab_cta0[plan.S] / 2;
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tw, ts, tb, (const T*)x, (const T*)bias, (T*)y, pieces, counters, plan,
-                                              device_error_word(device));
-  e = cudaGetLastError();
+  const bool dependent = pdl_enabled_for_next_launch();
+  e = launch_kernel_as(dependent, kern, dim3(grid), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb, (const T*)x,
+                       (const T*)bias, (T*)y, pieces, counters, plan, device_error_word(device), dependent ? 1 : 0);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
 }
@@ -640,9 +653,9 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
     }
   }
   g_last_impl = 3;
-  qmm_general_kernel<T><<<(N + 7) / 8, 256, 0, st>>>((const T*)x, (const uint32_t*)wq, (const T*)sc, (const T*)bi,
-                                                     (const T*)bias, (T*)y, M, K, N, G);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(qmm_general_kernel<T>, dim3((N + 7) / 8), dim3(256), 0, st, (const T*)x,
+                                (const uint32_t*)wq, (const T*)sc, (const T*)bi, (const T*)bias, (T*)y, M, K, N, G);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm general launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
 }

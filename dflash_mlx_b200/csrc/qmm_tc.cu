@@ -240,6 +240,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const uint32_t lane_base = (uint32_t)((warp & 3) << 5) << 16;
     const uint32_t xaddr = smem_u32(xbuf);
     bool aborted = false;
+    // The producer warp above requests weights (written by no kernel) at once; the warps here read the previous
+    // kernel's output and write this kernel's, so they first wait for the previous kernel of the stream.
+    pdl_wait();
+    pdl_trigger();
     // Activation slab: read straight from global memory (it is L2 resident), re-tiled to the K-major core-matrix
     // layout [k/8][16 tokens][8] with the k order inside every 8-block permuted to (0,4,1,5,2,6,3,7) - the order in
     // which LOP3 yields nibble pairs.  A warp covers 16 tokens x 2 k-blocks: full 32-byte sectors from global
@@ -572,10 +576,10 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   }
   unsigned* counters = (unsigned*)ws;
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
-  qmm_tc_kernel<<<plan.slab_cta0[plan.S], kThreads, kSmemBytes, st>>>(tw, ts, tb, (const __nv_bfloat16*)x, (const __nv_bfloat16*)bias,
-                                                                      (__nv_bfloat16*)y, pieces, counters, plan,
-                                                                      device_error_word(device));
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(qmm_tc_kernel, dim3(plan.slab_cta0[plan.S]), dim3(kThreads), kSmemBytes, st, tw, ts, tb,
+                                (const __nv_bfloat16*)x, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, pieces, counters,
+                                plan, device_error_word(device));
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm_tc launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
 }

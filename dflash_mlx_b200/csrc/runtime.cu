@@ -2,6 +2,7 @@
 // tensor-map encoder lookup and device properties.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -16,7 +17,21 @@ int* g_status_ptr[64] = {};
 int g_sm_count[64] = {};
 tensormap_encode_fn g_encoder = nullptr;
 bool g_encoder_tried = false;
+int g_pdl = -1;                        // -1: not decided yet (environment DFLASH_PDL, default on)
+thread_local int g_pdl_skip = 0;       // launches of this thread that must be plain (fully serialised)
 }  // namespace
+
+bool pdl_enabled_for_next_launch() {
+  if (g_pdl < 0) {
+    const char* e = getenv("DFLASH_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (g_pdl_skip > 0) {
+    --g_pdl_skip;
+    return false;
+  }
+  return g_pdl == 1;
+}
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -79,6 +94,16 @@ int sm_count(int device) {
 }  // namespace dflash
 
 extern "C" int dflash_version(void) { return 100; }
+
+extern "C" void dflash_set_pdl(int on) { dflash::g_pdl = on ? 1 : 0; }
+extern "C" int dflash_get_pdl(void) {
+  if (dflash::g_pdl < 0) {
+    const char* e = getenv("DFLASH_PDL");
+    dflash::g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return dflash::g_pdl;
+}
+extern "C" void dflash_pdl_plain_next(int launches) { dflash::g_pdl_skip = launches > 0 ? launches : 0; }
 
 extern "C" const char* dflash_last_error_string(void) { return dflash::g_err; }
 

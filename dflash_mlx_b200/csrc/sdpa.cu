@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
   constexpr int KS = D / 16;         // k-steps of Q K^T
   constexpr int NT_O = D / 8;        // n-tiles of O
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_wait();
+  pdl_trigger();
   const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = blockIdx.x, bhk = blockIdx.y, b = bhk / a.Hk, hk = bhk % a.Hk;
@@ -261,6 +263,8 @@ __global__ void __launch_bounds__(D) sdpa_combine_kernel(const SdpaArgs a, int r
   __shared__ float sw[1024];
   __shared__ float sred[D / 32];
   __shared__ float sden;
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* pm = a.part_m + (size_t)row * a.splits;
   const float* pl = a.part_l + (size_t)row * a.splits;
@@ -341,12 +345,12 @@ int launch(SdpaArgs a, void* ws, size_t ws_bytes, int requested_splits, cudaStre
     attr_done[device & 63] = true;
   }
   dim3 grid(a.splits, a.B * a.Hk, zg);
-  kern<<<grid, nwarps * 32, smem, st>>>(a);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(kern, grid, dim3(nwarps * 32), smem, st, a);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa partials launch: %s", cudaGetErrorString(e));
   if (a.splits > 1) {
-    sdpa_combine_kernel<T, D><<<(unsigned)rows, D, 0, st>>>(a, (int)rows);
-    e = cudaGetLastError();
+    e = launch_kernel(sdpa_combine_kernel<T, D>, dim3((unsigned)rows), dim3(D), 0, st, a, (int)rows);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa combine launch: %s", cudaGetErrorString(e));
   }
   return DFLASH_OK;

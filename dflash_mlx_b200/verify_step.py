@@ -210,6 +210,13 @@ class HybridVerifyModel:
                                         self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
         self._chk(st, "dflash_verify_qmm")
 
+    def _reduce(self, t):
+        """Sum of a row-parallel output over the ranks.  The collective joins the stream through an event, so the
+        library's next kernel is launched as an ordinary (fully serialised) kernel."""
+        if self.all_reduce is not None:
+            self.all_reduce(t)
+            self.lib.dflash_pdl_plain_next(1)
+
     def _add_rmsnorm(self, delta, w):
         st = self.lib.dflash_add_rmsnorm(self.h.data_ptr(), _lib.ptr(delta), w.data_ptr(), self.h.data_ptr(),
                                          self.x.data_ptr(), self.cfg.block, self.cfg.hidden, self.cfg.eps, _lib.BF16, self._st())
@@ -291,15 +298,13 @@ class HybridVerifyModel:
                           "dflash_gated_rmsnorm")
                 self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
-            if self.all_reduce is not None:
-                self.all_reduce(self.delta)
+            self._reduce(self.delta)
             self._add_rmsnorm(self.delta, L["post_norm"])
             self._qmm(self.x, L["gate_up"], self.gu)
             self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
                       "dflash_swiglu")
             self._qmm(self.act, L["down"], self.delta)
-            if self.all_reduce is not None:
-                self.all_reduce(self.delta)
+            self._reduce(self.delta)
             delta = self.delta
         self._add_rmsnorm(delta, self.w["norm"])
         self._qmm(self.x, self.w["lm_head"], self.logits)

@@ -44,6 +44,19 @@ DFLASH_API const char* dflash_last_error_string(void);
  * bounded wait.  This call synchronises the device. */
 DFLASH_API int dflash_device_error(int device);
 
+/* Programmatic dependent launch (no counterpart in the reference; Metal orders its dispatches itself).
+ * When on (default; environment DFLASH_PDL=0 turns it off), every kernel of this library is launched so
+ * that its blocks may be scheduled while the previous kernel of the same stream is still draining; each
+ * kernel waits on the device for that previous kernel to finish before it reads or writes anything a
+ * kernel may have produced, so results do not change.  Works in plain streams and under stream capture.
+ *   dflash_set_pdl(on)              process-wide switch
+ *   dflash_pdl_plain_next(n)        the next n launches made by the calling thread are ordinary,
+ *                                   fully serialised launches (use after work of another library that
+ *                                   was joined into the stream through an event, e.g. a collective) */
+DFLASH_API void dflash_set_pdl(int on);
+DFLASH_API int dflash_get_pdl(void);
+DFLASH_API void dflash_pdl_plain_next(int launches);
+
 /* ---------------------------------------------------------------------------------------------
  * verify_qmm: y[M,N] = x[M,K] . dequant(w_q)[N,K]^T (+ bias[N]),  M <= 16.
  * Replaces the Metal kernels `verify_mma2big` / `verify_mma2big_pipe` and their dispatcher
