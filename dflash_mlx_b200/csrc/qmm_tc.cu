@@ -3,21 +3,21 @@
 // accumulator in tensor memory.  Same contract as qmm_stream_kernel (qmm.cu); replaces the same reference code
 // (dflash_mlx/verify_qmm.py:28-331).
 //
-// Why: the mma.sync kernel spends ~54 warp instructions per 512 weights (fragment shuffling, per-fragment
-// scale FMAs, MMA issue by every warp).  Here a thread owns ONE weight row: it reads 32 bytes of nibbles per
-// quantisation group, turns them into bf16 (128 + nib) with LOP3 and writes them straight into tensor memory
-// (tcgen05.st); one elected thread issues the MMAs (M = 128 rows, N = 16 tokens, K = 16); the per-group
-// result comes back with tcgen05.ld and is folded into 16 fp32 registers with the row's scale - a per-thread
-// scalar - as   out += s * acc + (b - 128 s) * sum_{k in group} x[k].
+// A thread owns ONE weight row: it reads 32 bytes of nibbles per quantisation group, turns them into bf16
+// (128 + nib) with LOP3 and writes them straight into tensor memory (tcgen05.st); one thread issues the MMAs
+// (M = 128 rows, N = 16 tokens, K = 16); the per-group result comes back with tcgen05.ld and is folded into 16 fp32
+// registers with the row's scale - a per-thread scalar - as   out += s * acc + (b - 128 s) * sum_{k in group} x[k].
 //
-// Structure of a CTA (1 per SM, persistent over a span of work units):
-//   warps 0-15  : 4 sets x 4 warps.  Warp w may touch TMEM lanes 32*(w%4)..+31, so a set covers the 128 rows;
-//                 set j handles quantisation groups 2j and 2j+1 of every stage.
-//   warp 16     : TMEM allocation and TMA producer (weights: 128B-swizzled boxes; scales, biases; activation slab
-//                 as a 3-D map that lands directly in the K-major core-matrix layout the MMA wants).
-//   MMA issue   : no dedicated warp.  When a set has finished writing a group's operand, the LAST of its four warps
-//                 to get there (a shared-memory ticket) issues that group's four MMAs and the commit, so nothing
-//                 waits for a polling thread.
+// Structure of a CTA (1 per SM, persistent over a span of work units).  The three steps of a group run in
+// different warps and meet only through mbarriers, with several operand and accumulator buffers in flight, so no
+// warp ever waits for the round trip of its own group:
+//   warps 0-7   : dequantisers.  Warp w may touch TMEM lanes 32*(w%4)..+31; warps 0-3 take the even groups of the
+//                 group sequence, warps 4-7 the odd ones.  wait(operand buffer free) -> LOP3 -> tcgen05.st -> arrive.
+//   warps 8-15  : epilogue, same split.  wait(accumulator ready) -> tcgen05.ld -> arrive(accumulator free) -> FMAs;
+//                 at the end of a row tile the two halves are summed through shared memory and stored.
+//   warp 16     : TMEM allocation and TMA producer (weights: 128B-swizzled boxes; scales; biases).
+//   warp 17     : one thread issues every MMA: wait(operand ready, accumulator free) -> 4 x tcgen05.mma ->
+//                 tcgen05.commit to "operand free" and to "accumulator ready".
 // Work unit = 128 rows x 8 groups (one 36 KB stage); K slabs, stream-K spans, fp32 partial tiles, batched
 // tickets and the deterministic last-arriver reduction are those of qmm.cu.
 #include <mutex>
@@ -31,27 +31,32 @@ namespace tc {
 constexpr int kRows = 128;               // weight rows per tile
 constexpr int kG = 64;                   // quantisation group
 constexpr int kBK = 8 * kG;              // k per stage
-constexpr int kSets = 4;
-constexpr int kDequantWarps = 16;
-constexpr int kDequant = kDequantWarps * 32;  // 512
-constexpr int kThreads = kDequant + 32;
-constexpr int kStages = 3;
+constexpr int kDqWarps = 8, kEpWarps = 8;
+constexpr int kWorkers = (kDqWarps + kEpWarps) * 32;  // 512: these threads also load the activation slab
+constexpr int kEp = kEpWarps * 32;                    // 256
+constexpr int kProducerWarp = kDqWarps + kEpWarps, kMmaWarp = kProducerWarp + 1;
+constexpr int kMmaWarps = 3;             // one issuing thread each; pairs of groups are dealt to them round robin
+constexpr int kThreads = kWorkers + 32 + 32 * kMmaWarps;
+constexpr int kTileF4 = 512;             // float4 entries of one fp32 partial tile: [token quad][row]
+constexpr int kStages = 4;
 constexpr int kWBytes = kRows * (kBK / 2);    // 32 KB
 constexpr int kSBBytes = kRows * 16;          // 2 KB
 constexpr int kStageBytes = kWBytes + 2 * kSBBytes;
 constexpr int kSlabK = 2048;
 constexpr int kXBytes = kSlabK * 32;          // [k/8][16 tok][8] bf16
 constexpr int kXsBytes = (kSlabK / kG) * 16 * 4;
-constexpr int kRedBytes = kSets * kRows * 16 * 4;
+constexpr int kRedBytes = 2 * 2 * kRows * 16;  // [writer half][2 token quads][row] float4
 constexpr int kMaxSlabs = 64;
 constexpr int kMaxPend = 32;
 constexpr int kMaxRowTiles = 16384;
-constexpr int kNumBars = 2 * kStages + 1 + 2 * kSets;  // full, empty, x, mma_done[set][2]
+constexpr int kNP = 4;                   // buffers, one per PAIR of groups of a unit: operand 64 TMEM columns (128 k),
+                                         // accumulator 2 x 16 columns
+constexpr int kNA = kNP, kND = kNP;
+constexpr int kNumBars = 2 * kStages + 2 * kNA + 2 * kND;  // full, empty, a_ready, a_free, d_ready, d_free
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kXsBytes + kRedBytes + 8 * kNumBars +
-                              3 * kMaxPend * 4 + 2 * kSets * 4 + 64;
-constexpr uint32_t kTmemCols = 512;
-// TMEM columns: set j owns [96 j, 96 j + 96): A buffers at +0 and +32 (32 columns = 64 k), D buffers at +64, +80.
-constexpr uint32_t kSetCols = 96;
+                              3 * kMaxPend * 4 + 64;
+constexpr uint32_t kTmemCols = 512;      // A buffers at columns 0..255, accumulators at 256..383
+constexpr uint32_t kDCol0 = 64 * kNP;
 
 struct Plan {
   int M, K, N, NT, S, maxp;
@@ -151,22 +156,27 @@ __device__ __forceinline__ void store_rows(const float4& v, T* __restrict__ y, c
   if (tok + 3 < M) y[(size_t)(tok + 3) * N + n] = __float2bfloat16_rn(v.w + bv);
 }
 
-// Thread `tid` of the CTA that took the last ticket of row tile nt sums that tile's partial tiles in a fixed order.
+// The epilogue threads of the CTA that took the last ticket of row tile nt sum that tile's partial tiles in a fixed
+// order; thread (half, r) owns token quads 2*half and 2*half+1 of row r.
 __device__ __noinline__ void finalize_tile(const Plan& plan, const float4* pieces, unsigned* counters,
                                            __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ bias, int nt,
-                                           int tid, int set, int r) {
-  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                                           int etid, int half, int r) {
+  float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+  const int i0 = (2 * half) * kRows + r, i1 = i0 + kRows;
   for (int s2 = 0; s2 < plan.S; ++s2) {
     const SlabGeom g2 = slab_geom(plan, s2);
     int f;
     const int np = tile_pieces(g2, nt, &f);
     for (int p = 0; p < np; ++p) {
-      const float4 a = ld_cg_f4(&pieces[((size_t)(s2 * plan.maxp + p) * plan.NT + nt) * kDequant + tid]);
-      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+      const float4* base = &pieces[((size_t)(s2 * plan.maxp + p) * plan.NT + nt) * kTileF4];
+      const float4 a = ld_cg_f4(base + i0), b = ld_cg_f4(base + i1);
+      v0.x += a.x; v0.y += a.y; v0.z += a.z; v0.w += a.w;
+      v1.x += b.x; v1.y += b.y; v1.z += b.z; v1.w += b.w;
     }
   }
-  if (tid == 0) counters[nt] = 0;
-  store_rows<__nv_bfloat16>(v, y, bias, nt * kRows + r, set, plan.M, plan.N);
+  if (etid == 0) counters[nt] = 0;
+  store_rows<__nv_bfloat16>(v0, y, bias, nt * kRows + r, 2 * half, plan.M, plan.N);
+  store_rows<__nv_bfloat16>(v1, y, bias, nt * kRows + r, 2 * half + 1, plan.M, plan.N);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -182,11 +192,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   float4* red = (float4*)((uint8_t*)xs + kXsBytes);
   uint64_t* bars = (uint64_t*)((uint8_t*)red + kRedBytes);
   volatile int* pend = (volatile int*)(bars + kNumBars);
-  int* tickets = (int*)(pend + 3 * kMaxPend);  // [set][buf]: warps of the set that have written the operand
-  uint32_t* tmem_holder = (uint32_t*)(tickets + 2 * kSets);
+  uint32_t* tmem_holder = (uint32_t*)(pend + 3 * kMaxPend);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t bar_full = bar0, bar_empty = bar0 + 8 * kStages, bar_x = bar0 + 16 * kStages;
-  const uint32_t bar_done = bar_x + 8;  // [set][buf]
+  const uint32_t bar_full = bar0, bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_aready = bar_empty + 8 * kStages, bar_afree = bar_aready + 8 * kNA;
+  const uint32_t bar_dready = bar_afree + 8 * kNA, bar_dfree = bar_dready + 8 * kND;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -201,22 +211,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, kDequantWarps);
+      mbar_init(bar_empty + 8 * i, kDqWarps + kEpWarps);
     }
-    mbar_init(bar_x, 1);
-    for (int i = 0; i < 2 * kSets; ++i) {
-      mbar_init(bar_done + 8 * i, 1);  // tcgen05.commit
-      tickets[i] = 0;
+    for (int i = 0; i < kNA; ++i) {
+      mbar_init(bar_aready + 8 * i, 4);  // the four warps that cover the 128 rows
+      mbar_init(bar_afree + 8 * i, 1);   // tcgen05.commit
+    }
+    for (int i = 0; i < kND; ++i) {
+      mbar_init(bar_dready + 8 * i, 1);  // tcgen05.commit
+      mbar_init(bar_dfree + 8 * i, 4);
     }
     mbar_fence_init();
   }
-  if (warp == kDequantWarps) tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+  if (warp == kProducerWarp) tmem_alloc(smem_u32(tmem_holder), kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_holder;
 
-  if (warp == kDequantWarps) {
+  if (warp == kProducerWarp) {
     // ======================= TMA producer =======================
     if (lane == 0) {
       const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
@@ -234,11 +247,39 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (++kc == sg.cs) { kc = 0; ++nt; }
       }
     }
+  } else if (warp >= kMmaWarp) {
+    // ======================= MMA issue =======================
+    named_bar_sync(2, kWorkers + 32 * kMmaWarps);  // the worker warps have written the activation slab
+    if (lane == 0) {
+      const uint32_t xaddr = smem_u32(xbuf);
+      bool aborted = false;
+      // Pair p of the span (4 per unit) is handled by issuing thread p % kMmaWarps and uses buffer p % 4; waits
+      // and commits are per pair, so a thread pays their latency once per 8 MMAs.
+      const unsigned npairs = (u_end - u_begin) * 4u;
+      for (unsigned p = (unsigned)(warp - kMmaWarp); p < npairs; p += kMmaWarps) {
+        const unsigned ui = p >> 2;
+        const int j = (int)(p & 3u);
+        const uint32_t upar = ui & 1u;
+        const int kc = (int)((u_begin + ui) % (unsigned)sg.cs);
+        if (!aborted && !mbar_wait(bar_aready + 8 * j, upar)) { aborted = true; atomicExch(err, 12); }
+        if (!aborted && !mbar_wait(bar_dfree + 8 * j, upar ^ 1)) { aborted = true; atomicExch(err, 13); }
+        tc_fence_after();
+#pragma unroll
+        for (int g2 = 0; g2 < 2; ++g2) {
+          const int gs = kc * 8 + 2 * j + g2;  // group index inside the slab
+          const uint32_t d = tmem + kDCol0 + 32 * j + 16 * g2, a = tmem + 64 * j + 32 * g2;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            tc_mma(d, a + 8 * i, smem_desc(xaddr + (uint32_t)(gs * 8 + 2 * i) * 256u, 256u, 128u), kIdesc, i > 0);
+        }
+        tc_commit(bar_afree + 8 * j);
+        tc_commit(bar_dready + 8 * j);
+      }
+    }
   } else {
-    // ======================= dequant / epilogue warps =======================
-    const int set = warp >> 2, r = ((warp & 3) << 5) | lane;  // TMEM lane = weight row inside the tile
+    // ======================= worker warps: dequantisers (0-7) and epilogue (8-15) =======================
+    const int r = ((warp & 3) << 5) | lane;  // TMEM lane = weight row inside the tile
     const uint32_t lane_base = (uint32_t)((warp & 3) << 5) << 16;
-    const uint32_t xaddr = smem_u32(xbuf);
     bool aborted = false;
     // The producer warp above requests weights (written by no kernel) at once; the warps here read the previous
     // kernel's output and write this kernel's, so they first wait for the previous kernel of the stream.
@@ -250,23 +291,23 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // memory, consecutive 16-byte chunks in shared memory.
     {
       const int kb_lim = (plan.K - sg.c0 * kBK) / 8;  // k-blocks that exist from the slab start
-      uint4 v[kXBytes / 16 / kDequant];
+      uint4 v[kXBytes / 16 / kWorkers];
 #pragma unroll
-      for (int j = 0; j < kXBytes / 16 / kDequant; ++j) {
-        const int ci = tid + j * kDequant, tok = ci & 15, kb = ci >> 4;
+      for (int j = 0; j < kXBytes / 16 / kWorkers; ++j) {
+        const int ci = tid + j * kWorkers, tok = ci & 15, kb = ci >> 4;
         v[j] = make_uint4(0, 0, 0, 0);
         if (tok < M && kb < kb_lim) v[j] = *(const uint4*)(x + (size_t)tok * plan.K + (size_t)sg.c0 * kBK + kb * 8);
       }
 #pragma unroll
-      for (int j = 0; j < kXBytes / 16 / kDequant; ++j) {
+      for (int j = 0; j < kXBytes / 16 / kWorkers; ++j) {
         uint4 o;
         o.x = prmt(v[j].x, v[j].z, 0x5410); o.y = prmt(v[j].x, v[j].z, 0x7632);
         o.z = prmt(v[j].y, v[j].w, 0x5410); o.w = prmt(v[j].y, v[j].w, 0x7632);
-        ((uint4*)xbuf)[tid + j * kDequant] = o;
+        ((uint4*)xbuf)[tid + j * kWorkers] = o;
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    named_bar_sync(1, kDequant);
+    named_bar_sync(2, kWorkers + 32 * kMmaWarps);  // the slab is complete: the MMA warp may read it
     // group sums of x: thread (g, tok) adds the 64 activations of group g for token tok
     {
       const int g = tid >> 4, tok = tid & 15;
@@ -283,172 +324,180 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
       xs[g * 16 + tok] = acc;
     }
-    named_bar_sync(1, kDequant);
+    named_bar_sync(1, kWorkers);
 
-    float out[16];
+    if (warp < kDqWarps) {
+      // ----------------------------- dequantisers -----------------------------
+      const int ph = warp >> 2;  // 0: even groups of the sequence, 1: odd groups
+      int stage = 0;
+      uint32_t par = 0;
+      uint32_t upar = 0;  // parity of the unit inside this CTA's span
+      for (unsigned u = u_begin; u < u_end; ++u) {
+        if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 15); }
+        const uint8_t* st = stages + stage * kStageBytes;
+        // This warp's two pairs of groups (128 k = 64 bytes of nibbles per row each).
 #pragma unroll
-    for (int i = 0; i < 16; ++i) out[i] = 0.f;
-    // up to two submitted-but-uncollected groups: (scale, folded bias, slab group index)
-    float ps[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
-    int pg[2] = {0, 0};
-    unsigned n = 0, ncol = 0;  // groups submitted / collected by this thread (a unit submits two: buffers 0, 1)
-    bool primed = false;       // two groups are in flight
-    int npend = 0;
-
-    // collect = wait for the MMAs of group `ncol` (buffer `buf`), start the TMEM load of its accumulator ...
-    auto collect_begin = [&](const int buf, uint32_t (&dr)[16]) {
-      const uint32_t par = (ncol >> 1) & 1;
-      if (!aborted && !mbar_wait(bar_done + 8 * (set * 2 + buf), par)) { aborted = true; atomicExch(err, 14); }
-      tc_fence_after();
-      tc_ld16_issue(tmem + lane_base + set * kSetCols + 64 + 16 * buf, dr);
-    };
-    // ... and fold it into `out` with that group's scale and bias.
-    auto collect_end = [&](const int buf, uint32_t (&dr)[16]) {
-      tc_ld16_wait(dr);
-      const float sc = ps[buf], bq = pb[buf];
-      const float4* xr = (const float4*)(xs + pg[buf] * 16);
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = 2 * jj + ph;
+          const uint8_t* wrow = st + (j >> 1) * (kRows * 128) + r * 128;
+          const int c0 = 4 * (j & 1);
+          uint4 w4[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 xv = xr[i];
-        out[4 * i + 0] = fmaf(sc, __uint_as_float(dr[4 * i + 0]), fmaf(bq, xv.x, out[4 * i + 0]));
-        out[4 * i + 1] = fmaf(sc, __uint_as_float(dr[4 * i + 1]), fmaf(bq, xv.y, out[4 * i + 1]));
-        out[4 * i + 2] = fmaf(sc, __uint_as_float(dr[4 * i + 2]), fmaf(bq, xv.z, out[4 * i + 2]));
-        out[4 * i + 3] = fmaf(sc, __uint_as_float(dr[4 * i + 3]), fmaf(bq, xv.w, out[4 * i + 3]));
-      }
-      ++ncol;
-    };
-    auto flush_tickets = [&]() {
-      named_bar_sync(1, kDequant);
-      if (tid == 32) {
-        __threadfence();
-        for (int i0 = 0; i0 < npend; i0 += 8) {
-          unsigned t[8];
+          for (int c = 0; c < 4; ++c) w4[c] = *(const uint4*)(wrow + (((c0 + c) ^ (r & 7)) << 4));
+          if (!aborted && !mbar_wait(bar_afree + 8 * j, upar ^ 1)) { aborted = true; atomicExch(err, 16); }
+          tc_fence_after();
+          const uint32_t a_addr = tmem + lane_base + 64 * j;
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (i0 + j < npend) t[j] = atomicAdd(&counters[pend[i0 + j]], 1u);
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t words[4] = {w4[c].x, w4[c].y, w4[c].z, w4[c].w};
+            uint32_t regs[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (i0 + j < npend) pend[2 * kMaxPend + i0 + j] = (t[j] == (unsigned)(pend[kMaxPend + i0 + j] - 1));
+            for (int w = 0; w < 4; ++w)
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                regs[4 * w + q] = lop3_and_or(words[w] >> (4 * q), 0x000F000Fu, 0x43004300u);
+            tc_st16(a_addr + 16 * c, regs);
+          }
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_aready + 8 * j);
         }
-        __threadfence();
-      }
-      named_bar_sync(1, kDequant);
-      for (int i = 0; i < npend; ++i)
-        if (pend[2 * kMaxPend + i]) finalize_tile(plan, pieces, counters, y, bias, pend[i], tid, set, r);
-      named_bar_sync(1, kDequant);
-    };
-
-    int stage = 0, nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
-    uint32_t par = 0;
-    for (unsigned u = u_begin; u < u_end; ++u) {
-      if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 15); }
-      const uint8_t* st = stages + stage * kStageBytes;
-      const uint32_t s2 = *(const uint32_t*)(st + kWBytes + r * 16 + set * 4);
-      const uint32_t b2 = *(const uint32_t*)(st + kWBytes + kSBBytes + r * 16 + set * 4);
-#pragma unroll
-      for (int g2 = 0; g2 < 2; ++g2, ++n) {
-        const int buf = g2;
-        const int gi = 2 * set + g2;
-        const uint8_t* wrow = st + (gi >> 2) * (kRows * 128) + r * 128;
-        const int c0 = 2 * (gi & 3);
-        // long-latency operations are issued back to back and their waits pushed behind independent work:
-        // weights (shared memory) -> previous accumulator (TMEM load) -> dequantise -> TMEM store -> fold -> publish
-        const uint4 w0 = *(const uint4*)(wrow + (((c0) ^ (r & 7)) << 4));
-        const uint4 w1 = *(const uint4*)(wrow + (((c0 + 1) ^ (r & 7)) << 4));
-        uint32_t dr[16];
-        if (primed) collect_begin(buf, dr);  // also means A[buf] and D[buf] are free again
-        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-        const uint32_t a_addr = tmem + lane_base + set * kSetCols + 32 * buf;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t regs[16];
-#pragma unroll
-          for (int w = 0; w < 4; ++w)
-#pragma unroll
-            for (int p = 0; p < 4; ++p)
-              regs[4 * w + p] = lop3_and_or(words[4 * half + w] >> (4 * p), 0x000F000Fu, 0x43004300u);
-          tc_st16(a_addr + 16 * half, regs);
-        }
-        if (primed) collect_end(buf, dr);
-        tc_wait_st();
-        tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          const int old = atomicAdd(&tickets[set * 2 + buf], 1);
-          if ((old & 3) == 3) {  // the set's operand for this group is complete: issue its MMAs
-            __threadfence_block();
-            tc_fence_after();
-            const int gs = kc * 8 + gi;  // group index inside the slab
-            const uint32_t d = tmem + set * kSetCols + 64 + 16 * buf, a = tmem + set * kSetCols + 32 * buf;
+        if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+        upar ^= 1;
+        if (++stage == kStages) { stage = 0; par ^= 1; }
+      }
+    } else {
+      // ----------------------------- epilogue -----------------------------
+      const int half = (warp - kDqWarps) >> 2;  // 0: even groups of the sequence, 1: odd groups
+      const int etid = tid - kDqWarps * 32;     // 0..255
+      float out[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              tc_mma(d, a + 8 * i, smem_desc(xaddr + (uint32_t)(gs * 8 + 2 * i) * 256u, 256u, 128u), kIdesc, i > 0);
-            tc_commit(bar_done + 8 * (set * 2 + buf));
+      for (int i = 0; i < 16; ++i) out[i] = 0.f;
+      int npend = 0;
+      auto flush_tickets = [&]() {
+        named_bar_sync(3, kEp);
+        if (etid == 32) {
+          __threadfence();
+          for (int i0 = 0; i0 < npend; i0 += 8) {
+            unsigned t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i0 + j < npend) t[j] = atomicAdd(&counters[pend[i0 + j]], 1u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i0 + j < npend) pend[2 * kMaxPend + i0 + j] = (t[j] == (unsigned)(pend[kMaxPend + i0 + j] - 1));
+          }
+          __threadfence();
+        }
+        named_bar_sync(3, kEp);
+        for (int i = 0; i < npend; ++i)
+          if (pend[2 * kMaxPend + i]) finalize_tile(plan, pieces, counters, y, bias, pend[i], etid, half, r);
+        named_bar_sync(3, kEp);
+      };
+
+      int stage = 0, nt = (int)(u_begin / sg.cs), kc = (int)(u_begin % sg.cs);
+      uint32_t par = 0;
+      uint32_t upar = 0;  // parity of the unit inside this CTA's span
+      for (unsigned u = u_begin; u < u_end; ++u) {
+        if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 17); }
+        const uint8_t* st = stages + stage * kStageBytes;
+        const uint4 s8 = *(const uint4*)(st + kWBytes + r * 16);             // the row's 8 scales
+        const uint4 b8 = *(const uint4*)(st + kWBytes + kSBBytes + r * 16);  // and 8 biases
+        const uint32_t sw[4] = {s8.x, s8.y, s8.z, s8.w}, bw[4] = {b8.x, b8.y, b8.z, b8.w};
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * stage);  // the scales and biases are in registers
+        // this warp's two pairs of groups; the two accumulators of a pair are fetched together
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = 2 * jj + half;
+          uint32_t dr[2][16];
+          if (!aborted && !mbar_wait(bar_dready + 8 * j, upar)) { aborted = true; atomicExch(err, 14); }
+          tc_fence_after();
+          tc_ld16_issue(tmem + lane_base + kDCol0 + 32 * j, dr[0]);
+          tc_ld16_issue(tmem + lane_base + kDCol0 + 32 * j + 16, dr[1]);
+          tc_ld16_wait(dr[0]);
+          tc_ld16_wait(dr[1]);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_dfree + 8 * j);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int gi = 2 * j + q;
+            // groups 2j and 2j+1 share word j of the row's scales: low and high bf16
+            const float sc = __uint_as_float(q ? (sw[j] & 0xFFFF0000u) : (sw[j] << 16));
+            const float bi = __uint_as_float(q ? (bw[j] & 0xFFFF0000u) : (bw[j] << 16));
+            const float bq = fmaf(-128.f, sc, bi);
+            const float4* xr = (const float4*)(xs + (kc * 8 + gi) * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 xv = xr[i];
+              out[4 * i + 0] = fmaf(sc, __uint_as_float(dr[q][4 * i + 0]), fmaf(bq, xv.x, out[4 * i + 0]));
+              out[4 * i + 1] = fmaf(sc, __uint_as_float(dr[q][4 * i + 1]), fmaf(bq, xv.y, out[4 * i + 1]));
+              out[4 * i + 2] = fmaf(sc, __uint_as_float(dr[q][4 * i + 2]), fmaf(bq, xv.z, out[4 * i + 2]));
+              out[4 * i + 3] = fmaf(sc, __uint_as_float(dr[q][4 * i + 3]), fmaf(bq, xv.w, out[4 * i + 3]));
+            }
           }
         }
-        const float sc = __uint_as_float((g2 ? (s2 >> 16) : (s2 & 0xFFFFu)) << 16);
-        const float bi = __uint_as_float((g2 ? (b2 >> 16) : (b2 & 0xFFFFu)) << 16);
-        ps[buf] = sc;
-        pb[buf] = fmaf(-128.f, sc, bi);
-        pg[buf] = kc * 8 + gi;
-      }
-      primed = true;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
-      if (++stage == kStages) { stage = 0; par ^= 1; }
+        upar ^= 1;
+        if (++stage == kStages) { stage = 0; par ^= 1; }
 
-      const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
-      if (seg_end) {
-        {
-          uint32_t d0[16], d1[16];
-          collect_begin(0, d0);
-          ++ncol;              // the parity of buffer 1's barrier belongs to the next group
-          collect_begin(1, d1);
-          --ncol;
-          collect_end(0, d0);
-          collect_end(1, d1);
-        }
-        primed = false;
+        const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
+        if (seg_end) {
+          // Each half holds the sums of its own groups for all 16 tokens.  It keeps token quads 2*half, 2*half+1
+          // and hands the other two to its partner through shared memory.
+          float4 v0, v1;
+          if (half == 0) {
+            red[(0 * 2 + 0) * kRows + r] = make_float4(out[8], out[9], out[10], out[11]);
+            red[(0 * 2 + 1) * kRows + r] = make_float4(out[12], out[13], out[14], out[15]);
+            v0 = make_float4(out[0], out[1], out[2], out[3]);
+            v1 = make_float4(out[4], out[5], out[6], out[7]);
+          } else {
+            red[(1 * 2 + 0) * kRows + r] = make_float4(out[0], out[1], out[2], out[3]);
+            red[(1 * 2 + 1) * kRows + r] = make_float4(out[4], out[5], out[6], out[7]);
+            v0 = make_float4(out[8], out[9], out[10], out[11]);
+            v1 = make_float4(out[12], out[13], out[14], out[15]);
+          }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          red[(set * 4 + i) * kRows + r] = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
-          out[4 * i] = out[4 * i + 1] = out[4 * i + 2] = out[4 * i + 3] = 0.f;
+          for (int i = 0; i < 16; ++i) out[i] = 0.f;
+          named_bar_sync(3, kEp);
+          {
+            const float4 a = red[((half ^ 1) * 2 + 0) * kRows + r], b = red[((half ^ 1) * 2 + 1) * kRows + r];
+            v0.x += a.x; v0.y += a.y; v0.z += a.z; v0.w += a.w;
+            v1.x += b.x; v1.y += b.y; v1.z += b.z; v1.w += b.w;
+          }
+          int total = 0, first_here = 0;
+          for (int sl = lane; sl < plan.S; sl += 32) {
+            const SlabGeom g2 = slab_geom(plan, sl);
+            int f;
+            total += tile_pieces(g2, nt, &f);
+          }
+          total = __reduce_add_sync(0xffffffffu, total);
+          tile_pieces(sg, nt, &first_here);
+          if (total > 1) {
+            float4* base = &pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kTileF4];
+            base[(2 * half) * kRows + r] = v0;
+            base[(2 * half + 1) * kRows + r] = v1;
+            if (etid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
+            ++npend;
+          } else {
+            store_rows<__nv_bfloat16>(v0, y, bias, nt * kRows + r, 2 * half, M, N);
+            store_rows<__nv_bfloat16>(v1, y, bias, nt * kRows + r, 2 * half + 1, M, N);
+          }
+          named_bar_sync(3, kEp);
+          if (npend == kMaxPend) { flush_tickets(); npend = 0; }
         }
-        named_bar_sync(1, kDequant);
-        float4 v = red[(0 * 4 + set) * kRows + r];  // tokens 4*set .. 4*set+3 of row r, summed over the 4 sets
-#pragma unroll
-        for (int s3 = 1; s3 < kSets; ++s3) {
-          const float4 a = red[(s3 * 4 + set) * kRows + r];
-          v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-        }
-        int total = 0, first_here = 0;
-        for (int sl = lane; sl < plan.S; sl += 32) {
-          const SlabGeom g2 = slab_geom(plan, sl);
-          int f;
-          total += tile_pieces(g2, nt, &f);
-        }
-        total = __reduce_add_sync(0xffffffffu, total);
-        tile_pieces(sg, nt, &first_here);
-        if (total > 1) {
-          pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kDequant + tid] = v;
-          if (tid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
-          ++npend;
-        } else {
-          store_rows<__nv_bfloat16>(v, y, bias, nt * kRows + r, set, M, N);
-        }
-        named_bar_sync(1, kDequant);
-        if (npend == kMaxPend) { flush_tickets(); npend = 0; }
+        if (++kc == sg.cs) { kc = 0; ++nt; }
       }
-      if (++kc == sg.cs) { kc = 0; ++nt; }
+      if (npend > 0) flush_tickets();
     }
-    if (npend > 0) flush_tickets();
   }
 
   // every warp ends here: the accumulator memory goes back before the CTA exits
   tc_fence_before();
   __syncthreads();
-  if (warp == kDequantWarps) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -487,7 +536,7 @@ bool make_plan(int M, int K, int N, int device, int max_blocks, Plan* p) {
 }
 
 size_t counters_bytes() { return (size_t)kMaxRowTiles * 4; }
-size_t plan_workspace(const Plan& p) { return counters_bytes() + (size_t)p.S * p.maxp * p.NT * kDequant * sizeof(float4); }
+size_t plan_workspace(const Plan& p) { return counters_bytes() + (size_t)p.S * p.maxp * p.NT * kTileF4 * sizeof(float4); }
 
 struct MapKey {
   const void* p; int a, b, kind;
