@@ -255,7 +255,8 @@ class DenseStepWorkload:
         per_launch = self.bytes["qmm"] / self.n_qmm
         achieved = per_launch / us_per_launch / 1e3
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src, "kernel": "qmm_stream_kernel",
+                "traffic": None, "peak_source": peak_src,
+                "kernel": "verify matmul = qmm_stream_kernel (mma.sync) + qmm_tc_kernel (tcgen05; shapes with N*K >= 60e6, K <= 8192)",
                 "launches_per_step": self.n_qmm, "algorithmic_bytes_per_launch": per_launch,
                 "us_per_launch": us_per_launch, "matmul_share_of_step": aux_ms / ms_per_step,
                 "whole_step_gbps": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9}

@@ -499,7 +499,9 @@ __global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ 
 
 // ------------------------------------------------------------------------------------------
 int g_max_blocks = 0;
-int g_impl = 0;  // 0/1 = mma.sync streaming kernel (measured faster today), 2 = tcgen05 kernel where it applies
+int g_impl = 0;  // 0 = by shape (tcgen05 kernel for the large shapes it is measured faster on), 1 = mma.sync
+                 // streaming kernel always, 2 = tcgen05 kernel wherever it applies
+long long g_tc_min_weights = 60ll * 1000 * 1000;  // N*K from which impl 0 picks the tcgen05 kernel
 thread_local int g_last_impl = 0;  // 1 = mma.sync streaming kernel, 2 = tcgen05 kernel, 3 = general kernel
 
 bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
@@ -634,7 +636,7 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
                int N, int G, void* ws, size_t ws_bytes, cudaStream_t st) {
   int device = 0;
   cudaGetDevice(&device);
-  if (g_impl == 2 && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
+  if ((g_impl == 2 || (g_impl == 0 && (long long)N * K >= g_tc_min_weights && K <= 8192)) && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
       ((uintptr_t)ws & 255) == 0) {
     const int rc = tc::launch(x, wq, sc, bi, bias, y, M, K, N, ws, ws_bytes, st, device, g_max_blocks);
     if (rc <= 0) { g_last_impl = 2; return rc; }

@@ -8,16 +8,19 @@
 // (M = 128 rows, N = 16 tokens, K = 16); the per-group result comes back with tcgen05.ld and is folded into 16 fp32
 // registers with the row's scale - a per-thread scalar - as   out += s * acc + (b - 128 s) * sum_{k in group} x[k].
 //
-// Structure of a CTA (1 per SM, persistent over a span of work units).  The three steps of a group run in
-// different warps and meet only through mbarriers, with several operand and accumulator buffers in flight, so no
-// warp ever waits for the round trip of its own group:
-//   warps 0-7   : dequantisers.  Warp w may touch TMEM lanes 32*(w%4)..+31; warps 0-3 take the even groups of the
-//                 group sequence, warps 4-7 the odd ones.  wait(operand buffer free) -> LOP3 -> tcgen05.st -> arrive.
-//   warps 8-15  : epilogue, same split.  wait(accumulator ready) -> tcgen05.ld -> arrive(accumulator free) -> FMAs;
-//                 at the end of a row tile the two halves are summed through shared memory and stored.
+// Structure of a CTA (1 per SM, persistent over a span of work units).  The three steps of a PAIR of groups (128 k)
+// run in different warps and meet only through mbarriers, with several operand and accumulator buffers in flight, so
+// no warp waits for the round trip of its own work.  (Measured on B200: a satisfied mbarrier wait costs ~80 cycles,
+// a hand-over ~90, one M128 x N16 x K16 tcgen05.mma ~64 cycles of its issuing thread and ~42 of the tensor pipe -
+// hence hand-overs per pair, not per group, and three issuing threads.)
+//   warps 0-7   : dequantisers.  Warp w may touch TMEM lanes 32*(w%4)..+31; warps 0-3 take the even pairs of the
+//                 sequence, warps 4-7 the odd ones.  wait(operand buffer free) -> LOP3 -> tcgen05.st -> arrive.
+//   warps 8-15  : epilogue.  Warps 8-11 own tokens 0-7, warps 12-15 tokens 8-15, of every pair:
+//                 wait(accumulators ready) -> tcgen05.ld -> arrive(accumulators free) -> FMAs; a thread ends up with
+//                 its row's 8 outputs, so the end of a row tile needs no exchange between warps.
 //   warp 16     : TMEM allocation and TMA producer (weights: 128B-swizzled boxes; scales; biases).
-//   warp 17     : one thread issues every MMA: wait(operand ready, accumulator free) -> 4 x tcgen05.mma ->
-//                 tcgen05.commit to "operand free" and to "accumulator ready".
+//   warps 17-19 : one thread each issues MMAs, pairs dealt round robin: wait(operand ready, accumulators free) ->
+//                 8 x tcgen05.mma -> tcgen05.commit to "operand free" and to "accumulators ready".
 // Work unit = 128 rows x 8 groups (one 36 KB stage); K slabs, stream-K spans, fp32 partial tiles, batched
 // tickets and the deterministic last-arriver reduction are those of qmm.cu.
 #include <mutex>
@@ -45,18 +48,17 @@ constexpr int kStageBytes = kWBytes + 2 * kSBBytes;
 constexpr int kSlabK = 2048;
 constexpr int kXBytes = kSlabK * 32;          // [k/8][16 tok][8] bf16
 constexpr int kXsBytes = (kSlabK / kG) * 16 * 4;
-constexpr int kRedBytes = 2 * 2 * kRows * 16;  // [writer half][2 token quads][row] float4
 constexpr int kMaxSlabs = 64;
 constexpr int kMaxPend = 32;
 constexpr int kMaxRowTiles = 16384;
 constexpr int kNP = 4;                   // buffers, one per PAIR of groups of a unit: operand 64 TMEM columns (128 k),
                                          // accumulator 2 x 16 columns
-constexpr int kNA = kNP, kND = kNP;
+constexpr int kNA = 6, kND = kNP;        // operand buffers: pair p of the span uses p % 6; accumulators: p % 4
 constexpr int kNumBars = 2 * kStages + 2 * kNA + 2 * kND;  // full, empty, a_ready, a_free, d_ready, d_free
-constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kXsBytes + kRedBytes + 8 * kNumBars +
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kXBytes + kXsBytes + 8 * kNumBars +
                               3 * kMaxPend * 4 + 64;
 constexpr uint32_t kTmemCols = 512;      // A buffers at columns 0..255, accumulators at 256..383
-constexpr uint32_t kDCol0 = 64 * kNP;
+constexpr uint32_t kDCol0 = 64 * kNA;
 
 struct Plan {
   int M, K, N, NT, S, maxp;
@@ -135,6 +137,18 @@ __device__ __forceinline__ void tc_ld16_wait(uint32_t (&r)[16]) {
                :
                : "memory");
 }
+__device__ __forceinline__ void tc_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_ld8_wait(uint32_t (&r)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+               :
+               : "memory");
+}
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored as 128 contiguous
 // bytes; lbo = byte distance between core matrices along K, sbo = along the row (N) direction.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -189,8 +203,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   uint8_t* stages = smem;
   uint8_t* xbuf = stages + kStages * kStageBytes;
   float* xs = (float*)(xbuf + kXBytes);
-  float4* red = (float4*)((uint8_t*)xs + kXsBytes);
-  uint64_t* bars = (uint64_t*)((uint8_t*)red + kRedBytes);
+  uint64_t* bars = (uint64_t*)((uint8_t*)xs + kXsBytes);
   volatile int* pend = (volatile int*)(bars + kNumBars);
   uint32_t* tmem_holder = (uint32_t*)(pend + 3 * kMaxPend);
   const uint32_t bar0 = smem_u32(bars);
@@ -219,7 +232,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     }
     for (int i = 0; i < kND; ++i) {
       mbar_init(bar_dready + 8 * i, 1);  // tcgen05.commit
-      mbar_init(bar_dfree + 8 * i, 4);
+      mbar_init(bar_dfree + 8 * i, kEpWarps);  // both token halves have read the pair's accumulators
     }
     mbar_fence_init();
   }
@@ -261,18 +274,20 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int j = (int)(p & 3u);
         const uint32_t upar = ui & 1u;
         const int kc = (int)((u_begin + ui) % (unsigned)sg.cs);
-        if (!aborted && !mbar_wait(bar_aready + 8 * j, upar)) { aborted = true; atomicExch(err, 12); }
+        const int ab = (int)(p % (unsigned)kNA);
+        const uint32_t apar = (p / (unsigned)kNA) & 1u;
+        if (!aborted && !mbar_wait(bar_aready + 8 * ab, apar)) { aborted = true; atomicExch(err, 12); }
         if (!aborted && !mbar_wait(bar_dfree + 8 * j, upar ^ 1)) { aborted = true; atomicExch(err, 13); }
         tc_fence_after();
 #pragma unroll
         for (int g2 = 0; g2 < 2; ++g2) {
           const int gs = kc * 8 + 2 * j + g2;  // group index inside the slab
-          const uint32_t d = tmem + kDCol0 + 32 * j + 16 * g2, a = tmem + 64 * j + 32 * g2;
+          const uint32_t d = tmem + kDCol0 + 32 * j + 16 * g2, a = tmem + 64 * ab + 32 * g2;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             tc_mma(d, a + 8 * i, smem_desc(xaddr + (uint32_t)(gs * 8 + 2 * i) * 256u, 256u, 128u), kIdesc, i > 0);
         }
-        tc_commit(bar_afree + 8 * j);
+        tc_commit(bar_afree + 8 * ab);
         tc_commit(bar_dready + 8 * j);
       }
     }
@@ -328,10 +343,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
     if (warp < kDqWarps) {
       // ----------------------------- dequantisers -----------------------------
-      const int ph = warp >> 2;  // 0: even groups of the sequence, 1: odd groups
+      const int ph = warp >> 2;  // 0: even pairs of the sequence, 1: odd pairs
       int stage = 0;
       uint32_t par = 0;
-      uint32_t upar = 0;  // parity of the unit inside this CTA's span
+      int ab = ph;         // this warp's pairs use operand buffers ph, ph+2, ph+4, ph, ...
+      uint32_t fpar = 1;   // parity to wait for on "operand free" (the first use of a buffer passes at once)
       for (unsigned u = u_begin; u < u_end; ++u) {
         if (!aborted && !mbar_wait(bar_full + 8 * stage, par)) { aborted = true; atomicExch(err, 15); }
         const uint8_t* st = stages + stage * kStageBytes;
@@ -344,9 +360,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           uint4 w4[4];
 #pragma unroll
           for (int c = 0; c < 4; ++c) w4[c] = *(const uint4*)(wrow + (((c0 + c) ^ (r & 7)) << 4));
-          if (!aborted && !mbar_wait(bar_afree + 8 * j, upar ^ 1)) { aborted = true; atomicExch(err, 16); }
+          if (!aborted && !mbar_wait(bar_afree + 8 * ab, fpar)) { aborted = true; atomicExch(err, 16); }
           tc_fence_after();
-          const uint32_t a_addr = tmem + lane_base + 64 * j;
+          const uint32_t a_addr = tmem + lane_base + 64 * ab;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const uint32_t words[4] = {w4[c].x, w4[c].y, w4[c].z, w4[c].w};
@@ -361,20 +377,21 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tc_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_aready + 8 * j);
+          if (lane == 0) mbar_arrive(bar_aready + 8 * ab);
+          ab += 2;
+          if (ab >= kNA) { ab -= kNA; fpar ^= 1; }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
-        upar ^= 1;
         if (++stage == kStages) { stage = 0; par ^= 1; }
       }
     } else {
       // ----------------------------- epilogue -----------------------------
-      const int half = (warp - kDqWarps) >> 2;  // 0: even groups of the sequence, 1: odd groups
+      const int half = (warp - kDqWarps) >> 2;  // tokens 8*half .. 8*half+7 of every group
       const int etid = tid - kDqWarps * 32;     // 0..255
-      float out[16];
+      float out[8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) out[i] = 0.f;
+      for (int i = 0; i < 8; ++i) out[i] = 0.f;
       int npend = 0;
       auto flush_tickets = [&]() {
         named_bar_sync(3, kEp);
@@ -408,17 +425,16 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t sw[4] = {s8.x, s8.y, s8.z, s8.w}, bw[4] = {b8.x, b8.y, b8.z, b8.w};
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * stage);  // the scales and biases are in registers
-        // this warp's two pairs of groups; the two accumulators of a pair are fetched together
+        // every pair of groups: this warp takes its 8 token columns of both accumulators
 #pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = 2 * jj + half;
-          uint32_t dr[2][16];
+        for (int j = 0; j < 4; ++j) {
+          uint32_t dr[2][8];
           if (!aborted && !mbar_wait(bar_dready + 8 * j, upar)) { aborted = true; atomicExch(err, 14); }
           tc_fence_after();
-          tc_ld16_issue(tmem + lane_base + kDCol0 + 32 * j, dr[0]);
-          tc_ld16_issue(tmem + lane_base + kDCol0 + 32 * j + 16, dr[1]);
-          tc_ld16_wait(dr[0]);
-          tc_ld16_wait(dr[1]);
+          tc_ld8_issue(tmem + lane_base + kDCol0 + 32 * j + 8 * half, dr[0]);
+          tc_ld8_issue(tmem + lane_base + kDCol0 + 32 * j + 16 + 8 * half, dr[1]);
+          tc_ld8_wait(dr[0]);
+          tc_ld8_wait(dr[1]);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_dfree + 8 * j);
@@ -429,9 +445,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             const float sc = __uint_as_float(q ? (sw[j] & 0xFFFF0000u) : (sw[j] << 16));
             const float bi = __uint_as_float(q ? (bw[j] & 0xFFFF0000u) : (bw[j] << 16));
             const float bq = fmaf(-128.f, sc, bi);
-            const float4* xr = (const float4*)(xs + (kc * 8 + gi) * 16);
+            const float4* xr = (const float4*)(xs + (kc * 8 + gi) * 16 + 8 * half);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 2; ++i) {
               const float4 xv = xr[i];
               out[4 * i + 0] = fmaf(sc, __uint_as_float(dr[q][4 * i + 0]), fmaf(bq, xv.x, out[4 * i + 0]));
               out[4 * i + 1] = fmaf(sc, __uint_as_float(dr[q][4 * i + 1]), fmaf(bq, xv.y, out[4 * i + 1]));
@@ -445,28 +461,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
         const bool seg_end = (kc == sg.cs - 1) || (u == u_end - 1);
         if (seg_end) {
-          // Each half holds the sums of its own groups for all 16 tokens.  It keeps token quads 2*half, 2*half+1
-          // and hands the other two to its partner through shared memory.
-          float4 v0, v1;
-          if (half == 0) {
-            red[(0 * 2 + 0) * kRows + r] = make_float4(out[8], out[9], out[10], out[11]);
-            red[(0 * 2 + 1) * kRows + r] = make_float4(out[12], out[13], out[14], out[15]);
-            v0 = make_float4(out[0], out[1], out[2], out[3]);
-            v1 = make_float4(out[4], out[5], out[6], out[7]);
-          } else {
-            red[(1 * 2 + 0) * kRows + r] = make_float4(out[0], out[1], out[2], out[3]);
-            red[(1 * 2 + 1) * kRows + r] = make_float4(out[4], out[5], out[6], out[7]);
-            v0 = make_float4(out[8], out[9], out[10], out[11]);
-            v1 = make_float4(out[12], out[13], out[14], out[15]);
-          }
+          // thread (half, r) holds row r of the tile for token quads 2*half and 2*half+1: nothing to exchange
+          const float4 v0 = make_float4(out[0], out[1], out[2], out[3]), v1 = make_float4(out[4], out[5], out[6], out[7]);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) out[i] = 0.f;
-          named_bar_sync(3, kEp);
-          {
-            const float4 a = red[((half ^ 1) * 2 + 0) * kRows + r], b = red[((half ^ 1) * 2 + 1) * kRows + r];
-            v0.x += a.x; v0.y += a.y; v0.z += a.z; v0.w += a.w;
-            v1.x += b.x; v1.y += b.y; v1.z += b.z; v1.w += b.w;
-          }
+          for (int i = 0; i < 8; ++i) out[i] = 0.f;
           int total = 0, first_here = 0;
           for (int sl = lane; sl < plan.S; sl += 32) {
             const SlabGeom g2 = slab_geom(plan, sl);
@@ -485,7 +483,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             store_rows<__nv_bfloat16>(v0, y, bias, nt * kRows + r, 2 * half, M, N);
             store_rows<__nv_bfloat16>(v1, y, bias, nt * kRows + r, 2 * half + 1, M, N);
           }
-          named_bar_sync(3, kEp);
           if (npend == kMaxPend) { flush_tickets(); npend = 0; }
         }
         if (++kc == sg.cs) { kc = 0; ++nt; }

@@ -78,8 +78,9 @@ DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* sca
                       size_t workspace_bytes, void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
-/* Kernel choice for bf16 / group-64 shapes: 0 (default) or 1 = the mma.sync streaming kernel (the faster one in
- * today's measurements), 2 = the tcgen05 kernel (dequantised operand in tensor memory, accumulator in TMEM).
+/* Kernel choice for bf16 / group-64 shapes: 0 (default) = by shape: the tcgen05 kernel (dequantised operand in
+ * tensor memory, accumulator in TMEM) for N*K >= 60e6 with K <= 8192, where it is measured faster, else the
+ * mma.sync streaming kernel; 1 = mma.sync kernel always; 2 = tcgen05 kernel wherever it applies.
  * Other dtypes / group sizes always use the mma.sync kernel. */
 DFLASH_API void dflash_verify_qmm_set_impl(int impl);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */

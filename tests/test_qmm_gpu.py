@@ -133,3 +133,26 @@ def test_bad_arguments_raise(vq):
         vq.quantized_matmul(x.cuda().float(), wq.cuda(), s.cuda(), b.cuda())
     with pytest.raises(ValueError):
         vq.quantized_matmul(x.cuda(), wq.cuda()[:, :10], s.cuda(), b.cuda())
+
+
+def test_kernel_choice_by_shape(vq):
+    """Default policy: large bf16 / group-64 shapes with K <= 8192 run the tcgen05 kernel, the rest the mma.sync
+    kernel; impl 1 forces the mma.sync kernel.  Both answers are within tolerance of the oracle and of each other."""
+    from dflash_mlx_b200 import _lib
+    lib = _lib.lib()
+    K, N = 5120, 12288                            # N*K = 62.9e6
+    try:
+        lib.dflash_verify_qmm_set_impl(0)
+        e0, y0 = _run(vq, 16, K, N)
+        assert lib.dflash_verify_qmm_last_impl() == 2
+        lib.dflash_verify_qmm_set_impl(1)
+        e1, y1 = _run(vq, 16, K, N)
+        assert lib.dflash_verify_qmm_last_impl() == 1
+        assert e0 <= REL_TOL and e1 <= REL_TOL, (e0, e1)
+        assert oq.max_rel_err(y0.float(), y1.float()) <= 4e-3
+        lib.dflash_verify_qmm_set_impl(0)
+        _run(vq, 16, 16384, 8192)                 # K > 8192: many K slabs, stays on the mma.sync kernel
+        assert lib.dflash_verify_qmm_last_impl() == 1
+    finally:
+        lib.dflash_verify_qmm_set_impl(0)
+    assert lib.dflash_device_error(0) == 0
