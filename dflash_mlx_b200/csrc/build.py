@@ -10,7 +10,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libdflash_b200.so"
-SOURCES = ["runtime.cu", "qmm.cu", "qmm_tc.cu", "gdn.cu", "sdpa.cu", "glue.cu", "comm.cu"]
+SOURCES = ["runtime.cu", "qmm.cu", "qmm_tc.cu", "gdn.cu", "sdpa.cu", "glue.cu", "peer.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v"]
 
@@ -52,17 +52,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(str(obj))
     if rebuilt or not LIB.exists():
         cmd = [nvcc, "-shared", "-o", str(LIB), *objs, "-lcudart", "-Xlinker", "--no-undefined"]
-        if (CSRC / "comm.cu").exists():
-            cmd += _nccl_link_flags()
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stderr)
             raise RuntimeError("link of libdflash_b200.so failed")
     return LIB
-
-
-def _nccl_link_flags():
-    return []
 
 
 if __name__ == "__main__":

@@ -163,3 +163,115 @@ def shard_caches(cfg, caches, rank: int, world: int):
     for v in caches["v"]:
         out["v"].append(v[kv0:kv0 + lc.kv_heads].contiguous())
     return out
+
+
+class PeerReducer:
+    """Row-parallel sum + residual add + RMSNorm in ONE kernel over peer-mapped memory (NVLink), in place of an NCCL
+    all-reduce followed by the add/norm kernel.  Every rank owns an inbox and a flag array allocated by the library
+    (``cudaMalloc``), exports them through CUDA IPC and maps the other ranks' copies; the kernel pushes this rank's
+    partial block into every inbox, publishes per-row flags, waits (bounded) for the other ranks' rows and finishes
+    the residual add and the norm.  ``group`` is only used at set-up, to exchange the 64-byte IPC handles.
+
+    world == 1 works without any process group (the kernel pushes to its own inbox): that is what a single-GPU
+    test exercises."""
+
+    def __init__(self, rank: int, world: int, rows: int, hidden: int, device, group=None, _wire=None):
+        import ctypes
+
+        from . import _lib
+        self.lib = _lib.lib()
+        self._ct = ctypes
+        c = ctypes
+        vp, i32, sz = c.c_void_p, c.c_int, c.c_size_t
+        _lib.declare("dflash_peer_inbox_bytes", sz, [i32, i32, i32])
+        _lib.declare("dflash_peer_flags_bytes", sz, [i32, i32])
+        _lib.declare("dflash_peer_alloc", i32, [sz, c.POINTER(vp)])
+        _lib.declare("dflash_peer_free", i32, [vp])
+        _lib.declare("dflash_peer_export", i32, [vp, c.c_char_p])
+        _lib.declare("dflash_peer_open", i32, [c.c_char_p, c.POINTER(vp)])
+        _lib.declare("dflash_peer_close", i32, [vp])
+        _lib.declare("dflash_peer_set_wait_polls", None, [c.c_uint])
+        _lib.declare("dflash_peer_reduce_add_rmsnorm", i32,
+                     [vp, c.POINTER(vp), c.POINTER(vp), i32, i32, vp, vp, vp, vp, i32, i32, c.c_float, i32, vp])
+        self._check = _lib.check
+        self.rank, self.world, self.rows, self.hidden = rank, world, rows, hidden
+        self.dev = torch.device(device)
+        self._own, self._opened = [], []
+        with torch.cuda.device(self.dev):
+            nb_in = self.lib.dflash_peer_inbox_bytes(world, rows, hidden)
+            nb_fl = self.lib.dflash_peer_flags_bytes(world, rows)
+            if nb_in == 0 or nb_fl == 0:
+                raise ValueError("PeerReducer: world 1..8, hidden a multiple of 8")
+            if _wire is not None:        # buffers of every rank live in this process (see local_group)
+                self._inbox = (vp * world)(*_wire[0])
+                self._flags = (vp * world)(*_wire[1])
+                return
+            inbox, flags = vp(), vp()
+            self._check(self.lib.dflash_peer_alloc(nb_in, c.byref(inbox)), "dflash_peer_alloc")
+            self._own.append(inbox.value)
+            self._check(self.lib.dflash_peer_alloc(nb_fl, c.byref(flags)), "dflash_peer_alloc")
+            self._own.append(flags.value)
+            inbox_ptrs, flag_ptrs = [None] * world, [None] * world
+            inbox_ptrs[rank], flag_ptrs[rank] = inbox.value, flags.value
+            if world > 1:
+                import torch.distributed as dist
+                h_in, h_fl = c.create_string_buffer(64), c.create_string_buffer(64)
+                self._check(self.lib.dflash_peer_export(inbox, h_in), "dflash_peer_export")
+                self._check(self.lib.dflash_peer_export(flags, h_fl), "dflash_peer_export")
+                gathered = [None] * world
+                dist.all_gather_object(gathered, (rank, h_in.raw, h_fl.raw), group=group)
+                for (r, hi, hf) in gathered:
+                    if r == rank:
+                        continue
+                    pi, pf = vp(), vp()
+                    self._check(self.lib.dflash_peer_open(hi, c.byref(pi)), "dflash_peer_open")
+                    self._opened.append(pi.value)
+                    self._check(self.lib.dflash_peer_open(hf, c.byref(pf)), "dflash_peer_open")
+                    self._opened.append(pf.value)
+                    inbox_ptrs[r], flag_ptrs[r] = pi.value, pf.value
+                dist.barrier(group=group)        # every rank has mapped every buffer before the first push
+            self._inbox = (vp * world)(*inbox_ptrs)
+            self._flags = (vp * world)(*flag_ptrs)
+
+    @classmethod
+    def local_group(cls, world: int, rows: int, hidden: int, device):
+        """``world`` reducers whose inboxes all live on ONE device of this process, wired to each other by plain device
+        pointers.  Their kernels must not be launched so that one waits for another (launches of one GPU are not
+        guaranteed to run at the same time): use it with a short wait limit, for tests of the data path and of the
+        give-up path."""
+        first = cls(0, world, rows, hidden, device, _wire=([None] * world, [None] * world))
+        c, lib = first._ct, first.lib
+        inboxes, flags = [], []
+        with torch.cuda.device(first.dev):
+            for _ in range(world):
+                a, b = c.c_void_p(), c.c_void_p()
+                first._check(lib.dflash_peer_alloc(lib.dflash_peer_inbox_bytes(world, rows, hidden), c.byref(a)), "dflash_peer_alloc")
+                first._check(lib.dflash_peer_alloc(lib.dflash_peer_flags_bytes(world, rows), c.byref(b)), "dflash_peer_alloc")
+                inboxes.append(a.value)
+                flags.append(b.value)
+        group = [cls(r, world, rows, hidden, device, _wire=(inboxes, flags)) for r in range(world)]
+        group[0]._own = inboxes + flags
+        return group
+
+    def set_wait_polls(self, polls: int) -> None:
+        """Bound of the device-side wait for the other ranks' rows (a poll is roughly half a microsecond)."""
+        self.lib.dflash_peer_set_wait_polls(int(polls))
+
+    def reduce_add_rmsnorm(self, delta: torch.Tensor, h: torch.Tensor, w: torch.Tensor, x: torch.Tensor, eps: float,
+                           dtype_code: int) -> None:
+        """h += sum over ranks of delta;  x = rmsnorm(h) * w  (h is updated in place)."""
+        st = torch.cuda.current_stream(self.dev).cuda_stream
+        rc = self.lib.dflash_peer_reduce_add_rmsnorm(delta.data_ptr(), self._inbox, self._flags, self.rank, self.world,
+                                                     h.data_ptr(), w.data_ptr(), h.data_ptr(), x.data_ptr(), self.rows,
+                                                     self.hidden, eps, dtype_code, st)
+        self._check(rc, "dflash_peer_reduce_add_rmsnorm")
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (call after a barrier: no rank may still push)."""
+        with torch.cuda.device(self.dev):
+            torch.cuda.synchronize(self.dev)
+            for p in self._opened:
+                self.lib.dflash_peer_close(p)
+            for p in self._own:
+                self.lib.dflash_peer_free(p)
+        self._opened, self._own = [], []

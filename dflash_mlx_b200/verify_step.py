@@ -135,11 +135,12 @@ class HybridVerifyModel:
     """Preallocated verify-step engine.  ``tp_world`` > 1 runs one tensor-parallel shard (heads, the MLP's
     intermediate dimension and the vocabulary are split; ``all_reduce`` sums the row-parallel outputs)."""
 
-    def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None):
+    def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None, peer=None):
         _declare()
         self.cfg, self.w, self.dev = cfg, weights, torch.device(device)
         self.lib = _lib.lib()
         self.all_reduce, self.all_gather = all_reduce, all_gather
+        self.peer = peer        # parallel.PeerReducer: fused sum + residual add + norm over peer memory (else all_reduce)
         T, H, bf = cfg.block, cfg.hidden, torch.bfloat16
         dev = self.dev
         z = lambda *s, dt=bf: torch.zeros(*s, dtype=dt, device=dev)  # noqa: E731
@@ -217,6 +218,16 @@ class HybridVerifyModel:
             self.all_reduce(t)
             self.lib.dflash_pdl_plain_next(1)
 
+    def _reduce_add_rmsnorm(self, delta, w):
+        """h += sum over ranks of a row-parallel output; x = rmsnorm(h) * w."""
+        if delta is not None and self.peer is not None:
+            self.launches_per_step += 1
+            self.peer.reduce_add_rmsnorm(delta, self.h, w, self.x, self.cfg.eps, _lib.BF16)
+            return
+        if delta is not None:
+            self._reduce(delta)
+        self._add_rmsnorm(delta, w)
+
     def _add_rmsnorm(self, delta, w):
         st = self.lib.dflash_add_rmsnorm(self.h.data_ptr(), _lib.ptr(delta), w.data_ptr(), self.h.data_ptr(),
                                          self.x.data_ptr(), self.cfg.block, self.cfg.hidden, self.cfg.eps, _lib.BF16, self._st())
@@ -256,7 +267,7 @@ class HybridVerifyModel:
         ig = ia = 0
         N = self.offset + T
         for i, L in enumerate(self.w["layers"]):
-            self._add_rmsnorm(delta, L["in_norm"])
+            self._reduce_add_rmsnorm(delta, L["in_norm"])
             self._qmm(self.x, L["proj"], self.proj)
             if cfg.is_attention(i):
                 ld = L["proj"]["w"].shape[0]
@@ -298,15 +309,13 @@ class HybridVerifyModel:
                           "dflash_gated_rmsnorm")
                 self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
-            self._reduce(self.delta)
-            self._add_rmsnorm(self.delta, L["post_norm"])
+            self._reduce_add_rmsnorm(self.delta, L["post_norm"])
             self._qmm(self.x, L["gate_up"], self.gu)
             self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
                       "dflash_swiglu")
             self._qmm(self.act, L["down"], self.delta)
-            self._reduce(self.delta)
             delta = self.delta
-        self._add_rmsnorm(delta, self.w["norm"])
+        self._reduce_add_rmsnorm(delta, self.w["norm"])
         self._qmm(self.x, self.w["lm_head"], self.logits)
         v_local = self.w["lm_head"]["w"].shape[0]
         self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")

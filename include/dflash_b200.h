@@ -201,6 +201,32 @@ DFLASH_API int dflash_attn_prep(const void* proj, long long ld, int k_off, int v
 DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,
                                 int Hq, int D, int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel reduction over peer-mapped memory, fused with the residual add and RMSNorm that consume it.
+ * Generalises the reference's single collective, `mx.distributed.all_sum` after the GatedDeltaNet out_proj
+ * (dflash_mlx/runtime.py:449-450), to every row-parallel projection of the step:
+ *     h_out = h_in + sum over ranks of delta_rank ;  x = rmsnorm(h_out) * w        (one kernel, one CTA per row)
+ * Each rank owns an inbox (dflash_peer_inbox_bytes) and a flag array (dflash_peer_flags_bytes), both allocated
+ * zero-filled by dflash_peer_alloc (these two calls DO allocate device memory: cudaMalloc), exported with
+ * dflash_peer_export (a 64-byte CUDA IPC handle to hand to the other processes) and mapped there with
+ * dflash_peer_open.  inbox_ptrs[r] / flag_ptrs[r] are HOST arrays of `world` device pointers: rank r's inbox / flags
+ * as visible from this process (its own allocation for r == rank).  The kernel writes this rank's block into every
+ * inbox, publishes per-row sequence numbers, waits - at most dflash_peer_set_wait_polls() polls, then it records
+ * device error 21 and leaves the row unwritten - for the other ranks' rows and finishes add + norm.
+ * Every rank must issue the same sequence of calls.  h_out may alias h_in.  world <= 8, H % 8 == 0, H <= 16384.
+ * Plain peer loads / stores only (no multicast). */
+DFLASH_API size_t dflash_peer_inbox_bytes(int world, int T_rows, int H);
+DFLASH_API size_t dflash_peer_flags_bytes(int world, int T_rows);
+DFLASH_API int dflash_peer_alloc(size_t bytes, void** dev_ptr);
+DFLASH_API int dflash_peer_free(void* dev_ptr);
+DFLASH_API int dflash_peer_export(void* dev_ptr, unsigned char* handle64);
+DFLASH_API int dflash_peer_open(const unsigned char* handle64, void** dev_ptr);
+DFLASH_API int dflash_peer_close(void* dev_ptr);
+DFLASH_API void dflash_peer_set_wait_polls(unsigned polls);
+DFLASH_API int dflash_peer_reduce_add_rmsnorm(const void* delta, void* const* inbox_ptrs, void* const* flag_ptrs, int rank,
+                                              int world, const void* h_in, const void* w, void* h_out, void* x,
+                                              int T_rows, int H, float eps, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

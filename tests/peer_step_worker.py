@@ -1,0 +1,60 @@
+"""Worker of tests/test_peer_reduce_gpu.py::test_two_gpus_fused_step_matches_nccl_step (one process per GPU, launched
+with torchrun): a small tensor-parallel verify step with the fused peer reduction against the same step with NCCL."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    from dflash_mlx_b200 import parallel
+    from dflash_mlx_b200.verify_step import HybridConfig, HybridVerifyModel, init_weights, weights_to
+    full = HybridConfig(layers=4, hidden=1024, intermediate=2048, q_heads=4, kv_heads=2, head_dim=128, rope_dims=64,
+                        gdn_k_heads=4, gdn_v_heads=8, vocab=4096, max_context=256)
+    W = weights_to(init_weights(full, 0, "cpu"), "cpu")
+    cfg, Wl = parallel.shard_weights(full, W, rank, world)
+    Wr = weights_to(Wl, "cuda")
+    ar, ag = parallel.make_collectives(world)
+    ids = torch.arange(16, dtype=torch.int32, device="cuda") * 7 % full.vocab
+    out = {}
+    for mode in ("nccl", "peer"):
+        peer = parallel.PeerReducer(rank, world, full.block, full.hidden, "cuda") if mode == "peer" else None
+        m = HybridVerifyModel(cfg, Wr, "cuda", all_reduce=ar, all_gather=ag, peer=peer)
+        m.prefill_synthetic(64, seed=3)
+        m.arm_rollback()
+        m.verify(ids)
+        torch.cuda.synchronize()
+        eager_tokens = m.tokens.clone()
+        m._armed = True
+        m.capture()
+        m.verify_captured(ids)
+        torch.cuda.synchronize()
+        assert torch.equal(m.tokens, eager_tokens), mode
+        out[mode] = (m.tokens.clone(), m.h.clone().float())
+        dist.barrier()
+        if peer is not None:
+            peer.close()
+    rel = float((out["nccl"][1] - out["peer"][1]).abs().max() / out["nccl"][1].abs().max())
+    same = float((out["nccl"][0] == out["peer"][0]).float().mean())
+    from dflash_mlx_b200 import _lib
+    err = _lib.lib().dflash_device_error(torch.cuda.current_device())
+    ok = rel <= 3e-2 and same >= 0.8 and err == 0
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"rel={rel:.4g} same_tokens={same:.3f} device_error={err}")
+        print("PEER_STEP_OK" if int(flag) == 1 else "PEER_STEP_FAILED")
+    sys.stdout.flush()
+    dist.barrier()
+    os._exit(0 if int(flag) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
