@@ -200,7 +200,7 @@ class DenseStepWorkload:
     def __init__(self, rank, world, device, layers=None):
         import torch
         from dflash_mlx_b200.verify_step import HybridConfig, HybridVerifyModel, init_weights
-        from dflash_mlx_b200.parallel import shard_config, make_collectives
+        from dflash_mlx_b200.parallel import shard_config, make_collectives, PeerReducer
         self.torch, self.device, self.world, self.rank = torch, device, world, rank
         full = HybridConfig(max_context=self.CONTEXT + 64)
         if layers:
@@ -211,7 +211,22 @@ class DenseStepWorkload:
         with torch.cuda.device(device):
             weights = init_weights(cfg, 0xDF1D + rank, device)
         ar, ag = make_collectives(world)
-        self.model = HybridVerifyModel(cfg, weights, device, all_reduce=ar, all_gather=ag)
+        # row-parallel sums: the fused peer-memory kernel (default) or NCCL all-reduce + add/norm (DFLASH_TP_REDUCE=nccl)
+        peer, self.reduce_mode = None, "none"
+        if world > 1:
+            self.reduce_mode = os.environ.get("DFLASH_TP_REDUCE", "peer")
+            if self.reduce_mode == "peer":
+                try:
+                    peer = PeerReducer(rank, world, cfg.block, cfg.hidden, device)
+                except Exception as exc:  # CUDA IPC refused in this container: say so and use the NCCL path
+                    self.reduce_mode = "nccl (peer set-up failed: %s)" % str(exc)[:80]
+                import torch.distributed as dist
+                ok = torch.tensor([1 if peer is not None else 0], device=device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if int(ok) == 0 and peer is not None:
+                    peer = None
+                    self.reduce_mode = "nccl (peer set-up failed on another rank)"
+        self.model = HybridVerifyModel(cfg, weights, device, all_reduce=ar, all_gather=ag, peer=peer)
         self.model.prefill_synthetic(self.CONTEXT, 0xDF1D)
         gen = torch.Generator().manual_seed(0xDF1D)
         self.ids_host = torch.randint(0, full.vocab, (cfg.block,), generator=gen, dtype=torch.int32).pin_memory()
@@ -226,7 +241,7 @@ class DenseStepWorkload:
                        "block": cfg.block, "vocab": full.vocab, "gdn_dims": "Hk16/Hv32/128x128 (from config 2)",
                        "algorithmic_bytes_per_step_per_rank": self.bytes,
                        "l2": "inputs larger than L2: one step streams %.1f GB of weights" % (self.bytes["qmm"] / 1e9),
-                       "parallelism": f"tp{world}"}
+                       "parallelism": f"tp{world}", "row_parallel_reduce": self.reduce_mode}
 
     def step(self):
         self.model.verify(self.ids)
