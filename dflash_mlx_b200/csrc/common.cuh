@@ -62,6 +62,14 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 
 // ---- device helpers -----------------------------------------------------------------------
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait gives up (a fraction of a second)
+#ifndef DFLASH_SPIN_POLLS
+#define DFLASH_SPIN_POLLS 2
+#endif
+#ifndef DFLASH_SPIN_SLEEP_NS
+#define DFLASH_SPIN_SLEEP_NS 32
+#endif
+constexpr int kSpinPolls = DFLASH_SPIN_POLLS;      // failed polls before the waiting thread starts to sleep between polls
+constexpr int kSpinSleepNs = DFLASH_SPIN_SLEEP_NS;
 
 // Blocks until every kernel this one depends on has completed and its writes are visible (no-op for a plain launch).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -98,7 +106,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 2048) __nanosleep(64);
+    if (i >= (uint32_t)kSpinPolls) __nanosleep(i > 2048 ? 64 : kSpinSleepNs);
   }
   return false;
 }
