@@ -344,6 +344,118 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o,
   }
 }
 
+
+// ---- mixture of experts: routing --------------------------------------------------------------------------------
+// One CTA, one warp per token.  logits [T, E + 1] (column E is the shared expert's gate).  Per token: the top_k routed
+// experts by logit (ties to the lower index) and their softmax weights over those top_k (= softmax over all experts
+// renormalised on the chosen ones, mlx-lm / Qwen `norm_topk_prob`).  Then the experts any token chose that lie in
+// [e_lo, e_hi) are numbered in ascending id order into `slot_expert`; with `with_shared` the shared expert (id E) takes
+// the last slot with weight sigmoid(logit[t, E]).  wdense[t, slot] is token t's weight for that slot (0 if not routed).
+template <typename T>
+__global__ void __launch_bounds__(1024) moe_route_kernel(const T* __restrict__ logits, int T_rows, int E, int top_k, int e_lo,
+                                                         int e_hi, int with_shared, int n_max, int* __restrict__ slot_expert,
+                                                         int* __restrict__ n_out, float* __restrict__ wdense,
+                                                         int* __restrict__ topk_ids, float* __restrict__ topk_w) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int chosen[1024];     // expert -> 1 if some token chose it
+  __shared__ int slot_of[1024];    // expert -> slot (or -1)
+  __shared__ int warp_cnt[32];
+  __shared__ int s_ids[32][16];
+  __shared__ float s_w[32][16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) { chosen[i] = 0; slot_of[i] = -1; }
+  for (int i = threadIdx.x; i < T_rows * n_max; i += blockDim.x) wdense[i] = 0.f;
+  __syncthreads();
+  if (warp < T_rows) {
+    const T* row = logits + (size_t)warp * (E + 1);
+    constexpr int kPer = 32;  // experts per lane (E <= 1024)
+    float v[kPer];
+    const int per = (E + 31) / 32;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = (i < per && e < E) ? tof<T>(row[e]) : -INFINITY;
+    }
+    float mx0 = 0.f, den = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i)
+        if (i < per && v[i] > best) { best = v[i]; bi = lane + 32 * i; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (k == 0) mx0 = best;
+      const float w = __expf(best - mx0);
+      den += w;
+      if (lane == 0) { s_ids[warp][k] = bi; s_w[warp][k] = w; chosen[bi] = 1; }
+      if ((bi & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i)
+          if (i == (bi >> 5)) v[i] = -INFINITY;
+      }
+    }
+    if (lane == 0)
+      for (int k = 0; k < top_k; ++k) {
+        s_w[warp][k] /= den;
+        if (topk_ids != nullptr) { topk_ids[warp * top_k + k] = s_ids[warp][k]; topk_w[warp * top_k + k] = s_w[warp][k]; }
+      }
+  }
+  __syncthreads();
+  // number the chosen local experts in ascending order: thread e owns expert e (E <= blockDim.x is checked by the host)
+  const int e = threadIdx.x;
+  const int mine = (e < E && e >= e_lo && e < e_hi && chosen[e]) ? 1 : 0;
+  const unsigned bal = __ballot_sync(0xffffffffu, mine);
+  if (lane == 0) warp_cnt[warp] = __popc(bal);
+  __syncthreads();
+  int before = 0;
+  for (int w = 0; w < warp; ++w) before += warp_cnt[w];
+  int total = 0;
+  for (int w = 0; w < nwarp; ++w) total += warp_cnt[w];
+  if (mine) {
+    const int slot = before + __popc(bal & ((1u << lane) - 1u));
+    if (slot < n_max) { slot_expert[slot] = e; slot_of[e] = slot; }
+  }
+  int n = total < n_max ? total : n_max;
+  int shared_slot = -1;
+  if (with_shared && n < n_max) { shared_slot = n; ++n; }
+  if (threadIdx.x == 0) {
+    if (shared_slot >= 0) slot_expert[shared_slot] = E;
+    *n_out = n;
+  }
+  __syncthreads();
+  if (warp < T_rows) {
+    if (lane < top_k) {
+      const int sl = slot_of[s_ids[warp][lane]];
+      if (sl >= 0) wdense[warp * n_max + sl] = s_w[warp][lane];
+    }
+    if (lane == 0 && shared_slot >= 0)
+      wdense[warp * n_max + shared_slot] = sigmoidf(tof<T>(logits[(size_t)warp * (E + 1) + E]));
+  }
+}
+
+// act[t, slot * I + i] = w[t, slot] * silu(gu[t, slot * 2I + i]) * gu[t, slot * 2I + I + i]  for slot < *n  (the input of
+// the chunk-gathered down projection; rows of tokens that did not choose the expert are written as zeros)
+template <typename T>
+__global__ void __launch_bounds__(256) moe_swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ wdense,
+                                                         const int* __restrict__ n_dev, T* __restrict__ act, int T_rows, int I,
+                                                         int n_max) {
+  pdl_wait();
+  pdl_trigger();
+  const int slot = blockIdx.x, t = blockIdx.y;
+  if (slot >= *n_dev) return;
+  const float w = wdense[t * n_max + slot];
+  const T* g = gu + ((size_t)t * n_max + slot) * 2 * I;
+  T* o = act + ((size_t)t * n_max + slot) * I;
+  for (int i = threadIdx.x; i < I; i += blockDim.x)
+    o[i] = (w == 0.f) ? fromf<T>(0.f) : fromf<T>(w * tof<T>(fromf<T>(silu(tof<T>(g[i])) * tof<T>(g[I + i]))));
+}
+
 }  // namespace
 }  // namespace dflash
 
@@ -438,4 +550,27 @@ extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, v
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = (int)(((size_t)T_rows * Hq * D + 255) / 256);
   DFLASH_DISPATCH(dtype, (launch_kernel(attn_post_kernel<T>, dim3(blocks), dim3(256), 0, st, (const T*)o, (const T*)proj, ld, (T*)out, out_ld, T_rows, Hq, D)));
+}
+
+extern "C" int dflash_moe_route(const void* logits, int T_rows, int experts, int top_k, int e_lo, int e_hi, int with_shared,
+                                int n_max, int* slot_expert, int* n_active, float* wdense, int* topk_ids, float* topk_w,
+                                int dtype, void* stream) {
+  if (!logits || !slot_expert || !n_active || !wdense) return fail(DFLASH_ERR_BAD_ARG, "moe_route: null operand");
+  if (T_rows < 1 || T_rows > 32 || experts < 1 || experts > 1024 || top_k < 1 || top_k > 16 || top_k > experts || n_max < 1 ||
+      e_lo < 0 || e_hi > experts || e_lo > e_hi || (topk_ids != nullptr) != (topk_w != nullptr))
+    return fail(DFLASH_ERR_BAD_SHAPE, "moe_route: T <= 32, experts <= 1024, top_k <= 16, 0 <= e_lo <= e_hi <= experts");
+  int threads = (experts + 31) / 32 * 32;
+  if (threads < 32 * T_rows) threads = 32 * T_rows;
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (launch_kernel(moe_route_kernel<T>, dim3(1), dim3(threads), 0, st, (const T*)logits, T_rows, experts,
+                                        top_k, e_lo, e_hi, with_shared, n_max, slot_expert, n_active, wdense, topk_ids, topk_w)));
+}
+
+extern "C" int dflash_moe_swiglu(const void* gate_up, const float* wdense, const int* n_active, void* act, int T_rows, int I,
+                                 int n_max, int dtype, void* stream) {
+  if (!gate_up || !wdense || !n_active || !act || T_rows < 1 || I < 1 || n_max < 1)
+    return fail(DFLASH_ERR_BAD_ARG, "moe_swiglu: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (launch_kernel(moe_swiglu_kernel<T>, dim3(n_max, T_rows), dim3(256), 0, st, (const T*)gate_up, wdense,
+                                        n_active, (T*)act, T_rows, I, n_max)));
 }

@@ -47,6 +47,20 @@ struct QmmPlan {
   int slab_cta0[kMaxSlabs + 1];
 };
 
+// Expert-gathered variants (mixture-of-experts layers): the weights are E stacked matrices of `block_rows` rows and
+// one or more K chunks each, and only the experts listed in slot_expert[0 .. *n_dev) take part.
+//   mode 1: ROWS gathered.  y[M, slot * block_rows + r] = x[M,K] . W[slot_expert[slot]][r, :]   (fused gate|up of every
+//           active expert; row tile nt reads expert slot nt / block_tiles)
+//   mode 2: CHUNKS gathered.  y[M, r] = sum over slots of x[M, slot * Kb .. +Kb) . W[slot_expert[slot]][r, :]   (the
+//           experts' down projections, routing weights already folded into x; K chunk c reads expert slot c / cpb)
+// The number of active slots is only known on the device, so the work partition is made there (by one thread, into
+// shared memory) with the same rules as make_plan().
+struct GatherArgs {
+  const int* slot_expert;
+  const int* n_dev;
+  int mode, block_rows, block_tiles, cpb, csmax, blocks;
+};
+
 template <int G>
 struct Cfg {
   static constexpr int BK = 8 * G;
@@ -99,6 +113,27 @@ __device__ __forceinline__ int tile_pieces(const SlabGeom& g, int nt, int* first
   int b = cta_of((unsigned)(nt + 1) * g.cs - 1u, g.units, g.ctas);
   *first = a;
   return b - a + 1;
+}
+
+// make_plan() for a size known only on the device (see GatherArgs); `base` carries M and the padded strides K, N.
+__device__ void device_plan(const QmmPlan& base, const GatherArgs& ga, int n, QmmPlan* p) {
+  p->M = base.M; p->K = base.K; p->N = base.N;
+  int C;
+  if (ga.mode == 1) { p->NT = n * ga.block_tiles; C = base.slab_chunk0[base.S]; }
+  else { p->NT = base.NT; C = n * ga.cpb; }
+  p->S = (C + ga.csmax - 1) / ga.csmax;
+  for (int i = 0; i <= p->S; ++i) p->slab_chunk0[i] = (int)((long long)i * C / p->S);
+  const long long U = (long long)p->NT * C;
+  long long blocks = ga.blocks;
+  if (2 * blocks > U + 1) blocks = (U + 1) / 2;
+  if (blocks < p->S) blocks = p->S;
+  for (int i = 0; i <= p->S; ++i) p->slab_cta0[i] = 2 * (int)(blocks * p->slab_chunk0[i] / C);
+  for (int i = 1; i <= p->S; ++i)
+    if (p->slab_cta0[i] < p->slab_cta0[i - 1] + 2) p->slab_cta0[i] = p->slab_cta0[i - 1] + 2;
+  p->slab_cta0[p->S] = 2 * (int)blocks;
+  for (int i = p->S - 1; i >= 1; --i)
+    if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 2) p->slab_cta0[i] = p->slab_cta0[i + 1] - 2;
+  p->maxp = base.maxp;  // the host's bound for the largest case (sizes the workspace)
 }
 
 // Output element ownership after the cross-warp reduction: consumer thread (warp, lane) holds, for row
@@ -164,15 +199,38 @@ __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pi
   store_tile<T>(v, y, bias, nt, warp, rp, c, plan.M, plan.N);
 }
 
-template <typename T, int G>
+template <typename T, int G, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                   const __grid_constant__ CUtensorMap tmB, const T* __restrict__ x, const T* __restrict__ bias,
                   T* __restrict__ y, float4* __restrict__ pieces, unsigned* __restrict__ counters,
-                  const __grid_constant__ QmmPlan plan, int* __restrict__ err, const int dependent) {
+                  const __grid_constant__ QmmPlan base_plan, int* __restrict__ err, const int dependent,
+                  const __grid_constant__ GatherArgs ga) {
   using C = Cfg<G>;
   using TR = MmaTraits<T>;
   extern __shared__ uint8_t smem_raw[];
+  const QmmPlan* plan_ptr = &base_plan;
+  if constexpr (MODE != 0) {
+    // the partition depends on the number of active expert slots, which the routing kernel left on the device
+    __shared__ QmmPlan dyn_plan;
+    __shared__ int dyn_n;
+    pdl_wait();  // n_dev and slot_expert are written by an earlier kernel of the stream
+    if (threadIdx.x == 0) {
+      const int n = *ga.n_dev;
+      dyn_n = n;
+      if (n > 0) device_plan(base_plan, ga, n, &dyn_plan);
+    }
+    __syncthreads();
+    if (dyn_n <= 0) {  // no active expert on this rank: a chunk-gathered product is all zeros, a row-gathered one is empty
+      if (MODE == 2)
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)base_plan.M * base_plan.N;
+             i += (size_t)gridDim.x * blockDim.x)
+          y[i] = TR::from_float(0.f);
+      return;
+    }
+    plan_ptr = &dyn_plan;
+  }
+  const QmmPlan& plan = *plan_ptr;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Two independent workers share the CTA (and its activation slab): warps 0-7 are worker 0, warps 8-15
@@ -255,11 +313,18 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const uint32_t full = bar_full + 8 * pstage;
     const uint32_t dst = smem_u32(stages + pstage * C::kStageBytes);
     mbar_arrive_expect_tx(full, C::kStageBytes);
+    int wrow = pnt * kBN, wchunk = sg.c0 + pkc;  // first weight row and K chunk of the unit inside the stacked weights
+    if constexpr (MODE == 1) {
+      wrow = (ga.slot_expert[pnt / ga.block_tiles] * ga.block_tiles + pnt % ga.block_tiles) * kBN;
+    } else if constexpr (MODE == 2) {
+      wrow = ga.slot_expert[wchunk / ga.cpb] * ga.block_rows + pnt * kBN;
+      wchunk = wchunk % ga.cpb;
+    }
 #pragma unroll
     for (int j = 0; j < C::kBoxes; ++j)
-      tma_load_2d(dst + j * (kBN * 128), &tmW, (sg.c0 + pkc) * C::kWRowBytes + 128 * j, pnt * kBN, full, pol_stream);
-    tma_load_2d(dst + C::kWBytes, &tmS, (sg.c0 + pkc) * 8, pnt * kBN, full, pol_keep);
-    tma_load_2d(dst + C::kWBytes + C::kSBBytes, &tmB, (sg.c0 + pkc) * 8, pnt * kBN, full, pol_keep);
+      tma_load_2d(dst + j * (kBN * 128), &tmW, wchunk * C::kWRowBytes + 128 * j, wrow, full, pol_stream);
+    tma_load_2d(dst + C::kWBytes, &tmS, wchunk * 8, wrow, full, pol_keep);
+    tma_load_2d(dst + C::kWBytes + C::kSBBytes, &tmB, wchunk * 8, wrow, full, pol_keep);
     if (++pstage == C::kStages) { pstage = 0; ppar ^= 1; }
     if (++pkc == sg.cs) { pkc = 0; ++pnt; }
     ++pu;
@@ -612,7 +677,7 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   if (!get_map(wq, plan.N, plan.K / 2, 0, &tw) || !get_map(sc, plan.N, plan.K / G, 1, &ts) ||
       !get_map(bi, plan.N, plan.K / G, 1, &tb))
     return DFLASH_ERR_LAUNCH;
-  auto kern = qmm_stream_kernel<T, G>;
+  auto kern = qmm_stream_kernel<T, G, 0>;
   static bool attr_done[64] = {};
   if (!attr_done[device & 63]) {
     cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
@@ -625,9 +690,53 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   const int grid = plan.slab_cta0[plan.S] / 2;
   const bool dependent = pdl_enabled_for_next_launch();
   e = launch_kernel_as(dependent, kern, dim3(grid), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb, (const T*)x,
-                       (const T*)bias, (T*)y, pieces, counters, plan, device_error_word(device), dependent ? 1 : 0);
+                       (const T*)bias, (T*)y, pieces, counters, plan, device_error_word(device), dependent ? 1 : 0,
+                       GatherArgs{});
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm launch: %s", cudaGetErrorString(e));
+  return DFLASH_OK;
+}
+
+// Expert-gathered launch (see GatherArgs).  E stacked expert matrices of block_rows x Kb.
+template <typename T, int MODE>
+int launch_gather(const void* x, const void* wq, const void* sc, const void* bi, void* y, int M, int E, int block_rows,
+                  int Kb, const int* slot_expert, const int* n_dev, int n_max, void* ws, size_t ws_bytes,
+                  cudaStream_t st) {
+  constexpr int G = 64;
+  using C = Cfg<G>;
+  int device = 0;
+  cudaGetDevice(&device);
+  QmmPlan plan;
+  const int K = MODE == 1 ? Kb : n_max * Kb, N = MODE == 1 ? n_max * block_rows : block_rows;
+  if (!make_plan(M, K, N, G, device, &plan)) return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm: shape too large");
+  plan.maxp = C::kSlabKMax / C::BK + 1;  // bound for every number of active slots
+  const size_t need = plan_workspace(plan);
+  if (ws == nullptr || ws_bytes < need)
+    return fail(DFLASH_ERR_WORKSPACE, "moe_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
+  if (((uintptr_t)ws & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+  CUtensorMap tw, ts, tb;
+  if (!get_map(wq, E * block_rows, Kb / 2, 0, &tw) || !get_map(sc, E * block_rows, Kb / G, 1, &ts) ||
+      !get_map(bi, E * block_rows, Kb / G, 1, &tb))
+    return DFLASH_ERR_LAUNCH;
+  auto kern = qmm_stream_kernel<T, G, MODE>;
+  static bool attr_done[64] = {};
+  if (!attr_done[device & 63]) {
+    cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+    if (e0 != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e0));
+    attr_done[device & 63] = true;
+  }
+  GatherArgs ga;
+  ga.slot_expert = slot_expert; ga.n_dev = n_dev; ga.mode = MODE; ga.block_rows = block_rows;
+  ga.block_tiles = block_rows / kBN; ga.cpb = Kb / C::BK; ga.csmax = C::kSlabKMax / C::BK;
+  ga.blocks = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
+  unsigned* counters = (unsigned*)ws;
+  float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
+  const bool dependent = pdl_enabled_for_next_launch();
+  cudaError_t e = launch_kernel_as(dependent, kern, dim3(ga.blocks), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb,
+                                   (const T*)x, (const T*)nullptr, (T*)y, pieces, counters, plan,
+                                   device_error_word(device), dependent ? 1 : 0, ga);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "moe_qmm launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
 }
 
@@ -682,6 +791,40 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
     if (t > need) need = t;
   }
   return need;
+}
+
+extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode) {
+  if (M < 1 || M > 16 || block_rows < kBN || block_rows % kBN != 0 || Kb < 512 || Kb % 512 != 0 || n_max < 1 ||
+      (mode != 1 && mode != 2))
+    return 0;
+  int device = 0;
+  cudaGetDevice(&device);
+  QmmPlan plan;
+  const int K = mode == 1 ? Kb : n_max * Kb, N = mode == 1 ? n_max * block_rows : block_rows;
+  if (!make_plan(M, K, N, 64, device, &plan)) return 0;
+  plan.maxp = Cfg<64>::kSlabKMax / Cfg<64>::BK + 1;
+  return plan_workspace(plan);
+}
+
+extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
+                              int experts, int block_rows, int Kb, int mode, const int* slot_expert, const int* n_active,
+                              int n_max, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w_q || !scales || !biases || !y || !slot_expert || !n_active)
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm: null operand");
+  if (M < 1 || M > 16 || experts < 1 || n_max < 1 || n_max > experts || (mode != 1 && mode != 2))
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm: need 1 <= M <= 16, 1 <= n_max <= experts, mode 1 or 2");
+  if (block_rows < kBN || block_rows % kBN != 0 || Kb < 512 || Kb % 512 != 0)
+    return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm: block_rows %% 64 == 0 and Kb %% 512 == 0 (group size 64)");
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (!al(x) || !al(w_q) || !al(scales) || !al(biases)) return fail(DFLASH_ERR_MISALIGNED, "moe_qmm: operands must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DFLASH_BF16)
+    return mode == 1 ? launch_gather<__nv_bfloat16, 1>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st)
+                     : launch_gather<__nv_bfloat16, 2>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st);
+  if (dtype == DFLASH_F16)
+    return mode == 1 ? launch_gather<__half, 1>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st)
+                     : launch_gather<__half, 2>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st);
+  return fail(DFLASH_ERR_BAD_ARG, "moe_qmm: dtype %d (want bf16 or f16)", dtype);
 }
 
 extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }

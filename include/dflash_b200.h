@@ -202,6 +202,36 @@ DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, v
                                 int Hq, int D, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Mixture-of-experts block of a verify step (16 tokens, top_k of E routed experts + one shared expert).
+ * The reference has no expert code of its own: routed experts run through mlx-lm's SwitchGLU / `mx.gather_qmm`
+ * (dependency), only the shared expert reaches its verify matmul (dflash_mlx/verify_linear.py:160).  These entry
+ * points put the whole block on the same weight-streaming kernel: because every rank holds all 16 tokens, each
+ * ACTIVE expert's matrices are streamed once and applied to all 16 rows, with the routing weight (0 for tokens that
+ * did not choose the expert) folded into the activations of the down projection.
+ *
+ * dflash_moe_route: logits dtype[T, E+1] (column E = shared-expert gate).  Per token the top_k experts by logit (ties
+ *   to the lower index) with softmax weights over the chosen ones.  Experts in [e_lo, e_hi) chosen by any token are
+ *   numbered in ascending order: slot_expert[slot] = expert id; with_shared != 0 appends the shared expert (id E,
+ *   weight sigmoid(logit[t,E])).  *n_active = number of slots (<= n_max); wdense f32[T, n_max] = weight of token t for
+ *   a slot.  topk_ids int[T,top_k] / topk_w f32[T,top_k] are optional outputs (both or neither).  One thread block.
+ * dflash_moe_qmm, experts stacked as w_q uint32[experts * block_rows, Kb/8] (+ scales, biases), group size 64:
+ *   mode 1 (rows gathered):   y[M, slot*block_rows + r] = x[M,Kb] . W[slot_expert[slot]][r,:]      y: dtype[M, n_max*block_rows]
+ *   mode 2 (chunks gathered): y[M, r] = sum_slot x[M, slot*Kb .. +Kb) . W[slot_expert[slot]][r,:]  x: dtype[M, n_max*Kb]
+ *   Only slots < *n_active are read / written; the work partition is made on the device from *n_active, so nothing
+ *   synchronises the host.  block_rows % 64 == 0, Kb % 512 == 0.  Workspace as for dflash_verify_qmm
+ *   (dflash_moe_qmm_workspace_bytes, zero-filled once, may be the same buffer).
+ * dflash_moe_swiglu: act[t, slot*I + i] = w[t,slot] * silu(gu[t, slot*2I + i]) * gu[t, slot*2I + I + i], slot < *n_active. */
+DFLASH_API int dflash_moe_route(const void* logits, int T_rows, int experts, int top_k, int e_lo, int e_hi, int with_shared,
+                                int n_max, int* slot_expert, int* n_active, float* wdense, int* topk_ids, float* topk_w,
+                                int dtype, void* stream);
+DFLASH_API size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode);
+DFLASH_API int dflash_moe_qmm(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
+                              int experts, int block_rows, int Kb, int mode, const int* slot_expert, const int* n_active,
+                              int n_max, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+DFLASH_API int dflash_moe_swiglu(const void* gate_up, const float* wdense, const int* n_active, void* act, int T_rows, int I,
+                                 int n_max, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Tensor-parallel reduction over peer-mapped memory, fused with the residual add and RMSNorm that consume it.
  * Generalises the reference's single collective, `mx.distributed.all_sum` after the GatedDeltaNet out_proj
  * (dflash_mlx/runtime.py:449-450), to every row-parallel projection of the step:
