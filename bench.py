@@ -196,17 +196,21 @@ class DenseStepWorkload:
     name = "dense_step_cfg4"
     metric, unit, higher_is_better, scaling, dtype = "m16_int4_verify_step_latency", "us", False, "strong", "bf16"
     CONTEXT = 4096
+    MOE = False
 
     def __init__(self, rank, world, device, layers=None):
         import torch
         from dflash_mlx_b200.verify_step import HybridConfig, HybridVerifyModel, init_weights
         from dflash_mlx_b200.parallel import shard_config, make_collectives, PeerReducer
         self.torch, self.device, self.world, self.rank = torch, device, world, rank
-        full = HybridConfig(max_context=self.CONTEXT + 64)
+        full = HybridConfig.moe_cfg5(max_context=self.CONTEXT + 64) if self.MOE else HybridConfig(max_context=self.CONTEXT + 64)
         if layers:
             full.layers = layers
         self.full_cfg = full
         cfg = shard_config(full, world)
+        if self.MOE and world > 1:      # expert parallel: a contiguous range of experts per rank, shared expert on rank 0
+            per = full.moe_experts // world
+            cfg.moe_e_lo, cfg.moe_e_hi, cfg.moe_shared_here = rank * per, (rank + 1) * per, rank == 0
         self.cfg = cfg
         with torch.cuda.device(device):
             weights = init_weights(cfg, 0xDF1D + rank, device)
@@ -239,6 +243,8 @@ class DenseStepWorkload:
         self.n_qmm = len(self.model.qmm_launch_list())
         self.config = {"workload": self.name, "layers": cfg.layers, "hidden": cfg.hidden, "context": self.CONTEXT,
                        "block": cfg.block, "vocab": full.vocab, "gdn_dims": "Hk16/Hv32/128x128 (from config 2)",
+                       "experts": ("%d top-%d + shared, inter %d, experts %d..%d on this rank" % (
+                           full.moe_experts, full.moe_top_k, full.moe_inter, *cfg.moe_local)) if self.MOE else "none",
                        "algorithmic_bytes_per_step_per_rank": self.bytes,
                        "l2": "inputs larger than L2: one step streams %.1f GB of weights" % (self.bytes["qmm"] / 1e9),
                        "parallelism": f"tp{world}", "row_parallel_reduce": self.reduce_mode}
@@ -278,6 +284,39 @@ class DenseStepWorkload:
 
     def cpu_baseline(self, budget_s=25.0):
         return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s)
+
+
+class MoeStepWorkload(DenseStepWorkload):
+    """Configuration 5 of BASELINE.json: one verify step of the 40-layer mixture-of-experts hybrid model (256 experts,
+    top-8, one shared expert of intermediate 512, hidden 2048; attention 16 q / 2 KV heads of 256 and GatedDeltaNet
+    16 / 32 heads of 128 from configurations 3 and 2) at context 8192.  N > 1: attention / GatedDeltaNet heads tensor
+    parallel, experts expert-parallel (256 / N per rank, shared expert on rank 0); every rank holds all 16 tokens, so
+    there is no dispatch - the ranks' partial block outputs are summed by the same fused peer-memory reduction."""
+    name = "moe_step_cfg5"
+    CONTEXT = 8192
+    MOE = True
+
+    def aux_step(self):
+        self.model.run_experts_only()
+
+    def roofline(self, ms_per_step, aux_ms, peak, peak_src):
+        """Dominant kernels = the two expert-gathered matmuls of every layer (replayed alone, with the routing kernels,
+        as a second CUDA graph); algorithmic bytes = matrices of the experts some token chose."""
+        n = 2 * self.cfg.layers
+        per_launch = self.bytes["experts"] / n
+        us_per_launch = aux_ms * 1e3 / n
+        achieved = per_launch / us_per_launch / 1e3
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": peak_src,
+                "kernel": "expert-gathered qmm_stream_kernel (rows gathered: gate|up; K chunks gathered: down), timed with "
+                          "their routing and SwiGLU kernels",
+                "launches_per_step": n, "algorithmic_bytes_per_launch": per_launch, "us_per_launch": us_per_launch,
+                "matmul_share_of_step": aux_ms / ms_per_step,
+                "whole_step_gbps": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9}
+
+    def cpu_baseline(self, budget_s=25.0):
+        slots = int(round(self.bytes.get("active_expert_slots_per_layer", 0) * self.cfg.layers))
+        return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s, expert_slots=slots)
 
 
 class ReplayWorkload:
@@ -436,7 +475,7 @@ class SdpaWorkload:
                 "sample": "dense-softmax torch restatement, best of 3; MLX unavailable on this box"}
 
 
-def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
+def dense_step_cpu_baseline(cfg, context, budget_s=25.0, expert_slots=0):
     """CPU path of one dense verify step on all host cores, from a bounded sample: every distinct linear shape
     is timed with the C restatement of the stock qmm (oracle/qmm_ref.c), the GDN recurrence and the attention
     with the torch oracle on one layer each; the step time is sum(count x time).  Element-wise glue is left out
@@ -455,18 +494,26 @@ def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
     n_attn = sum(cfg.is_attention(i) for i in range(cfg.layers))
     n_gdn = cfg.layers - n_attn
     H, I, G, T = cfg.hidden, cfg.intermediate, cfg.group_size, cfg.block
-    shapes = [("gdn_proj", cfg.gdn_proj_n, H, n_gdn), ("gdn_out", H, cfg.gdn_v_heads * cfg.gdn_dv, n_gdn),
-              ("attn_proj", cfg.attn_proj_n, H, n_attn), ("attn_o", H, cfg.q_heads * cfg.head_dim, n_attn),
-              ("gate_up", 2 * I, H, cfg.layers), ("down", H, I, cfg.layers), ("lm_head", cfg.vocab, H, 1)]
+    shapes = [("gdn_proj", cfg.gdn_proj_n, H, n_gdn, T), ("gdn_out", H, cfg.gdn_v_heads * cfg.gdn_dv, n_gdn, T),
+              ("attn_proj", cfg.attn_proj_n, H, n_attn, T), ("attn_o", H, cfg.q_heads * cfg.head_dim, n_attn, T),
+              ("lm_head", cfg.vocab, H, 1, T)]
+    if cfg.moe_experts > 0:
+        # routed experts see only the tokens that chose them (top_k * T / distinct experts, about 1.25 rows): timed with
+        # 2 rows; expert_slots = active (expert, layer) pairs of the measured step, shared expert included
+        slots = expert_slots if expert_slots else cfg.layers * min(T * cfg.moe_top_k, cfg.moe_experts)
+        shapes += [("router", cfg.moe_experts + 1, H, cfg.layers, T), ("expert_gate_up", 2 * cfg.moe_inter, H, slots, 2),
+                   ("expert_down", H, cfg.moe_inter, slots, 2)]
+    else:
+        shapes += [("gate_up", 2 * I, H, cfg.layers, T), ("down", H, I, cfg.layers, T)]
     total, parts = 0.0, {}
     reps = 3 if budget_s >= 20 else 2
-    for name, n, k, count in shapes:
+    for name, n, k, count, rows in shapes:
         if count == 0:
             continue
         wq, s, b = oq.random_quantized(n, k, seed=7, group_size=G)
-        x = torch.randn(T, k).bfloat16()
-        y = torch.empty(T, n, dtype=torch.float32)
-        args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), T, k, n, G)
+        x = torch.randn(rows, k).bfloat16()
+        y = torch.empty(rows, n, dtype=torch.float32)
+        args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), rows, k, n, G)
         lib.qmm_ref(*args)
         ts = []
         for _ in range(reps):
@@ -486,13 +533,14 @@ def dense_step_cpu_baseline(cfg, context, budget_s=25.0):
     parts["attention"] = time.perf_counter() - t0
     total += n_attn * parts["attention"]
     return {"value": total * 1e6, "unit": "us", "cores": int(lib.qmm_ref_threads()), "kind": "port",
-            "sample": "sum over the step of count x time of each distinct op (7 linear shapes with the C qmm, best of "
+            "sample": "sum over the step of count x time of each distinct op (every linear shape with the C qmm, best of "
                       f"{reps}; one GDN recurrence and one attention with the torch oracle); {note}; MLX unavailable on "
                       "this box: CPU baseline = restatement of the stock path",
             "parts_ms": {k2: round(v2 * 1e3, 3) for k2, v2 in parts.items()}}
 
 
-WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload, "gdn_replay_cfg2": ReplayWorkload,
+WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload, "moe_step_cfg5": MoeStepWorkload,
+             "gdn_replay_cfg2": ReplayWorkload,
              "verify_sdpa_cfg3": SdpaWorkload}
 DEFAULT_WORKLOAD = "dense_step_cfg4"
 

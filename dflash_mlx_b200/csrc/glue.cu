@@ -349,8 +349,9 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o,
 // One CTA, one warp per token.  logits [T, E + 1] (column E is the shared expert's gate).  Per token: the top_k routed
 // experts by logit (ties to the lower index) and their softmax weights over those top_k (= softmax over all experts
 // renormalised on the chosen ones, mlx-lm / Qwen `norm_topk_prob`).  Then the experts any token chose that lie in
-// [e_lo, e_hi) are numbered in ascending id order into `slot_expert`; with `with_shared` the shared expert (id E) takes
-// the last slot with weight sigmoid(logit[t, E]).  wdense[t, slot] is token t's weight for that slot (0 if not routed).
+// [e_lo, e_hi) are numbered in ascending id order into `slot_expert` as indices into this rank's expert stack
+// (e - e_lo); with `with_shared` the shared expert (stack index e_hi - e_lo) takes the last slot with weight
+// sigmoid(logit[t, E]).  wdense[t, slot] is token t's weight for that slot (0 if not routed).
 template <typename T>
 __global__ void __launch_bounds__(1024) moe_route_kernel(const T* __restrict__ logits, int T_rows, int E, int top_k, int e_lo,
                                                          int e_hi, int with_shared, int n_max, int* __restrict__ slot_expert,
@@ -419,13 +420,13 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const T* __restrict__ l
   for (int w = 0; w < nwarp; ++w) total += warp_cnt[w];
   if (mine) {
     const int slot = before + __popc(bal & ((1u << lane) - 1u));
-    if (slot < n_max) { slot_expert[slot] = e; slot_of[e] = slot; }
+    if (slot < n_max) { slot_expert[slot] = e - e_lo; slot_of[e] = slot; }  // index inside this rank's stack
   }
   int n = total < n_max ? total : n_max;
   int shared_slot = -1;
   if (with_shared && n < n_max) { shared_slot = n; ++n; }
   if (threadIdx.x == 0) {
-    if (shared_slot >= 0) slot_expert[shared_slot] = E;
+    if (shared_slot >= 0) slot_expert[shared_slot] = e_hi - e_lo;  // the shared expert follows the rank's experts
     *n_out = n;
   }
   __syncthreads();

@@ -35,10 +35,24 @@ def _declare():
     _declared = True
 
 
+def slice_experts(gate_up: dict, down: dict, experts: int, inter: int, hidden: int, e_lo: int, e_hi: int,
+                  with_shared: bool):
+    """The stack a rank holds: experts e_lo..e_hi-1 (+ the shared expert, stored at index ``experts`` of the full
+    stack) of full gate_up / down stacks."""
+    def cut(d, rows_per):
+        parts = {k: [v[e_lo * rows_per: e_hi * rows_per]] for k, v in d.items()}
+        if with_shared:
+            for k, v in d.items():
+                parts[k].append(v[experts * rows_per: (experts + 1) * rows_per])
+        return {k: torch.cat(v, dim=0).contiguous() for k, v in parts.items()}
+    return cut(gate_up, 2 * inter), cut(down, hidden)
+
+
 class MoEBlock:
     """Buffers and launch sequence of one MoE block shape.  ``gate_up`` / ``down`` are dicts ``{"w","s","b"}`` holding
     the experts stacked along the rows: expert e occupies rows ``[e*2I, (e+1)*2I)`` of gate_up (gate rows first, then
-    up) and rows ``[e*H, (e+1)*H)`` of down; index ``experts`` is the shared expert."""
+    up) and rows ``[e*H, (e+1)*H)`` of down.  A rank holds only ITS stack: experts ``e_lo .. e_hi-1`` followed by the
+    shared expert if it owns it (``slice_experts`` cuts that out of a full stack)."""
 
     def __init__(self, rows: int, hidden: int, inter: int, experts: int, top_k: int, device, *, e_lo: int = 0,
                  e_hi: int | None = None, with_shared: bool = True, dtype=torch.bfloat16, workspace: torch.Tensor = None):

@@ -67,6 +67,12 @@ class HybridConfig:
     group_size: int = 64
     eps: float = 1e-6
     block: int = 16                    # tokens per verify step
+    moe_experts: int = 0               # > 0: the MLP of every layer is a mixture of experts (+ one shared expert)
+    moe_top_k: int = 8
+    moe_inter: int = 512               # intermediate size of one expert
+    moe_e_lo: int = 0                  # expert-parallel shard: this rank holds experts [moe_e_lo, moe_e_hi)
+    moe_e_hi: int = 0                  # (0 = all) and the shared expert if moe_shared_here
+    moe_shared_here: bool = True
     max_context: int = 4096 + 64
 
     def is_attention(self, i: int) -> bool:
@@ -79,6 +85,20 @@ class HybridConfig:
     @property
     def gdn_proj_n(self) -> int:        # qkv | z | b | a
         return self.conv_dim + self.gdn_v_heads * self.gdn_dv + 2 * self.gdn_v_heads
+
+    @classmethod
+    def moe_cfg5(cls, **kw):
+        """The benchmark's 5th configuration: 40 layers (3 GDN : 1 attention), hidden 2048, 256 experts top-8 + one
+        shared expert of intermediate 512; attention / GDN dimensions from its 3rd / 2nd configurations."""
+        base = dict(layers=40, hidden=2048, intermediate=512, q_heads=16, kv_heads=2, head_dim=256, moe_experts=256,
+                    moe_top_k=8, moe_inter=512, max_context=8192 + 64)
+        base.update(kw)
+        return cls(**base)
+
+    @property
+    def moe_local(self):
+        """(e_lo, e_hi) of this rank's routed experts."""
+        return self.moe_e_lo, (self.moe_e_hi if self.moe_e_hi > 0 else self.moe_experts)
 
     @property
     def attn_proj_n(self) -> int:       # (query | gate) per head | k | v
@@ -101,8 +121,17 @@ def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
     H, I, G = cfg.hidden, cfg.intermediate, cfg.group_size
     layers: List[Dict] = []
     for i in range(cfg.layers):
-        L: Dict = {"in_norm": (1.0 + 0.1 * rn(H)).to(bf), "post_norm": (1.0 + 0.1 * rn(H)).to(bf),
-                   "gate_up": _rand_quantized(2 * I, H, gen, device, G), "down": _rand_quantized(H, I, gen, device, G)}
+        L: Dict = {"in_norm": (1.0 + 0.1 * rn(H)).to(bf), "post_norm": (1.0 + 0.1 * rn(H)).to(bf)}
+        if cfg.moe_experts > 0:
+            # router (+ shared-expert gate as its last row) and this rank's stack of experts (+ the shared one)
+            lo, hi = cfg.moe_local
+            n_local = hi - lo + (1 if cfg.moe_shared_here else 0)
+            L["router"] = _rand_quantized(cfg.moe_experts + 1, H, gen, device, G, w_std=0.05)
+            L["experts_gate_up"] = _rand_quantized(n_local * 2 * cfg.moe_inter, H, gen, device, G)
+            L["experts_down"] = _rand_quantized(n_local * H, cfg.moe_inter, gen, device, G)
+        else:
+            L["gate_up"] = _rand_quantized(2 * I, H, gen, device, G)
+            L["down"] = _rand_quantized(H, I, gen, device, G)
         if cfg.is_attention(i):
             L["proj"] = _rand_quantized(cfg.attn_proj_n, H, gen, device, G)
             L["q_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
@@ -184,6 +213,18 @@ class HybridVerifyModel:
                                                                                     L[name]["w"].shape[0], cfg.group_size))
             need = max(need, self.lib.dflash_verify_qmm_workspace_bytes(T, H, weights["lm_head"]["w"].shape[0], cfg.group_size))
             self.qmm_ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+            self.moe = None
+            self._moe_counts = None        # a list while moe_active_slots() records the active experts per layer
+            if cfg.moe_experts > 0:
+                from .moe import MoEBlock
+                lo, hi = cfg.moe_local
+                need = max(need, self.lib.dflash_verify_qmm_workspace_bytes(T, H, cfg.moe_experts + 1, cfg.group_size))
+                self.moe = MoEBlock(T, H, cfg.moe_inter, cfg.moe_experts, cfg.moe_top_k, dev, e_lo=lo, e_hi=hi,
+                                    with_shared=cfg.moe_shared_here)
+                need = max(need, self.moe.workspace_bytes())
+                self.qmm_ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+                self.moe.ws = self.qmm_ws            # one zero-filled workspace serves every matmul of the stream
+                self.router_logits = z(cfg.layers, T, cfg.moe_experts + 1)   # kept per layer (routing can be replayed)
             sdpa_need = self.lib.dflash_verify_sdpa_workspace_bytes(1, cfg.q_heads, cfg.kv_heads, cfg.max_context,
                                                                     cfg.head_dim, 0)
             self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
@@ -259,6 +300,7 @@ class HybridVerifyModel:
         if self.offset + T > cfg.max_context:
             raise ValueError("KV cache capacity exceeded")
         self.launches_per_step = 0
+        self._last_ids = ids
         st, BF = self._st(), _lib.BF16
         cur, nxt = self.cur, self.cur ^ 1
         self._chk(lib.dflash_embed(ids.data_ptr(), self.w["embed"].data_ptr(), self.h.data_ptr(), T, cfg.hidden,
@@ -310,10 +352,18 @@ class HybridVerifyModel:
                 self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
             self._reduce_add_rmsnorm(self.delta, L["post_norm"])
-            self._qmm(self.x, L["gate_up"], self.gu)
-            self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
-                      "dflash_swiglu")
-            self._qmm(self.act, L["down"], self.delta)
+            if self.moe is not None:
+                # router -> top-k -> gate|up of the active experts -> weighted SwiGLU -> down summed over the experts
+                self._qmm(self.x, L["router"], self.router_logits[i])
+                self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
+                self.launches_per_step += self.moe.launches
+                if self._moe_counts is not None:
+                    self._moe_counts.append(self.moe.n_active.clone())
+            else:
+                self._qmm(self.x, L["gate_up"], self.gu)
+                self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
+                          "dflash_swiglu")
+                self._qmm(self.act, L["down"], self.delta)
             delta = self.delta
         self._reduce_add_rmsnorm(delta, self.w["norm"])
         self._qmm(self.x, self.w["lm_head"], self.logits)
@@ -362,10 +412,18 @@ class HybridVerifyModel:
         for i, L in enumerate(self.w["layers"]):
             out.append((self.x, L["proj"], self.proj))
             out.append((self.mix_attn, L["o_proj"], self.delta) if self.cfg.is_attention(i) else (self.mix_gdn, L["out_proj"], self.delta))
-            out.append((self.x, L["gate_up"], self.gu))
-            out.append((self.act, L["down"], self.delta))
+            if self.moe is not None:
+                out.append((self.x, L["router"], self.router_logits[i]))   # the expert matmuls are not in this list
+            else:
+                out.append((self.x, L["gate_up"], self.gu))
+                out.append((self.act, L["down"], self.delta))
         out.append((self.x, self.w["lm_head"], self.logits))
         return out
+
+    def run_experts_only(self):
+        """The expert blocks of every layer alone, with the routing of the last verify pass (timing aid)."""
+        for i, L in enumerate(self.w["layers"]):
+            self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
 
     def run_qmm_only(self):
         for x, W, o in self.qmm_launch_list():
@@ -382,7 +440,29 @@ class HybridVerifyModel:
         kv = len(self.attn_layers) * (2 * cfg.kv_heads * N * cfg.head_dim * 2 + 2 * cfg.q_heads * T * cfg.head_dim * 2)
         st = len(self.gdn_layers) * (2 * cfg.gdn_v_heads * cfg.gdn_dv * cfg.gdn_dk * 4
                                      + T * (cfg.gdn_v_heads * cfg.gdn_dv * (4 + 2 + 2) + 2 * cfg.gdn_k_heads * cfg.gdn_dk * 2))
-        return {"qmm": qmm, "kv": kv, "gdn": st, "total": qmm + kv + st}
+        out = {"qmm": qmm, "kv": kv, "gdn": st}
+        if self.moe is not None:
+            # only the experts some token chose are streamed: counted from one recorded pass
+            slots = self.moe_active_slots()
+            per_expert = 3 * cfg.moe_inter * cfg.hidden          # gate, up and down matrices
+            out["experts"] = int(sum(slots) * (per_expert // 2 + 2 * (per_expert // G) * 2))
+            out["active_expert_slots_per_layer"] = float(sum(slots)) / max(len(slots), 1)
+        out["total"] = sum(v for k, v in out.items() if k in ("qmm", "kv", "gdn", "experts"))
+        return out
+
+    def moe_active_slots(self):
+        """Active expert slots (routed experts chosen by some token, + the shared expert) of every layer for the ids of
+        the last verify pass, from one extra eager pass (synchronises)."""
+        self._moe_counts = []
+        armed, ids = self._armed, getattr(self, "_last_ids", None)
+        if ids is None:
+            ids = torch.zeros(self.cfg.block, dtype=torch.int32, device=self.dev)
+        self.verify(ids)
+        torch.cuda.synchronize(self.dev)
+        counts = [int(c) for c in self._moe_counts]
+        self._moe_counts = None
+        self._armed = armed
+        return counts
 
     # ---- acceptance and rollback (runtime.py:101-108, 878-907; recurrent_rollback_cache.py:148-171) -------
     @staticmethod

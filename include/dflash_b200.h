@@ -211,8 +211,9 @@ DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, v
  *
  * dflash_moe_route: logits dtype[T, E+1] (column E = shared-expert gate).  Per token the top_k experts by logit (ties
  *   to the lower index) with softmax weights over the chosen ones.  Experts in [e_lo, e_hi) chosen by any token are
- *   numbered in ascending order: slot_expert[slot] = expert id; with_shared != 0 appends the shared expert (id E,
- *   weight sigmoid(logit[t,E])).  *n_active = number of slots (<= n_max); wdense f32[T, n_max] = weight of token t for
+ *   numbered in ascending order: slot_expert[slot] = expert id - e_lo, i.e. the index inside the calling rank's stack
+ *   of expert matrices; with_shared != 0 appends the shared expert (stack index e_hi - e_lo, weight
+ *   sigmoid(logit[t,E])).  *n_active = number of slots (<= n_max); wdense f32[T, n_max] = weight of token t for
  *   a slot.  topk_ids int[T,top_k] / topk_w f32[T,top_k] are optional outputs (both or neither).  One thread block.
  * dflash_moe_qmm, experts stacked as w_q uint32[experts * block_rows, Kb/8] (+ scales, biases), group size 64:
  *   mode 1 (rows gathered):   y[M, slot*block_rows + r] = x[M,Kb] . W[slot_expert[slot]][r,:]      y: dtype[M, n_max*block_rows]

@@ -18,6 +18,7 @@ import math
 import torch
 
 from . import gdn as og
+from . import moe as omoe
 from . import qmm as oq
 from . import sdpa as osd
 
@@ -107,6 +108,24 @@ def attn_layer(cfg, L, x, kcache, vcache, offset):
     return _lin(gated, L["o_proj"], cfg.group_size)
 
 
+def _embed_local_stack(cfg, L):
+    """A rank's expert stack (experts e_lo..e_hi-1, then the shared expert if it is here) placed at the global row
+    positions oracle/moe.py indexes by."""
+    lo, hi = cfg.moe_local
+    E, I, H = cfg.moe_experts, cfg.moe_inter, cfg.hidden
+    out = []
+    for name, rows in (("experts_gate_up", 2 * I), ("experts_down", H)):
+        d = {}
+        for k, v in L[name].items():
+            full = torch.zeros((E + 1) * rows, v.shape[1], dtype=v.dtype)
+            full[lo * rows: hi * rows] = v[: (hi - lo) * rows]
+            if cfg.moe_shared_here:
+                full[E * rows: (E + 1) * rows] = v[(hi - lo) * rows: (hi - lo + 1) * rows]
+            d[k] = full
+        out.append(d)
+    return out
+
+
 def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None):
     """caches: {"conv": [Lg][keep,cd] bf16, "state": [Lg][Hv,Dv,Dk] f32, "k"/"v": [La][Hk,cap,D] bf16}.
     Returns (logits bf16 [T,V], greedy tokens, new_caches, tapes) without touching the input GDN caches.
@@ -131,10 +150,22 @@ def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None
             out = reduce(out)
         h = (h.float() + out.float()).to(BF)
         x = _rms(h, L["post_norm"], cfg.eps)
-        gu = _lin(x, L["gate_up"], cfg.group_size)
-        I = gu.shape[1] // 2
-        act = (torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()).to(BF)
-        mlp = _lin(act, L["down"], cfg.group_size)
+        if "router" in L:
+            # mixture of experts (mlx-lm switch layers + shared expert): the rank's experts are stacked locally
+            logits = _lin(x, L["router"], cfg.group_size)
+            lo, hi = cfg.moe_local
+            E = cfg.moe_experts
+            if lo == 0 and hi == E and cfg.moe_shared_here:
+                gu_s, dn_s = L["experts_gate_up"], L["experts_down"]
+            else:  # re-embed the local stack at its global position (rows of experts this rank lacks stay zero)
+                gu_s, dn_s = _embed_local_stack(cfg, L)
+            mlp = omoe.moe_ref(x, logits, gu_s, dn_s, cfg.moe_top_k, inter=cfg.moe_inter, group_size=cfg.group_size,
+                               e_lo=lo, e_hi=hi, with_shared=cfg.moe_shared_here)
+        else:
+            gu = _lin(x, L["gate_up"], cfg.group_size)
+            I = gu.shape[1] // 2
+            act = (torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()).to(BF)
+            mlp = _lin(act, L["down"], cfg.group_size)
         if reduce is not None:
             mlp = reduce(mlp)
         h = (h.float() + mlp.float()).to(BF)

@@ -26,6 +26,8 @@ def _run(mod, x, logits, gu, dn, top_k, inter, E, **kw):
     _lib, moe = mod
     T, H = x.shape
     blk = moe.MoEBlock(T, H, inter, E, top_k, "cuda", **kw)
+    if kw:                                          # a rank holds only its own experts (+ the shared one if it owns it)
+        gu, dn = moe.slice_experts(gu, dn, E, inter, H, kw["e_lo"], kw["e_hi"], kw["with_shared"])
     out = torch.full((T, H), 7.0, dtype=torch.bfloat16, device="cuda")
     blk(x.cuda(), logits.cuda(), _cuda(gu), _cuda(dn), out)
     torch.cuda.synchronize()

@@ -26,6 +26,34 @@ def small_case(seed=5, context=64):
     return cfg, W, caches, ids, context
 
 
+SMALL_MOE = dict(SMALL, intermediate=512, moe_experts=16, moe_top_k=2, moe_inter=512)
+
+
+def small_moe_case(seed=11, context=64):
+    """The small hybrid model with a mixture-of-experts MLP (16 experts, top-2, one shared expert) in every layer."""
+    cfg0, W0, caches, ids, ctx = small_case(seed, context)
+    cfg = HybridConfig(**SMALL_MOE)
+    return cfg, init_weights(cfg, seed, "cpu"), caches, ids, ctx
+
+
+def test_moe_step_oracle_runs_and_expert_parallel_parts_add_up():
+    import copy
+    cfg, W, caches, ids, ctx = small_moe_case()
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    logits, toks, _, _ = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
+    assert logits.shape == (16, cfg.vocab) and torch.isfinite(logits.float()).all()
+    # one layer's MoE output equals the sum of two expert-parallel halves (the first owns the shared expert)
+    from oracle import moe as omoe
+    L = W["layers"][0]
+    x = torch.randn(16, cfg.hidden, generator=torch.Generator().manual_seed(3)).bfloat16()
+    lg = torch.randn(16, cfg.moe_experts + 1, generator=torch.Generator().manual_seed(4)).bfloat16()
+    whole = omoe.moe_ref(x, lg, L["experts_gate_up"], L["experts_down"], 2, inter=512)
+    a = omoe.moe_ref(x, lg, L["experts_gate_up"], L["experts_down"], 2, inter=512, e_lo=0, e_hi=8, with_shared=True)
+    b = omoe.moe_ref(x, lg, L["experts_gate_up"], L["experts_down"], 2, inter=512, e_lo=8, e_hi=16, with_shared=False)
+    err = float((whole.float() - a.float() - b.float()).abs().max() / whole.float().abs().max())
+    assert err <= 1e-2
+
+
 def test_rollback_equals_processing_only_the_accepted_tokens():
     cfg, W, caches, ids, ctx = small_case()
     clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731

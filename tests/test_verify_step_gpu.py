@@ -95,3 +95,48 @@ def test_device_side_accept_length_and_full_accept(setup):
     fwd = m.state[m.cur ^ 1].clone()
     m.rollback(15, drafted_tokens=15)
     assert torch.equal(m.state[m.cur], fwd) and m.offset == ctx + 16
+
+
+def test_moe_step_matches_oracle():
+    """The same step with a mixture-of-experts MLP in every layer (16 experts, top-2, shared expert): logits within
+    tolerance, and the captured graph (routing sizes read on the device) reproduces the eager result."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import HybridVerifyModel, weights_to
+    from dflash_mlx_b200 import _lib
+    from tests.test_verify_step import small_moe_case
+    cfg, W, caches, ids, ctx = small_moe_case()
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    ref_logits, ref_toks, _, _ = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
+    m = HybridVerifyModel(cfg, weights_to(W, "cuda"), "cuda")
+
+    def restore():
+        for l in range(len(caches["state"])):
+            m.state[0][l].copy_(caches["state"][l]); m.state[1][l].copy_(caches["state"][l])
+            m.conv[0][l].copy_(caches["conv"][l]); m.conv[1][l].copy_(caches["conv"][l])
+        for l in range(len(caches["k"])):
+            m.kcache[l].copy_(caches["k"][l]); m.vcache[l].copy_(caches["v"][l])
+        m.cur, m.offset, m._armed = 0, ctx, False
+
+    restore()
+    m.arm_rollback()
+    logits = m.verify(ids.cuda()).clone()
+    torch.cuda.synchronize()
+    assert _rel(logits, ref_logits) <= 5e-2           # a token whose 2nd/3rd router logits nearly tie may pick another expert
+    slots = m.moe_active_slots()
+    assert len(slots) == cfg.layers and all(2 <= s <= 17 for s in slots)
+    restore()
+    m.arm_rollback()
+    eager = m.verify(ids.cuda()).clone()
+    toks = m.tokens.clone()
+    restore()
+    m._armed = True
+    m.capture()
+    restore()
+    m._armed = True
+    m.verify_captured(ids.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(m.tokens, toks)
+    assert torch.equal(m.logits.view(-1)[: eager.numel()].view_as(eager), eager)
+    assert "experts" in m.algorithmic_bytes()
+    assert _lib.lib().dflash_device_error(0) == 0
