@@ -97,10 +97,17 @@ def shard_weights(cfg, W, rank: int, world: int):
     if world == 1:
         return lc, W
     G, dev = cfg.group_size, W["norm"].device
-    if cfg.intermediate % world != 0 or (cfg.intermediate // world) % (8 * G) != 0:
+    moe = getattr(cfg, "moe_experts", 0) > 0
+    if not moe and (cfg.intermediate % world != 0 or (cfg.intermediate // world) % (8 * G) != 0):
         raise ValueError("shard_weights needs intermediate/world to be a multiple of 8 groups")
     I, Il = cfg.intermediate, cfg.intermediate // world
     lc.intermediate = Il
+    if moe:
+        # expert parallel: a contiguous range of routed experts per rank, the shared expert on rank 0, router replicated
+        if cfg.moe_experts % world != 0:
+            raise ValueError("shard_weights needs the number of experts to be divisible by the ranks")
+        per = cfg.moe_experts // world
+        lc.moe_e_lo, lc.moe_e_hi, lc.moe_shared_here = rank * per, (rank + 1) * per, rank == 0
     D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
     hq0, hq1 = rank * lc.q_heads, (rank + 1) * lc.q_heads
     kv0 = (rank * Hkv) // world if Hkv >= world else hq0 // (Hq // Hkv)
@@ -110,9 +117,15 @@ def shard_weights(cfg, W, rank: int, world: int):
     gv0, gv1 = rank * lc.gdn_v_heads, (rank + 1) * lc.gdn_v_heads
     layers = []
     for i, L in enumerate(W["layers"]):
-        gu_idx = torch.cat([_arange(rank * Il, (rank + 1) * Il, dev), _arange(I + rank * Il, I + (rank + 1) * Il, dev)])
-        o = {"in_norm": L["in_norm"], "post_norm": L["post_norm"], "gate_up": _rows(L["gate_up"], gu_idx),
-             "down": _cols(L["down"], rank * Il, (rank + 1) * Il, G)}
+        o = {"in_norm": L["in_norm"], "post_norm": L["post_norm"]}
+        if moe:
+            from .moe import slice_experts
+            gu_l, dn_l = slice_experts(L["experts_gate_up"], L["experts_down"], cfg.moe_experts, cfg.moe_inter, cfg.hidden,
+                                       lc.moe_e_lo, lc.moe_e_hi, lc.moe_shared_here)
+            o.update(router=L["router"], experts_gate_up=gu_l, experts_down=dn_l)
+        else:
+            gu_idx = torch.cat([_arange(rank * Il, (rank + 1) * Il, dev), _arange(I + rank * Il, I + (rank + 1) * Il, dev)])
+            o.update(gate_up=_rows(L["gate_up"], gu_idx), down=_cols(L["down"], rank * Il, (rank + 1) * Il, G))
         if cfg.is_attention(i):
             idx = torch.cat([_arange(hq0 * 2 * D, hq1 * 2 * D, dev),
                              _arange(2 * Hq * D + kv0 * D, 2 * Hq * D + kv1 * D, dev),

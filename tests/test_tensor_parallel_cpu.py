@@ -10,7 +10,7 @@ import torch.multiprocessing as mp
 
 from dflash_mlx_b200 import parallel
 from oracle import model as om
-from tests.test_verify_step import small_case
+from tests.test_verify_step import small_case, small_moe_case
 
 
 def _free_port():
@@ -19,16 +19,22 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port):
+def _worker(rank, world, port, moe=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(2)
     try:
-        cfg, W, caches, ids, ctx = small_case()
+        cfg, W, caches, ids, ctx = small_moe_case() if moe else small_case()
         lc, lw = parallel.shard_weights(cfg, W, rank, world)
         lcaches = parallel.shard_caches(cfg, caches, rank, world)
-        assert lc.q_heads == cfg.q_heads // world and lc.intermediate == cfg.intermediate // world
+        assert lc.q_heads == cfg.q_heads // world
+        if moe:   # expert parallel: half of the routed experts each, the shared expert on rank 0
+            per = cfg.moe_experts // world
+            assert lc.moe_local == (rank * per, (rank + 1) * per) and lc.moe_shared_here == (rank == 0)
+            assert lw["layers"][0]["experts_down"]["w"].shape[0] == (per + (1 if rank == 0 else 0)) * cfg.hidden
+        else:
+            assert lc.intermediate == cfg.intermediate // world
         assert lw["layers"][0]["proj"]["w"].shape[0] == lc.gdn_proj_n
         assert lw["layers"][3]["proj"]["w"].shape[0] == lc.attn_proj_n
 
@@ -69,6 +75,10 @@ def _worker(rank, world, port):
 
 def test_two_rank_tensor_parallel_matches_single_rank():
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_two_rank_expert_parallel_matches_single_rank():
+    mp.spawn(_worker, args=(2, _free_port(), True), nprocs=2, join=True)
 
 
 def test_shard_config_rules():
