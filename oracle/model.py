@@ -126,11 +126,12 @@ def _embed_local_stack(cfg, L):
     return out
 
 
-def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None):
+def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None, router_logits=None):
     """caches: {"conv": [Lg][keep,cd] bf16, "state": [Lg][Hv,Dv,Dk] f32, "k"/"v": [La][Hk,cap,D] bf16}.
     Returns (logits bf16 [T,V], greedy tokens, new_caches, tapes) without touching the input GDN caches.
     For a tensor-parallel shard, ``reduce(t)`` must return the sum of ``t`` over the ranks (applied to the output of
-    every row-parallel projection) and ``gather_tokens(best_value, local_index)`` the global greedy tokens."""
+    every row-parallel projection) and ``gather_tokens(best_value, local_index)`` the global greedy tokens.
+    ``router_logits`` ([layers][T, E+1]) replaces the router matmul of a mixture-of-experts model."""
     h = W["embed"][ids.long()].to(BF)
     ig = ia = 0
     new = {"conv": [], "state": [], "k": caches["k"], "v": caches["v"]}
@@ -152,7 +153,8 @@ def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None
         x = _rms(h, L["post_norm"], cfg.eps)
         if "router" in L:
             # mixture of experts (mlx-lm switch layers + shared expert): the rank's experts are stacked locally
-            logits = _lin(x, L["router"], cfg.group_size)
+            # router logits may be injected per layer, so that routing is identical across implementations
+            logits = _lin(x, L["router"], cfg.group_size) if router_logits is None else router_logits[i]
             lo, hi = cfg.moe_local
             E = cfg.moe_experts
             if lo == 0 and hi == E and cfg.moe_shared_here:
