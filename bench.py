@@ -166,7 +166,7 @@ class QmmWorkload:
         import torch
         from oracle import qmm as oq
         from oracle.build_ref import load
-        out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "gpurun_out" / "oracle_native")))
+        out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "oracle" / "_build" / "native")))
         try:
             lib, kind_note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
         except Exception:
@@ -213,7 +213,7 @@ class DenseStepWorkload:
             cfg.moe_e_lo, cfg.moe_e_hi, cfg.moe_shared_here = rank * per, (rank + 1) * per, rank == 0
         self.cfg = cfg
         with torch.cuda.device(device):
-            weights = init_weights(cfg, 0xDF1D + rank, device)
+            weights = init_weights(cfg, 0xDF1D + rank, device, replicated_seed=0xDF1D if world > 1 else None)
         ar, ag = make_collectives(world)
         # row-parallel sums: the fused peer-memory kernel (default) or NCCL all-reduce + add/norm (DFLASH_TP_REDUCE=nccl)
         peer, self.reduce_mode = None, "none"
@@ -486,7 +486,7 @@ def dense_step_cpu_baseline(cfg, context, budget_s=25.0, expert_slots=0):
     from oracle import sdpa as osd
     from oracle.build_ref import load
     torch.set_num_threads(os.cpu_count() or 1)
-    out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "gpurun_out" / "oracle_native")))
+    out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "oracle" / "_build" / "native")))
     try:
         lib, note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
     except Exception:

@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const T* __restrict__ o,
 // [e_lo, e_hi) are numbered in ascending id order into `slot_expert` as indices into this rank's expert stack
 // (e - e_lo); with `with_shared` the shared expert (stack index e_hi - e_lo) takes the last slot with weight
 // sigmoid(logit[t, E]).  wdense[t, slot] is token t's weight for that slot (0 if not routed).
-template <typename T>
+template <typename T, int kPer>  // kPer = experts per lane: 8 covers E <= 256, 32 covers E <= 1024
 __global__ void __launch_bounds__(1024) moe_route_kernel(const T* __restrict__ logits, int T_rows, int E, int top_k, int e_lo,
                                                          int e_hi, int with_shared, int n_max, int* __restrict__ slot_expert,
                                                          int* __restrict__ n_out, float* __restrict__ wdense,
@@ -370,7 +370,6 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const T* __restrict__ l
   __syncthreads();
   if (warp < T_rows) {
     const T* row = logits + (size_t)warp * (E + 1);
-    constexpr int kPer = 32;  // experts per lane (E <= 1024)
     float v[kPer];
     const int per = (E + 31) / 32;
 #pragma unroll
@@ -563,7 +562,11 @@ extern "C" int dflash_moe_route(const void* logits, int T_rows, int experts, int
   int threads = (experts + 31) / 32 * 32;
   if (threads < 32 * T_rows) threads = 32 * T_rows;
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (launch_kernel(moe_route_kernel<T>, dim3(1), dim3(threads), 0, st, (const T*)logits, T_rows, experts,
+  if (experts <= 256)
+    DFLASH_DISPATCH(dtype, (launch_kernel(moe_route_kernel<T, 8>, dim3(1), dim3(threads), 0, st, (const T*)logits, T_rows,
+                                          experts, top_k, e_lo, e_hi, with_shared, n_max, slot_expert, n_active, wdense,
+                                          topk_ids, topk_w)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(moe_route_kernel<T, 32>, dim3(1), dim3(threads), 0, st, (const T*)logits, T_rows, experts,
                                         top_k, e_lo, e_hi, with_shared, n_max, slot_expert, n_active, wdense, topk_ids, topk_w)));
 }
 

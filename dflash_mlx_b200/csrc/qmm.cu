@@ -163,14 +163,17 @@ __device__ __forceinline__ void store_tile(const float4& v, T* __restrict__ y, c
 template <typename T>
 __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pieces, unsigned* counters,
                                            T* __restrict__ y, const T* __restrict__ bias, int nt, int ctid, int warp,
-                                           int rp, int c) {
+                                           int rp, int c, int rotmul = 0) {
+  // `nt` is the tile as stored (pieces, counters, y).  With rotmul != 0 slab s walks the tiles in the rotated order
+  // stored = (logical + s * rotmul) % NT, so its contributors are those of logical tile (nt - s * rotmul) mod NT.
+  auto logical = [&](int s_) { return rotmul == 0 ? nt : ((nt - (s_ * rotmul) % plan.NT) + plan.NT) % plan.NT; };
   // First the slot list (integer divisions only), then the loads eight at a time so that their latencies overlap,
   // then the sum in slot order (fixed order: deterministic).
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   int s2 = 0, p = 0, np = 0;
   {
     int f;
-    np = tile_pieces(slab_geom(plan, 0), nt, &f);
+    np = tile_pieces(slab_geom(plan, 0), logical(0), &f);
   }
   bool more = true;
   while (more) {
@@ -180,7 +183,7 @@ __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pi
       if (p >= np) {
         if (++s2 >= plan.S) { more = false; break; }
         int f;
-        np = tile_pieces(slab_geom(plan, s2), nt, &f);
+        np = tile_pieces(slab_geom(plan, s2), logical(s2), &f);
         p = 0;
         continue;
       }
@@ -252,6 +255,10 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   int s = 0;
   while (s + 1 < plan.S && 2 * (int)blockIdx.x >= plan.slab_cta0[s + 1]) ++s;  // slab starts are even
   const SlabGeom sg = slab_geom(plan, s);
+  // Chunk-gathered products: every slab walks the row tiles in its own rotated order, so that the workers of
+  // different slabs - which advance in step - do not all read addresses that differ by a multiple of an expert's size.
+  const int rotmul = (MODE == 2) ? 7 : 0;
+  const int rot = (MODE == 2) ? (s * rotmul) % plan.NT : 0;
   const int bl = vcta - sg.cta0;
   const bool has_work = bl < sg.ctas;
   if (2 * (int)blockIdx.x - sg.cta0 >= sg.ctas) return;  // neither worker has units
@@ -298,7 +305,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     named_bar_sync(bar_id, kConsumers);
     for (int i = 0; i < npend; ++i)
-      if (pend[2 * kMaxPend + i]) finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c);
+      if (pend[2 * kMaxPend + i]) finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c, rotmul);
     named_bar_sync(bar_id, kConsumers);
   };
 
@@ -313,11 +320,12 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const uint32_t full = bar_full + 8 * pstage;
     const uint32_t dst = smem_u32(stages + pstage * C::kStageBytes);
     mbar_arrive_expect_tx(full, C::kStageBytes);
-    int wrow = pnt * kBN, wchunk = sg.c0 + pkc;  // first weight row and K chunk of the unit inside the stacked weights
+    const int pntp = rotmul == 0 ? pnt : (pnt + rot) % plan.NT;  // the tile as stored
+    int wrow = pntp * kBN, wchunk = sg.c0 + pkc;  // first weight row and K chunk of the unit inside the stacked weights
     if constexpr (MODE == 1) {
       wrow = (ga.slot_expert[pnt / ga.block_tiles] * ga.block_tiles + pnt % ga.block_tiles) * kBN;
     } else if constexpr (MODE == 2) {
-      wrow = ga.slot_expert[wchunk / ga.cpb] * ga.block_rows + pnt * kBN;
+      wrow = ga.slot_expert[wchunk / ga.cpb] * ga.block_rows + pntp * kBN;
       wchunk = wchunk % ga.cpb;
     }
 #pragma unroll
@@ -492,21 +500,22 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       // pieces this row tile receives in total, and this worker's piece index inside its slab
       int total = 0, first_here = 0;
+      const int ntp = rotmul == 0 ? nt : (nt + rot) % NT;  // the tile as stored
       for (int s2 = lane; s2 < plan.S; s2 += 32) {
         const SlabGeom g2 = slab_geom(plan, s2);
         int f;
-        total += tile_pieces(g2, nt, &f);
+        total += tile_pieces(g2, rotmul == 0 ? nt : ((ntp - (s2 * rotmul) % NT) + NT) % NT, &f);
       }
       total = __reduce_add_sync(0xffffffffu, total);
       tile_pieces(sg, nt, &first_here);
 
       if (total > 1) {
-        pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid] = v;
+        pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + ntp) * kConsumers + ctid] = v;
       } else {
-        store_tile<T>(v, y, bias, nt, wwarp, rp, c, M, N);
+        store_tile<T>(v, y, bias, ntp, wwarp, rp, c, M, N);
       }
       if (total > 1) {
-        if (ctid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
+        if (ctid == 0) { pend[npend] = ntp; pend[kMaxPend + npend] = total; }
         ++npend;
       }
       named_bar_sync(bar_id, kConsumers);  // `red` is free again

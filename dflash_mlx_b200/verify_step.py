@@ -113,20 +113,24 @@ def _rand_quantized(n: int, k: int, gen: torch.Generator, device, group_size: in
     return {"w": w_q, "s": s.to(torch.bfloat16), "b": b.to(torch.bfloat16)}
 
 
-def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
-    """Random-init weights of the architecture (bf16 norms/embedding, int4 group-64 linears)."""
+def init_weights(cfg: HybridConfig, seed: int, device, replicated_seed: int = None) -> Dict:
+    """Random-init weights of the architecture (bf16 norms/embedding, int4 group-64 linears).  For a shard of a
+    parallel run pass the same ``replicated_seed`` on every rank: the tensors every rank holds a full copy of (norms,
+    embedding, expert router) are then drawn from it and agree across the ranks."""
     gen = torch.Generator(device=device).manual_seed(seed)
+    gen_rep = gen if replicated_seed is None else torch.Generator(device=device).manual_seed(replicated_seed)
     bf = torch.bfloat16
     rn = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=gen, device=device))  # noqa: E731
+    rr = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=gen_rep, device=device))  # noqa: E731
     H, I, G = cfg.hidden, cfg.intermediate, cfg.group_size
     layers: List[Dict] = []
     for i in range(cfg.layers):
-        L: Dict = {"in_norm": (1.0 + 0.1 * rn(H)).to(bf), "post_norm": (1.0 + 0.1 * rn(H)).to(bf)}
+        L: Dict = {"in_norm": (1.0 + 0.1 * rr(H)).to(bf), "post_norm": (1.0 + 0.1 * rr(H)).to(bf)}
         if cfg.moe_experts > 0:
             # router (+ shared-expert gate as its last row) and this rank's stack of experts (+ the shared one)
             lo, hi = cfg.moe_local
             n_local = hi - lo + (1 if cfg.moe_shared_here else 0)
-            L["router"] = _rand_quantized(cfg.moe_experts + 1, H, gen, device, G, w_std=0.05)
+            L["router"] = _rand_quantized(cfg.moe_experts + 1, H, gen_rep, device, G, w_std=0.05)
             L["experts_gate_up"] = _rand_quantized(n_local * 2 * cfg.moe_inter, H, gen, device, G)
             L["experts_down"] = _rand_quantized(n_local * H, cfg.moe_inter, gen, device, G)
         else:
@@ -134,8 +138,8 @@ def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
             L["down"] = _rand_quantized(H, I, gen, device, G)
         if cfg.is_attention(i):
             L["proj"] = _rand_quantized(cfg.attn_proj_n, H, gen, device, G)
-            L["q_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
-            L["k_norm"] = (1.0 + 0.1 * rn(cfg.head_dim)).to(bf)
+            L["q_norm"] = (1.0 + 0.1 * rr(cfg.head_dim)).to(bf)
+            L["k_norm"] = (1.0 + 0.1 * rr(cfg.head_dim)).to(bf)
             ko = cfg.q_heads * cfg.head_dim
             if getattr(cfg, "tp_world", 1) > 1:          # a shard's row-parallel K is padded to 8 groups
                 ko = (ko + 8 * G - 1) // (8 * G) * (8 * G)
@@ -145,10 +149,10 @@ def init_weights(cfg: HybridConfig, seed: int, device) -> Dict:
             L["conv_w"] = rn(cfg.conv_dim, cfg.conv_kernel, std=0.5).to(bf)
             L["A_log"] = torch.log(0.5 + 4.0 * torch.rand(cfg.gdn_v_heads, generator=gen, device=device)).float()
             L["dt_bias"] = rn(cfg.gdn_v_heads, std=0.5).float()
-            L["g_norm"] = (1.0 + 0.1 * rn(cfg.gdn_dv)).to(bf)
+            L["g_norm"] = (1.0 + 0.1 * rr(cfg.gdn_dv)).to(bf)
             L["out_proj"] = _rand_quantized(H, cfg.gdn_v_heads * cfg.gdn_dv, gen, device, G)
         layers.append(L)
-    return {"layers": layers, "embed": rn(getattr(cfg, "embed_rows", cfg.vocab), H, std=1.0).to(bf), "norm": (1.0 + 0.1 * rn(H)).to(bf),
+    return {"layers": layers, "embed": rr(getattr(cfg, "embed_rows", cfg.vocab), H, std=1.0).to(bf), "norm": (1.0 + 0.1 * rr(H)).to(bf),
             "lm_head": _rand_quantized(cfg.vocab, H, gen, device, G)}
 
 

@@ -19,6 +19,7 @@ Usage:  python tests/golden/make_golden.py --reference /path/to/dflash-mlx
 from __future__ import annotations
 
 import argparse
+import os
 import sys
 import types
 from pathlib import Path
@@ -80,7 +81,8 @@ def gdn_inputs(seed, B, T, Hk, Hv, Dk, Dv, vector_gate, with_mask):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("DFLASH_REFERENCE_DIR"), required="DFLASH_REFERENCE_DIR" not in os.environ,
+                    help="checkout of the dflash-mlx project (or set DFLASH_REFERENCE_DIR)")
     args = ap.parse_args()
     install_numpy_mlx()
     sys.path.insert(0, args.reference)
