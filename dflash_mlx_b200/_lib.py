@@ -7,6 +7,7 @@ stream, and raise ``RuntimeError`` with the library's message on a non-zero stat
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -14,6 +15,8 @@ import torch
 
 _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libdflash_b200.so"
+if os.environ.get("DFLASH_LIB"):          # an alternative build of the library (A/B measurements)
+    LIB_PATH = Path(os.environ["DFLASH_LIB"])
 _lock = threading.Lock()
 _lib = None
 

@@ -287,6 +287,7 @@ struct AttnPrepArgs {
   void* q; void* kcache; void* vcache; long long cache_head_stride;
   int T, Hq, Hk, D, rope_dims, offset;
   float eps, rope_base;
+  const int* offset_dev;  // when not NULL the cache offset is read on the device
 };
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
   if (idx >= a.T * heads) return;
   const int t = idx / heads, h = idx % heads;
   const T* row = (const T*)a.proj + (size_t)t * a.ld;
-  const int pos = a.offset + t;
+  const int pos = (a.offset_dev ? *a.offset_dev : a.offset) + t;
   if (h >= a.Hq + a.Hk) {  // value head: plain copy into the cache
     const int hk = h - a.Hq - a.Hk;
     T* dst = (T*)a.vcache + (size_t)hk * a.cache_head_stride + (size_t)pos * a.D;
@@ -530,18 +531,35 @@ extern "C" int dflash_gated_rmsnorm(const void* y, const void* proj, long long l
                                                                                  (const T*)w, (T*)out, rh, Hv, Dv, eps)));
 }
 
-extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
-                                const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
-                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
-                                int dtype, void* stream) {
+static int attn_prep_impl(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                          const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
+                          int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
+                          int dtype, void* stream, const int* offset_dev) {
   if (!proj || !q_norm_w || !k_norm_w || !q || !kcache || !vcache) return fail(DFLASH_ERR_BAD_ARG, "attn_prep: null operand");
   if (T_rows < 1 || rope_dims < 0 || rope_dims > D || rope_dims % 2 != 0 || offset < 0)
     return fail(DFLASH_ERR_BAD_SHAPE, "attn_prep: bad rope_dims/offset");
   AttnPrepArgs a{proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride,
-                 T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base};
+                 T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base, offset_dev};
   const int n = T_rows * (Hq + 2 * Hk);
   cudaStream_t st = (cudaStream_t)stream;
   DFLASH_DISPATCH(dtype, (launch_kernel(attn_prep_kernel<T>, dim3((n + 3) / 4), dim3(128), 0, st, a)));
+}
+
+extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                                const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
+                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
+                                int dtype, void* stream) {
+  return attn_prep_impl(proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride, T_rows, Hq, Hk, D,
+                        rope_dims, offset, eps, rope_base, dtype, stream, nullptr);
+}
+
+extern "C" int dflash_attn_prep_dev_offset(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                                           const void* k_norm_w, void* q, void* kcache, void* vcache,
+                                           long long cache_head_stride, int T_rows, int Hq, int Hk, int D, int rope_dims,
+                                           const int* offset_dev, float eps, float rope_base, int dtype, void* stream) {
+  if (!offset_dev) return fail(DFLASH_ERR_BAD_ARG, "attn_prep_dev_offset: offset_dev is NULL");
+  return attn_prep_impl(proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride, T_rows, Hq, Hk, D,
+                        rope_dims, 0, eps, rope_base, dtype, stream, offset_dev);
 }
 
 extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,

@@ -163,17 +163,14 @@ __device__ __forceinline__ void store_tile(const float4& v, T* __restrict__ y, c
 template <typename T>
 __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pieces, unsigned* counters,
                                            T* __restrict__ y, const T* __restrict__ bias, int nt, int ctid, int warp,
-                                           int rp, int c, int rotmul = 0) {
-  // `nt` is the tile as stored (pieces, counters, y).  With rotmul != 0 slab s walks the tiles in the rotated order
-  // stored = (logical + s * rotmul) % NT, so its contributors are those of logical tile (nt - s * rotmul) mod NT.
-  auto logical = [&](int s_) { return rotmul == 0 ? nt : ((nt - (s_ * rotmul) % plan.NT) + plan.NT) % plan.NT; };
+                                           int rp, int c) {
   // First the slot list (integer divisions only), then the loads eight at a time so that their latencies overlap,
   // then the sum in slot order (fixed order: deterministic).
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   int s2 = 0, p = 0, np = 0;
   {
     int f;
-    np = tile_pieces(slab_geom(plan, 0), logical(0), &f);
+    np = tile_pieces(slab_geom(plan, 0), nt, &f);
   }
   bool more = true;
   while (more) {
@@ -183,7 +180,7 @@ __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pi
       if (p >= np) {
         if (++s2 >= plan.S) { more = false; break; }
         int f;
-        np = tile_pieces(slab_geom(plan, s2), logical(s2), &f);
+        np = tile_pieces(slab_geom(plan, s2), nt, &f);
         p = 0;
         continue;
       }
@@ -200,6 +197,54 @@ __device__ __noinline__ void finalize_tile(const QmmPlan& plan, const float4* pi
   }
   if (ctid == 0) counters[nt] = 0;  // ready for the next launch
   store_tile<T>(v, y, bias, nt, warp, rp, c, plan.M, plan.N);
+}
+
+// Variant for products with many K slabs (the chunk-gathered expert product: dozens of pieces per row tile), run by
+// the worker (256 threads) that took the last ticket of row tile nt; same summation order as finalize_tile.
+// The list of pieces (integer divisions per K slab) is built once, by the lanes of the worker's first warp in parallel,
+// into `scratch` (shared memory, >= 4 * (1 + S * maxp) bytes); then every thread sums its element over the list, eight
+// loads in flight at a time.  Order = slab-major, then piece index: deterministic.
+template <typename T>
+__device__ __noinline__ void finalize_tile_coop(const QmmPlan& plan, const float4* pieces, unsigned* counters,
+                                           T* __restrict__ y, const T* __restrict__ bias, int nt, int ctid, int warp,
+                                           int rp, int c, int* scratch, int bar_id) {
+  const int lane = ctid & 31;
+  if (warp == 0) {
+    int base = 0;
+    for (int s0 = 0; s0 < plan.S; s0 += 32) {
+      const int s2 = s0 + lane;
+      int np = 0;
+      if (s2 < plan.S) {
+        int f;
+        np = tile_pieces(slab_geom(plan, s2), nt, &f);
+      }
+      int incl = np;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const int excl = base + incl - np;
+      for (int p = 0; p < np; ++p) scratch[1 + excl + p] = s2 * plan.maxp + p;
+      base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) scratch[0] = base;
+  }
+  named_bar_sync(bar_id, kConsumers);
+  const int P = scratch[0];
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < P; k0 += 8) {
+    float4 a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (k0 + i < P) a[i] = ld_cg_f4(&pieces[((size_t)scratch[1 + k0 + i] * plan.NT + nt) * kConsumers + ctid]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (k0 + i < P) { v.x += a[i].x; v.y += a[i].y; v.z += a[i].z; v.w += a[i].w; }
+  }
+  if (ctid == 0) counters[nt] = 0;  // ready for the next launch
+  store_tile<T>(v, y, bias, nt, warp, rp, c, plan.M, plan.N);
+  named_bar_sync(bar_id, kConsumers);  // `scratch` may be rebuilt for the next tile
 }
 
 template <typename T, int G, int MODE>
@@ -255,10 +300,6 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   int s = 0;
   while (s + 1 < plan.S && 2 * (int)blockIdx.x >= plan.slab_cta0[s + 1]) ++s;  // slab starts are even
   const SlabGeom sg = slab_geom(plan, s);
-  // Chunk-gathered products: every slab walks the row tiles in its own rotated order, so that the workers of
-  // different slabs - which advance in step - do not all read addresses that differ by a multiple of an expert's size.
-  const int rotmul = (MODE == 2) ? 7 : 0;
-  const int rot = (MODE == 2) ? (s * rotmul) % plan.NT : 0;
   const int bl = vcta - sg.cta0;
   const bool has_work = bl < sg.ctas;
   if (2 * (int)blockIdx.x - sg.cta0 >= sg.ctas) return;  // neither worker has units
@@ -305,7 +346,10 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     named_bar_sync(bar_id, kConsumers);
     for (int i = 0; i < npend; ++i)
-      if (pend[2 * kMaxPend + i]) finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c, rotmul);
+      if (pend[2 * kMaxPend + i]) {
+        if constexpr (MODE == 2) finalize_tile_coop<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c, (int*)red, bar_id);
+        else finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c);
+      }
     named_bar_sync(bar_id, kConsumers);
   };
 
@@ -320,12 +364,11 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const uint32_t full = bar_full + 8 * pstage;
     const uint32_t dst = smem_u32(stages + pstage * C::kStageBytes);
     mbar_arrive_expect_tx(full, C::kStageBytes);
-    const int pntp = rotmul == 0 ? pnt : (pnt + rot) % plan.NT;  // the tile as stored
-    int wrow = pntp * kBN, wchunk = sg.c0 + pkc;  // first weight row and K chunk of the unit inside the stacked weights
+    int wrow = pnt * kBN, wchunk = sg.c0 + pkc;  // first weight row and K chunk of the unit inside the stacked weights
     if constexpr (MODE == 1) {
       wrow = (ga.slot_expert[pnt / ga.block_tiles] * ga.block_tiles + pnt % ga.block_tiles) * kBN;
     } else if constexpr (MODE == 2) {
-      wrow = ga.slot_expert[wchunk / ga.cpb] * ga.block_rows + pntp * kBN;
+      wrow = ga.slot_expert[wchunk / ga.cpb] * ga.block_rows + pnt * kBN;
       wchunk = wchunk % ga.cpb;
     }
 #pragma unroll
@@ -500,22 +543,21 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       // pieces this row tile receives in total, and this worker's piece index inside its slab
       int total = 0, first_here = 0;
-      const int ntp = rotmul == 0 ? nt : (nt + rot) % NT;  // the tile as stored
       for (int s2 = lane; s2 < plan.S; s2 += 32) {
         const SlabGeom g2 = slab_geom(plan, s2);
         int f;
-        total += tile_pieces(g2, rotmul == 0 ? nt : ((ntp - (s2 * rotmul) % NT) + NT) % NT, &f);
+        total += tile_pieces(g2, nt, &f);
       }
       total = __reduce_add_sync(0xffffffffu, total);
       tile_pieces(sg, nt, &first_here);
 
       if (total > 1) {
-        pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + ntp) * kConsumers + ctid] = v;
+        pieces[((size_t)(s * plan.maxp + (bl - first_here)) * NT + nt) * kConsumers + ctid] = v;
       } else {
-        store_tile<T>(v, y, bias, ntp, wwarp, rp, c, M, N);
+        store_tile<T>(v, y, bias, nt, wwarp, rp, c, M, N);
       }
       if (total > 1) {
-        if (ctid == 0) { pend[npend] = ntp; pend[kMaxPend + npend] = total; }
+        if (ctid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
         ++npend;
       }
       named_bar_sync(bar_id, kConsumers);  // `red` is free again

@@ -56,6 +56,7 @@ struct SdpaArgs {
   int B, Hq, Hk, N, gqa, splits, blocks_per_split;
   long long k_head_stride, k_seq_stride, v_head_stride, v_seq_stride;  // in elements
   float scale_log2;
+  const int* n_dev;  // when not NULL: the KV length lives on the device (N above is then only its upper bound)
 };
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a swizzled tile with `row_bytes` per row.
@@ -84,8 +85,9 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
   uint8_t* sV = sK + 2 * kBN * RB;
   const uint32_t uQ = smem_u32(sQ), uK = smem_u32(sK), uV = smem_u32(sV);
 
+  const int N = a.n_dev ? max(16, min(*a.n_dev, a.N)) : a.N;
   const int blk0 = split * a.blocks_per_split;
-  const int nblk_total = (a.N + kBN - 1) / kBN;
+  const int nblk_total = (N + kBN - 1) / kBN;
   const int blk1 = min(blk0 + a.blocks_per_split, nblk_total);
 
   const T* kbase = (const T*)a.k + (size_t)bhk * a.k_head_stride;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
     const int n0 = blk * kBN;
     for (int i = threadIdx.x; i < kBN * CH; i += blockDim.x) {
       const int r = i / CH, ch = i % CH;
-      const bool ok = (n0 + r) < a.N;
+      const bool ok = (n0 + r) < N;
       const size_t rr = ok ? (size_t)(n0 + r) : 0;
       cp_async16(uK + buf * kBN * RB + swz(r, ch, RB), kbase + rr * a.k_seq_stride + ch * 8, ok);
       cp_async16(uV + buf * kBN * RB + swz(r, ch, RB), vbase + rr * a.v_seq_stride + ch * 8, ok);
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
 
     // ---- scale, visibility, online softmax (rows g and g+8 of this warp) ----
     const int n0 = blk * kBN;
-    const bool edge = (n0 + kBN > a.N - 16) || a.mask != nullptr;
+    const bool edge = (n0 + kBN > N - 16) || a.mask != nullptr;
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
     for (int j = 0; j < kBN / 8; ++j) {
@@ -162,9 +164,9 @@ __global__ void __launch_bounds__(256, 1) sdpa_partials_kernel(const SdpaArgs a)
         if (edge) {
           const int n = n0 + 8 * j + 2 * c + (e & 1);
           const int row = g + ((e >> 1) << 3);
-          bool vis = (n < a.N) && (n <= a.N - 16 + row);
+          bool vis = (n < N) && (n <= N - 16 + row);
           if (a.mask != nullptr && vis && head_ok) {
-            const float mv = TR::to_float(((const T*)a.mask)[(((size_t)b * a.Hq + hq) * 16 + row) * a.N + n]);
+            const float mv = TR::to_float(((const T*)a.mask)[(((size_t)b * a.Hq + hq) * 16 + row) * N + n]);
             vis = mv >= fmin_t;
             v += mv * kLog2e;
           }
@@ -371,10 +373,10 @@ extern "C" size_t dflash_verify_sdpa_workspace_bytes(int B, int Hq, int Hk, int 
   return (size_t)B * Hq * 16 * splits * (D + 2) * sizeof(float) + 256;
 }
 
-extern "C" int dflash_verify_sdpa(const void* q, const void* k, const void* v, const void* mask, void* out, int B, int Hq,
-                                  int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
-                                  long long v_head_stride, long long v_seq_stride, float scale, int dtype,
-                                  int num_splits, void* workspace, size_t workspace_bytes, void* stream) {
+static int verify_sdpa_impl(const void* q, const void* k, const void* v, const void* mask, void* out, int B, int Hq,
+                            int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
+                            long long v_head_stride, long long v_seq_stride, float scale, int dtype,
+                            int num_splits, void* workspace, size_t workspace_bytes, void* stream, const int* n_dev) {
   if (!q || !k || !v || !out) return fail(DFLASH_ERR_BAD_ARG, "verify_sdpa: null operand");
   if (B < 1 || Hq < 1 || Hk < 1 || Hq % Hk != 0) return fail(DFLASH_ERR_BAD_SHAPE, "verify_sdpa: bad head counts");
   if (N < 16) return fail(DFLASH_ERR_BAD_SHAPE, "verify_sdpa: N=%d must include the 16 query positions", N);
@@ -389,6 +391,7 @@ extern "C" int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
   a.k_head_stride = k_head_stride; a.k_seq_stride = k_seq_stride;
   a.v_head_stride = v_head_stride; a.v_seq_stride = v_seq_stride;
   a.scale_log2 = scale * kLog2e;
+  a.n_dev = n_dev;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == DFLASH_BF16)
     return D == 128 ? launch<__nv_bfloat16, 128>(a, workspace, workspace_bytes, num_splits, st)
@@ -397,6 +400,24 @@ extern "C" int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
     return D == 128 ? launch<__half, 128>(a, workspace, workspace_bytes, num_splits, st)
                     : launch<__half, 256>(a, workspace, workspace_bytes, num_splits, st);
   return fail(DFLASH_ERR_BAD_ARG, "verify_sdpa: dtype %d (want bf16 or f16)", dtype);
+}
+
+extern "C" int dflash_verify_sdpa(const void* q, const void* k, const void* v, const void* mask, void* out, int B, int Hq,
+                                  int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
+                                  long long v_head_stride, long long v_seq_stride, float scale, int dtype,
+                                  int num_splits, void* workspace, size_t workspace_bytes, void* stream) {
+  return verify_sdpa_impl(q, k, v, mask, out, B, Hq, Hk, N, D, k_head_stride, k_seq_stride, v_head_stride, v_seq_stride,
+                          scale, dtype, num_splits, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int dflash_verify_sdpa_dev_len(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk,
+                                          int N_max, const int* n_dev, int D, long long k_head_stride,
+                                          long long k_seq_stride, long long v_head_stride, long long v_seq_stride,
+                                          float scale, int dtype, int num_splits, void* workspace, size_t workspace_bytes,
+                                          void* stream) {
+  if (!n_dev) return fail(DFLASH_ERR_BAD_ARG, "verify_sdpa_dev_len: n_dev is NULL");
+  return verify_sdpa_impl(q, k, v, nullptr, out, B, Hq, Hk, N_max, D, k_head_stride, k_seq_stride, v_head_stride,
+                          v_seq_stride, scale, dtype, num_splits, workspace, workspace_bytes, stream, n_dev);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -42,6 +42,9 @@ def _declare():
     d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
     d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_f32, _f32, _i32, _vp])
     d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _ll, _i32, _i32, _i32, _i32, _vp])
+    d("dflash_attn_prep_dev_offset", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 5 + [_vp, _f32, _f32, _i32, _vp])
+    d("dflash_verify_sdpa_dev_len", _i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _ll, _ll, _ll, _ll, _f32,
+                                           _i32, _i32, _vp, ctypes.c_size_t, _vp])
     _declared = True
 
 
@@ -208,6 +211,9 @@ class HybridVerifyModel:
         self.ao = z(cfg.q_heads, T, cfg.head_dim)
         self.offset = 0
         self.steps_dev = z(1, dt=torch.int32)
+        self.offset_dev = None         # set by enable_device_offset(): the cache position then lives on the device
+        self.kvlen_dev = None
+        self._cycle_graphs = {}
         with torch.cuda.device(dev):
             need = 256
             for L in weights["layers"]:
@@ -303,6 +309,7 @@ class HybridVerifyModel:
             raise ValueError(f"ids must be {T} int32 tokens on the CUDA device")
         if self.offset + T > cfg.max_context:
             raise ValueError("KV cache capacity exceeded")
+        dev_off = self.offset_dev is not None
         self.launches_per_step = 0
         self._last_ids = ids
         st, BF = self._st(), _lib.BF16
@@ -320,14 +327,26 @@ class HybridVerifyModel:
                 k_off = 2 * cfg.q_heads * cfg.head_dim
                 v_off = k_off + cfg.kv_heads * cfg.head_dim
                 hs = cfg.max_context * cfg.head_dim
-                self._chk(lib.dflash_attn_prep(self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(),
-                                               L["k_norm"].data_ptr(), self.aq.data_ptr(), self.kcache[ia].data_ptr(),
-                                               self.vcache[ia].data_ptr(), hs, T, cfg.q_heads, cfg.kv_heads, cfg.head_dim,
-                                               cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st), "dflash_attn_prep")
-                self._chk(lib.dflash_verify_sdpa(self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(),
-                                                 None, self.ao.data_ptr(), 1, cfg.q_heads, cfg.kv_heads, N, cfg.head_dim,
-                                                 hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
-                                                 self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st), "dflash_verify_sdpa")
+                if dev_off:   # cache position and KV length are read on the device: the captured step serves every cycle
+                    self._chk(lib.dflash_attn_prep_dev_offset(
+                        self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(), L["k_norm"].data_ptr(),
+                        self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), hs, T, cfg.q_heads,
+                        cfg.kv_heads, cfg.head_dim, cfg.rope_dims, self.offset_dev.data_ptr(), cfg.eps, cfg.rope_base, BF, st),
+                        "dflash_attn_prep_dev_offset")
+                    self._chk(lib.dflash_verify_sdpa_dev_len(
+                        self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), self.ao.data_ptr(), 1,
+                        cfg.q_heads, cfg.kv_heads, cfg.max_context, self.kvlen_dev.data_ptr(), cfg.head_dim, hs, cfg.head_dim,
+                        hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0, self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st),
+                        "dflash_verify_sdpa_dev_len")
+                else:
+                    self._chk(lib.dflash_attn_prep(self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(),
+                                                   L["k_norm"].data_ptr(), self.aq.data_ptr(), self.kcache[ia].data_ptr(),
+                                                   self.vcache[ia].data_ptr(), hs, T, cfg.q_heads, cfg.kv_heads, cfg.head_dim,
+                                                   cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st), "dflash_attn_prep")
+                    self._chk(lib.dflash_verify_sdpa(self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(),
+                                                     None, self.ao.data_ptr(), 1, cfg.q_heads, cfg.kv_heads, N, cfg.head_dim,
+                                                     hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
+                                                     self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st), "dflash_verify_sdpa")
                 self.launches_per_step += 1      # partials + combine
                 self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix_attn.data_ptr(),
                                                self.mix_attn.shape[1], T, cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
@@ -467,6 +486,67 @@ class HybridVerifyModel:
         self._moe_counts = None
         self._armed = armed
         return counts
+
+    # ---- whole speculative cycle on the device (verify -> accept -> roll back), one graph launch -------------
+    def enable_device_offset(self) -> None:
+        """From now on the KV / RoPE position is a device scalar (initialised from ``self.offset``): ``verify`` reads it on
+        the device and ``cycle`` advances it there, so nothing in a cycle depends on a host value.  ``self.offset``
+        becomes an upper bound (each cycle adds a full block) until ``sync_offset`` reads the true value back."""
+        self.offset_dev = torch.tensor([self.offset], dtype=torch.int32, device=self.dev)
+        self.kvlen_dev = torch.tensor([self.offset + self.cfg.block], dtype=torch.int32, device=self.dev)
+        self._cycle_graphs = {}
+
+    def sync_offset(self) -> int:
+        """Reads the device-side position back (synchronises) and tightens ``self.offset`` to it."""
+        self.offset = int(self.offset_dev.item())
+        return self.offset
+
+    def cycle(self, block_ids: torch.Tensor) -> torch.Tensor:
+        """One speculative cycle for ``block_ids`` = [staged token, 15 drafted tokens] (int32 CUDA): verify pass, greedy
+        posterior, accepted length (runtime.py:101-108), rollback of the recurrent caches to the accepted prefix and
+        advance of the cache position by accepted + 1 - all enqueued, nothing synchronises.  Returns the accepted
+        length as a 1-element int32 CUDA tensor; the posterior tokens are in ``self.tokens``."""
+        if self.offset_dev is None:
+            raise RuntimeError("call enable_device_offset() first")
+        T = self.cfg.block
+        self.arm_rollback()
+        self.verify(block_ids)
+        n_acc = self.match_acceptance_length(block_ids[1:], self.tokens).reshape(1)
+        self.rollback(n_acc, drafted_tokens=T - 1)
+        self.offset_dev.add_(n_acc + 1)
+        self.kvlen_dev.copy_(self.offset_dev + T)
+        self.offset += T                       # upper bound of the position (see sync_offset)
+        self.n_accepted_dev = n_acc
+        return n_acc
+
+    def cycle_captured(self, block_ids: torch.Tensor) -> torch.Tensor:
+        """``cycle`` as ONE graph launch.  A graph is captured per parity of the double-buffered recurrent state (the
+        buffers swap roles every cycle) and reused for every later cycle, whatever the cache position."""
+        key = self.cur
+        T = self.cfg.block
+        if self.offset + T > self.cfg.max_context:
+            raise ValueError("KV cache capacity may be exceeded: call sync_offset()")
+        if key not in self._cycle_graphs:
+            if not hasattr(self, "block_static"):
+                self.block_static = torch.zeros(T, dtype=torch.int32, device=self.dev)
+                self.n_acc_static = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            # capture must not disturb the caches: the recorded work runs only at replay
+            saved = (self.cur, self.offset, self._armed)
+            side = torch.cuda.Stream(self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    self.n_acc_static.copy_(self.cycle(self.block_static))
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            self.cur, self.offset, self._armed = saved
+            self._cycle_graphs[key] = g
+        self.block_static.copy_(block_ids, non_blocking=True)
+        self._cycle_graphs[key].replay()
+        self.cur ^= 1
+        self.offset += T
+        self._armed = False
+        return self.n_acc_static
 
     # ---- acceptance and rollback (runtime.py:101-108, 878-907; recurrent_rollback_cache.py:148-171) -------
     @staticmethod

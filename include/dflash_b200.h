@@ -202,6 +202,23 @@ DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, v
                                 int Hq, int D, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Variants whose cache position lives on the DEVICE, so that one captured CUDA graph serves every speculative cycle
+ * (the reference re-reads its Python-side cache offset each cycle, dflash_mlx/runtime.py:546-550, 878-907; a graph
+ * cannot).  dflash_attn_prep_dev_offset = dflash_attn_prep with the offset read from *offset_dev (the caller keeps
+ * offset + T within the cache capacity).  dflash_verify_sdpa_dev_len = dflash_verify_sdpa (no mask array) whose KV
+ * length is min(*n_dev, N_max): the split-KV geometry and the workspace are those of N_max, splits beyond the actual
+ * length contribute nothing. */
+DFLASH_API int dflash_attn_prep_dev_offset(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
+                                           const void* k_norm_w, void* q, void* kcache, void* vcache,
+                                           long long cache_head_stride, int T_rows, int Hq, int Hk, int D, int rope_dims,
+                                           const int* offset_dev, float eps, float rope_base, int dtype, void* stream);
+DFLASH_API int dflash_verify_sdpa_dev_len(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk,
+                                          int N_max, const int* n_dev, int D, long long k_head_stride,
+                                          long long k_seq_stride, long long v_head_stride, long long v_seq_stride,
+                                          float scale, int dtype, int num_splits, void* workspace, size_t workspace_bytes,
+                                          void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Mixture-of-experts block of a verify step (16 tokens, top_k of E routed experts + one shared expert).
  * The reference has no expert code of its own: routed experts run through mlx-lm's SwitchGLU / `mx.gather_qmm`
  * (dependency), only the shared expert reaches its verify matmul (dflash_mlx/verify_linear.py:160).  These entry

@@ -142,3 +142,74 @@ def test_moe_step_matches_oracle():
     assert torch.equal(m.logits.view(-1)[: eager.numel()].view_as(eager), eager)
     assert "experts" in m.algorithmic_bytes()
     assert _lib.lib().dflash_device_error(0) == 0
+
+
+def test_device_side_cycle_matches_host_driven_cycle():
+    """verify -> accept -> roll back with the cache position on the device, as ONE replayed graph per cycle, against the
+    same cycles driven from the host (eager launches, host integers): identical tokens, accepted lengths, recurrent
+    state, conv window, KV cache and position after every cycle, for several cycles and accepted lengths."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import HybridVerifyModel, weights_to
+    from dflash_mlx_b200 import _lib
+    cfg, W, caches, ids, ctx = small_case()
+    Wc = weights_to(W, "cuda")
+
+    def fresh():
+        m = HybridVerifyModel(cfg, Wc, "cuda")
+        for l in range(len(caches["state"])):
+            m.state[0][l].copy_(caches["state"][l]); m.conv[0][l].copy_(caches["conv"][l])
+        for l in range(len(caches["k"])):
+            m.kcache[l].copy_(caches["k"][l]); m.vcache[l].copy_(caches["v"][l])
+        m.cur, m.offset = 0, ctx
+        return m
+
+    host, dev = fresh(), fresh()
+    dev.enable_device_offset()
+    gen = torch.Generator().manual_seed(77)
+    T = cfg.block
+    accepted = []
+    for cyc in range(5):
+        # a block whose first `want` drafted tokens agree with the target (built greedily with the host model)
+        want = [0, 3, 15, 1, 7][cyc]
+        block = torch.randint(0, cfg.vocab, (T,), generator=gen, dtype=torch.int32).cuda()
+        snap = (host.cur, host.offset, [host.state[i].clone() for i in range(2)], [host.conv[i].clone() for i in range(2)],
+                host.kcache.clone(), host.vcache.clone())
+        for j in range(want):
+            host.arm_rollback()
+            host.verify(block)
+            block[j + 1] = host.tokens[j]
+            host.cur, host.offset = snap[0], snap[1]
+            for i in range(2):
+                host.state[i].copy_(snap[2][i]); host.conv[i].copy_(snap[3][i])
+            host.kcache.copy_(snap[4]); host.vcache.copy_(snap[5])
+        if want < T - 1:                          # make sure the next drafted token is wrong
+            host.arm_rollback()
+            host.verify(block)
+            block[want + 1] = (host.tokens[want] + 1) % cfg.vocab
+            host.cur, host.offset = snap[0], snap[1]
+            for i in range(2):
+                host.state[i].copy_(snap[2][i]); host.conv[i].copy_(snap[3][i])
+            host.kcache.copy_(snap[4]); host.vcache.copy_(snap[5])
+        # host-driven cycle
+        host.arm_rollback()
+        host.verify(block)
+        n_host = int(host.match_acceptance_length(block[1:], host.tokens))
+        toks_host = host.tokens.clone()
+        host.rollback(n_host, drafted_tokens=T - 1)
+        # device-driven cycle, one graph launch
+        n_dev = dev.cycle_captured(block)
+        torch.cuda.synchronize()
+        assert n_host == want
+        assert int(n_dev) == n_host
+        assert torch.equal(dev.tokens, toks_host)
+        assert dev.cur == host.cur
+        assert torch.equal(dev.state[dev.cur], host.state[host.cur])
+        assert torch.equal(dev.conv[dev.cur], host.conv[host.cur])
+        assert int(dev.offset_dev) == host.offset
+        assert torch.equal(dev.kcache[:, :, : host.offset], host.kcache[:, :, : host.offset])
+        accepted.append(n_host)
+    assert accepted == [0, 3, 15, 1, 7]
+    assert dev.sync_offset() == host.offset
+    assert len(dev._cycle_graphs) == 2            # one graph per parity of the state buffers, reused afterwards
+    assert _lib.lib().dflash_device_error(0) == 0
