@@ -38,11 +38,11 @@ constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = 2 * kConsumers;  // two workers of 8 warps; thread 0 of a worker also issues its TMA loads
 constexpr int kRedBytes = 4 * 8 * 32 * 16;     // per worker: [4 warps][quad][lane] float4
 constexpr int kMaxSlabs = 64;
-constexpr int kMaxPend = 32;  // partial tiles a worker may hold before it takes their tickets
 constexpr int kMaxRowTiles = 16384;  // ticket counters kept in a fixed prefix of the workspace
 
 struct QmmPlan {
   int M, K, N, NT, S, maxp;
+  int pend_cap;  // partial tiles one worker may write: sizes its list in the workspace (tickets are taken after its last unit)
   int slab_chunk0[kMaxSlabs + 1];
   int slab_cta0[kMaxSlabs + 1];
 };
@@ -75,7 +75,7 @@ struct Cfg {
   static constexpr int kXRowBytes = kSlabKMax * 2 + 16;  // +16 B: rows land on different banks
   static constexpr int kXBytes = 16 * kXRowBytes;
   static constexpr size_t kSmemBytes =
-      1024 + (size_t)2 * kStages * kStageBytes + kXBytes + 2 * kRedBytes + 8 * (4 * kStages + 1) + 2 * 3 * kMaxPend * 4;
+      1024 + (size_t)2 * kStages * kStageBytes + kXBytes + 2 * kRedBytes + 8 * (4 * kStages + 1) + 64;
 };
 
 // Which weight row of a 16-row tile half a lane group reads: chosen per group size so that the
@@ -133,7 +133,8 @@ __device__ void device_plan(const QmmPlan& base, const GatherArgs& ga, int n, Qm
   p->slab_cta0[p->S] = 2 * (int)blocks;
   for (int i = p->S - 1; i >= 1; --i)
     if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 2) p->slab_cta0[i] = p->slab_cta0[i + 1] - 2;
-  p->maxp = base.maxp;  // the host's bound for the largest case (sizes the workspace)
+  p->maxp = base.maxp;  // the host's bounds for the largest case (they size the workspace)
+  p->pend_cap = base.pend_cap;
 }
 
 // Output element ownership after the cross-warp reduction: consumer thread (warp, lane) holds, for row
@@ -253,7 +254,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                   const __grid_constant__ CUtensorMap tmB, const T* __restrict__ x, const T* __restrict__ bias,
                   T* __restrict__ y, float4* __restrict__ pieces, unsigned* __restrict__ counters,
                   const __grid_constant__ QmmPlan base_plan, int* __restrict__ err, const int dependent,
-                  const __grid_constant__ GatherArgs ga) {
+                  const __grid_constant__ GatherArgs ga, int* __restrict__ pend_ws) {
   using C = Cfg<G>;
   using TR = MmaTraits<T>;
   extern __shared__ uint8_t smem_raw[];
@@ -291,7 +292,6 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   uint8_t* xbuf = smem + (size_t)2 * C::kStages * C::kStageBytes;
   float4* red = (float4*)(xbuf + C::kXBytes + (size_t)worker * kRedBytes);
   uint64_t* bars = (uint64_t*)(xbuf + C::kXBytes + 2 * kRedBytes);
-  volatile int* pend = (volatile int*)(bars + 4 * C::kStages + 1) + worker * 3 * kMaxPend;  // [nt | total | last]
   const uint32_t bar_full = smem_u32(bars) + worker * 16 * C::kStages, bar_empty = bar_full + 8 * C::kStages;
   const uint32_t bar_x = smem_u32(bars) + 32 * C::kStages;
 
@@ -328,6 +328,9 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   // Row tiles for which this worker has written a partial tile but not yet taken its ticket.  Tickets are
   // taken in batches (one gpu-scope fence per batch, normally one per kernel at the end of the span, when no
   // loads are in flight), by a thread that does not issue TMA loads.
+  // this worker's list of written partial tiles, in the workspace: [row tile | contributors | last?] x pend_cap
+  const int kMaxPend = plan.pend_cap;
+  volatile int* pend = (volatile int*)pend_ws + (size_t)vcta * 3 * kMaxPend;
   int npend = 0;
   auto flush_tickets = [&]() {
     named_bar_sync(bar_id, kConsumers);  // every pending partial-tile store has been issued
@@ -347,7 +350,8 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     named_bar_sync(bar_id, kConsumers);
     for (int i = 0; i < npend; ++i)
       if (pend[2 * kMaxPend + i]) {
-        if constexpr (MODE == 2) finalize_tile_coop<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c, (int*)red, bar_id);
+        // many K slabs: build the list of pieces cooperatively; few: every thread walks the slabs itself
+        if (plan.S > 4) finalize_tile_coop<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c, (int*)red, bar_id);
         else finalize_tile<T>(plan, pieces, counters, y, bias, pend[i], ctid, wwarp, rp, c);
       }
     named_bar_sync(bar_id, kConsumers);
@@ -557,14 +561,14 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         store_tile<T>(v, y, bias, nt, wwarp, rp, c, M, N);
       }
       if (total > 1) {
-        if (ctid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
-        ++npend;
+        if (npend < kMaxPend) {
+          if (ctid == 0) { pend[npend] = nt; pend[kMaxPend + npend] = total; }
+          ++npend;
+        } else if (ctid == 0) {
+          atomicExch(err, 4);  // cannot happen for a plan the host accepted
+        }
       }
       named_bar_sync(bar_id, kConsumers);  // `red` is free again
-      if (npend == kMaxPend) {
-        flush_tickets();
-        npend = 0;
-      }
     }
     if (++kc == sg.cs) { kc = 0; ++nt; }
   }
@@ -641,26 +645,38 @@ bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
   p->slab_cta0[p->S] = 2 * (int)blocks;
   for (int i = p->S - 1; i >= 1; --i)
     if (p->slab_cta0[i] > p->slab_cta0[i + 1] - 2) p->slab_cta0[i] = p->slab_cta0[i + 1] - 2;
-  int maxp = 1;
+  int maxp = 1, cap = 4;
   for (int i = 0; i < p->S; ++i) {
     const int cs = p->slab_chunk0[i + 1] - p->slab_chunk0[i];
     const long long Us = (long long)p->NT * cs;
     long long ctas = p->slab_cta0[i + 1] - p->slab_cta0[i];
     if (ctas > Us) ctas = Us;
     const long long L = Us / ctas;
+    const long long touched = (L + 1 + cs - 1) / cs + 2;  // row tiles one worker's span can touch
+    if (touched > cap) cap = (int)touched;
     const int mp = (int)((cs - 1 + L - 1) / L) + 1;
     if (cs > 1 && mp > maxp) maxp = mp;
     if ((Us + 1) * (p->slab_cta0[i + 1] - p->slab_cta0[i]) >= (1ll << 31)) return false;
   }
   p->maxp = maxp;
+  p->pend_cap = cap;
   return true;
 }
 
 // The ticket counters sit in a fixed-size prefix of the workspace, so that the bytes they occupy never
 // hold anything else (the workspace is zero-filled once and shared by calls of every shape).
 size_t counters_bytes(int) { return (size_t)kMaxRowTiles * 4; }
-size_t plan_workspace(const QmmPlan& p) {
-  return counters_bytes(p.NT) + (size_t)p.S * p.maxp * p.NT * kConsumers * sizeof(float4);
+// then the workers' lists of written partial tiles (sized for one worker pair per SM), then the partial tiles
+size_t pend_bytes(const QmmPlan& p, int device) {
+  // workers of this plan (two per block); an expert-gathered launch always uses one block per SM (or the cap) but at
+  // least one per K slab of its largest case
+  size_t workers = (size_t)p.slab_cta0[p.S];
+  const size_t full = 2 * (size_t)(g_max_blocks > 0 ? g_max_blocks : sm_count(device));
+  if (workers < full) workers = full;
+  return (workers * 3 * p.pend_cap * sizeof(int) + 255) / 256 * 256;
+}
+size_t plan_workspace(const QmmPlan& p, int device) {
+  return counters_bytes(p.NT) + pend_bytes(p, device) + (size_t)p.S * p.maxp * p.NT * kConsumers * sizeof(float4);
 }
 
 bool fast_path_ok(const void* x, const void* wq, const void* sc, const void* bi, int K, int G) {
@@ -737,12 +753,13 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   }
   cudaError_t e;
   unsigned* counters = (unsigned*)ws;
-  float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
+  int* pend_ws = (int*)((uint8_t*)ws + counters_bytes(plan.NT));
+  float4* pieces = (float4*)((uint8_t*)pend_ws + pend_bytes(plan, device));
   const int grid = plan.slab_cta0[plan.S] / 2;
   const bool dependent = pdl_enabled_for_next_launch();
   e = launch_kernel_as(dependent, kern, dim3(grid), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb, (const T*)x,
                        (const T*)bias, (T*)y, pieces, counters, plan, device_error_word(device), dependent ? 1 : 0,
-                       GatherArgs{});
+                       GatherArgs{}, pend_ws);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
@@ -761,7 +778,7 @@ int launch_gather(const void* x, const void* wq, const void* sc, const void* bi,
   const int K = MODE == 1 ? Kb : n_max * Kb, N = MODE == 1 ? n_max * block_rows : block_rows;
   if (!make_plan(M, K, N, G, device, &plan)) return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm: shape too large");
   plan.maxp = C::kSlabKMax / C::BK + 1;  // bound for every number of active slots
-  const size_t need = plan_workspace(plan);
+  const size_t need = plan_workspace(plan, device);
   if (ws == nullptr || ws_bytes < need)
     return fail(DFLASH_ERR_WORKSPACE, "moe_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
   if (((uintptr_t)ws & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
@@ -780,12 +797,14 @@ int launch_gather(const void* x, const void* wq, const void* sc, const void* bi,
   ga.slot_expert = slot_expert; ga.n_dev = n_dev; ga.mode = MODE; ga.block_rows = block_rows;
   ga.block_tiles = block_rows / kBN; ga.cpb = Kb / C::BK; ga.csmax = C::kSlabKMax / C::BK;
   ga.blocks = g_max_blocks > 0 ? g_max_blocks : sm_count(device);
+  if (ga.blocks < plan.S) ga.blocks = plan.S;  // every K slab of the largest case gets a block
   unsigned* counters = (unsigned*)ws;
-  float4* pieces = (float4*)((uint8_t*)ws + counters_bytes(plan.NT));
+  int* pend_ws = (int*)((uint8_t*)ws + counters_bytes(plan.NT));
+  float4* pieces = (float4*)((uint8_t*)pend_ws + pend_bytes(plan, device));
   const bool dependent = pdl_enabled_for_next_launch();
   cudaError_t e = launch_kernel_as(dependent, kern, dim3(ga.blocks), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb,
                                    (const T*)x, (const T*)nullptr, (T*)y, pieces, counters, plan,
-                                   device_error_word(device), dependent ? 1 : 0, ga);
+                                   device_error_word(device), dependent ? 1 : 0, ga, pend_ws);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "moe_qmm launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
@@ -803,7 +822,7 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
   }
   QmmPlan plan;
   if (fast_path_ok(x, wq, sc, bi, K, G) && make_plan(M, K, N, G, device, &plan)) {
-    const size_t need = plan_workspace(plan);
+    const size_t need = plan_workspace(plan, device);
     if (ws == nullptr || ws_bytes < need)
       return fail(DFLASH_ERR_WORKSPACE, "verify_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
     if (((uintptr_t)ws & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
@@ -836,7 +855,7 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
   cudaGetDevice(&device);
   QmmPlan plan;
   if (!make_plan(M, K, N, group_size, device, &plan)) return 256;
-  size_t need = plan_workspace(plan);
+  size_t need = plan_workspace(plan, device);
   if (group_size == 64) {
     const size_t t = tc::workspace_bytes(M, K, N, device, g_max_blocks);
     if (t > need) need = t;
@@ -854,7 +873,7 @@ extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, 
   const int K = mode == 1 ? Kb : n_max * Kb, N = mode == 1 ? n_max * block_rows : block_rows;
   if (!make_plan(M, K, N, 64, device, &plan)) return 0;
   plan.maxp = Cfg<64>::kSlabKMax / Cfg<64>::BK + 1;
-  return plan_workspace(plan);
+  return plan_workspace(plan, device);
 }
 
 extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
