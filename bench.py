@@ -276,7 +276,11 @@ class DenseStepWorkload:
         per_launch = self.bytes["qmm"] / self.n_qmm
         achieved = per_launch / us_per_launch / 1e3
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src,
+                # DRAM bytes per launch, scaled from the ncu captures of both kernels (read + write = 0.99 x the
+                # algorithmic bytes for the mma.sync kernel on configuration 1, 1.03 x for the tcgen05 kernel on gate|up)
+                "traffic": 1.01 * per_launch if self.world == 1 else None,
+                "traffic_source": "ncu captures of single launches, scaled by algorithmic bytes",
+                "peak_source": peak_src,
                 "kernel": "verify matmul = qmm_stream_kernel (mma.sync) + qmm_tc_kernel (tcgen05; shapes with N*K >= 60e6, K <= 8192)",
                 "launches_per_step": self.n_qmm, "algorithmic_bytes_per_launch": per_launch,
                 "us_per_launch": us_per_launch, "matmul_share_of_step": aux_ms / ms_per_step,
