@@ -568,10 +568,19 @@ def run_reference_arm(args, rank, world):
         config = {"workload": cls.name}
     else:
         from dflash_mlx_b200.verify_step import HybridConfig
-        cfg = HybridConfig(max_context=cls.CONTEXT + 64)
-        cb = dense_step_cpu_baseline(cfg, cls.CONTEXT, budget)
+        moe = getattr(cls, "MOE", False)
+        cfg = HybridConfig.moe_cfg5(max_context=cls.CONTEXT + 64) if moe else HybridConfig(max_context=cls.CONTEXT + 64)
+        # MoE: the expected number of distinct routed experts for 16 tokens x top-k uniform routing, + the shared one
+        slots = 0
+        if moe:
+            E, picks = cfg.moe_experts, cfg.block * cfg.moe_top_k
+            slots = int(round(cfg.layers * (E * (1.0 - (1.0 - 1.0 / E) ** picks) + 1)))
+        cb = dense_step_cpu_baseline(cfg, cls.CONTEXT, budget, expert_slots=slots)
         config = {"workload": cls.name, "layers": cfg.layers, "hidden": cfg.hidden, "context": cls.CONTEXT,
                   "block": cfg.block, "vocab": cfg.vocab}
+        if moe:
+            config["experts"] = "%d top-%d + shared, inter %d; %d active (expert, layer) pairs assumed" % (
+                cfg.moe_experts, cfg.moe_top_k, cfg.moe_inter, slots)
     line = {"impl": "reference", "metric": cls.metric, "value": cb["value"], "unit": cls.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
             "higher_is_better": cls.higher_is_better, "scaling": cls.scaling, "vs_baseline": None, "dtype": cls.dtype,
