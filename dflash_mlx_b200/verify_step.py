@@ -211,9 +211,12 @@ class HybridVerifyModel:
         self.ao = z(cfg.q_heads, T, cfg.head_dim)
         self.offset = 0
         self.steps_dev = z(1, dt=torch.int32)
+        self.capture_keys = []         # set_capture_layers(): residual-stream snapshots for the draft model's context feature
+        self.captured = None
         self.offset_dev = None         # set by enable_device_offset(): the cache position then lives on the device
         self.kvlen_dev = None
         self._cycle_graphs = {}
+        self._capture_at = {}
         with torch.cuda.device(dev):
             need = 256
             for L in weights["layers"]:
@@ -321,6 +324,8 @@ class HybridVerifyModel:
         N = self.offset + T
         for i, L in enumerate(self.w["layers"]):
             self._reduce_add_rmsnorm(delta, L["in_norm"])
+            if i in self._capture_at:          # h now holds the hidden state after layer i-1 (key i; key 0 = embeddings)
+                self.captured[self._capture_at[i]].copy_(self.h)
             self._qmm(self.x, L["proj"], self.proj)
             if cfg.is_attention(i):
                 ld = L["proj"]["w"].shape[0]
@@ -389,6 +394,8 @@ class HybridVerifyModel:
                 self._qmm(self.act, L["down"], self.delta)
             delta = self.delta
         self._reduce_add_rmsnorm(delta, self.w["norm"])
+        if cfg.layers in self._capture_at:
+            self.captured[self._capture_at[cfg.layers]].copy_(self.h)
         self._qmm(self.x, self.w["lm_head"], self.logits)
         v_local = self.w["lm_head"]["w"].shape[0]
         self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
@@ -486,6 +493,26 @@ class HybridVerifyModel:
         self._moe_counts = None
         self._armed = armed
         return counts
+
+    # ---- hidden-state capture for the draft model (runtime.py:779-821 `capture_layer_ids`, :182-187) ------------
+    def set_capture_layers(self, capture_layer_ids) -> None:
+        """Keys as in the reference: key k = hidden state (residual stream) after layer k-1, key 0 = the embeddings.
+        Every verify pass then leaves them in ``self.captured[j]`` (``[block, hidden]``, ascending key order)."""
+        keys = sorted(int(k) for k in capture_layer_ids)
+        if keys and (keys[0] < 0 or keys[-1] > self.cfg.layers):
+            raise ValueError("capture key out of range")
+        self.capture_keys = keys
+        self._capture_at = {k: j for j, k in enumerate(keys)}
+        self.captured = torch.zeros(max(len(keys), 1), self.cfg.block, self.cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+        self.graph = None
+        self._cycle_graphs = {}
+
+    def context_feature(self, target_layer_ids) -> torch.Tensor:
+        """``extract_context_feature_from_dict`` (runtime.py:182-187): the captured states of layers
+        ``target_layer_ids`` (keys id + 1) concatenated along the feature axis, ``[block, n * hidden]``.  The caller
+        keeps the first ``accepted + 1`` rows (runtime.py:1389-1392)."""
+        idx = [self._capture_at[int(l) + 1] for l in target_layer_ids]
+        return torch.cat([self.captured[j] for j in idx], dim=-1)
 
     # ---- whole speculative cycle on the device (verify -> accept -> roll back), one graph launch -------------
     def enable_device_offset(self) -> None:

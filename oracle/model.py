@@ -126,13 +126,16 @@ def _embed_local_stack(cfg, L):
     return out
 
 
-def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None, router_logits=None):
+def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None, router_logits=None, captured=None):
     """caches: {"conv": [Lg][keep,cd] bf16, "state": [Lg][Hv,Dv,Dk] f32, "k"/"v": [La][Hk,cap,D] bf16}.
     Returns (logits bf16 [T,V], greedy tokens, new_caches, tapes) without touching the input GDN caches.
     For a tensor-parallel shard, ``reduce(t)`` must return the sum of ``t`` over the ranks (applied to the output of
     every row-parallel projection) and ``gather_tokens(best_value, local_index)`` the global greedy tokens.
-    ``router_logits`` ([layers][T, E+1]) replaces the router matmul of a mixture-of-experts model."""
+    ``router_logits`` ([layers][T, E+1]) replaces the router matmul of a mixture-of-experts model.  ``captured``, when a
+    dict, receives the hidden state after every layer (key layer_index + 1, key 0 = embeddings; runtime.py:805-809)."""
     h = W["embed"][ids.long()].to(BF)
+    if captured is not None:
+        captured[0] = h.clone()
     ig = ia = 0
     new = {"conv": [], "state": [], "k": caches["k"], "v": caches["v"]}
     tapes = []
@@ -171,6 +174,8 @@ def verify_step_ref(cfg, W, ids, caches, offset, reduce=None, gather_tokens=None
         if reduce is not None:
             mlp = reduce(mlp)
         h = (h.float() + mlp.float()).to(BF)
+        if captured is not None:
+            captured[i + 1] = h.clone()
     x = _rms(h, W["norm"], cfg.eps)
     logits = _lin(x, W["lm_head"], cfg.group_size)
     toks = torch.argmax(logits.float(), dim=-1).to(torch.int32)

@@ -213,3 +213,30 @@ def test_device_side_cycle_matches_host_driven_cycle():
     assert dev.sync_offset() == host.offset
     assert len(dev._cycle_graphs) == 2            # one graph per parity of the state buffers, reused afterwards
     assert _lib.lib().dflash_device_error(0) == 0
+
+
+def test_hidden_state_capture_for_the_draft_model(setup):
+    """`capture_layer_ids` semantics of the reference's target forward (key k = residual stream after layer k-1, key 0 =
+    embeddings) and the context feature the draft model is fed (concatenation along the feature axis)."""
+    cfg, W, caches, ids, ctx, m = setup
+    for l in range(len(caches["state"])):
+        m.state[m.cur][l].copy_(caches["state"][l])
+        m.conv[m.cur][l].copy_(caches["conv"][l])
+    for l in range(len(caches["k"])):
+        m.kcache[l].copy_(caches["k"][l]); m.vcache[l].copy_(caches["v"][l])
+    m.offset = ctx
+    m.set_capture_layers({0, 2, cfg.layers})
+    m.arm_rollback()
+    m.verify(ids.cuda())
+    torch.cuda.synchronize()
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    cap = {}
+    om.verify_step_ref(cfg, W, ids, clone(caches), ctx, captured=cap)
+    assert torch.equal(m.captured[0].cpu(), cap[0])                      # embeddings: a gather, exact
+    assert _rel(m.captured[1], cap[2]) <= 3e-2
+    assert _rel(m.captured[2], cap[cfg.layers]) <= 3e-2
+    feat = m.context_feature([1, cfg.layers - 1])                        # target layer ids -> keys id + 1
+    assert feat.shape == (cfg.block, 2 * cfg.hidden)
+    assert torch.equal(feat[:, : cfg.hidden], m.captured[1]) and torch.equal(feat[:, cfg.hidden:], m.captured[2])
+    m.set_capture_layers(())
+    m._armed = False
