@@ -59,8 +59,6 @@ struct GatherArgs {
   const int* slot_expert;
   const int* n_dev;
   int mode, block_rows, block_tiles, cpb, csmax, blocks;
-  int x_swiglu;  // != 0: `x` is a fused gate|up block [M, 2K] and the activations are silu(gate) * up, formed while the
-                 // slab is loaded (the SwiGLU of an MLP fused into its down projection)
 };
 
 template <int G>
@@ -396,8 +394,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       bulk_load_1d(smem_u32(xbuf + r * C::kXRowBytes), x + (size_t)r * K + (size_t)sg.c0 * C::BK,
                    (uint32_t)(slabK * 2), bar_x);
   };
-  const bool xsw = ga.x_swiglu != 0;
-  if (!dependent && !xsw && threadIdx.x == 0) issue_x();
+  if (!dependent && threadIdx.x == 0) issue_x();
   if (ctid == 0) {
 #pragma unroll 1
     for (int j = 0; j < C::kStages - 1; ++j) issue_one();
@@ -405,26 +402,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (dependent) {
     pdl_wait();
     pdl_trigger();
-    if (!xsw && threadIdx.x == 0) issue_x();
-  }
-  if (xsw) {
-    // activations = silu(gate) * up, rounded to T like the stand-alone SwiGLU kernel; all 512 threads, 16 bytes each
-    const int chunks = slabK / 8;
-    const T* gsrc = x + (size_t)sg.c0 * C::BK;
-    for (int i = threadIdx.x; i < M * chunks; i += 2 * kConsumers) {
-      const int r = i / chunks, ch = i - r * chunks;
-      const uint4 gv = *(const uint4*)(gsrc + (size_t)r * 2 * K + ch * 8);
-      const uint4 uv = *(const uint4*)(gsrc + (size_t)r * 2 * K + K + ch * 8);
-      const T* gp = (const T*)&gv;
-      const T* up = (const T*)&uv;
-      T o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float gf = TR::to_float(gp[j]);
-        o[j] = TR::from_float(gf / (1.f + __expf(-gf)) * TR::to_float(up[j]));
-      }
-      ((uint4*)(xbuf + r * C::kXRowBytes))[ch] = *(const uint4*)o;
-    }
+    if (threadIdx.x == 0) issue_x();
   }
 
   // rows >= M of the activation slab are zeros (all 512 threads take part)
@@ -433,7 +411,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       ((uint4*)(xbuf + r * C::kXRowBytes))[i] = make_uint4(0, 0, 0, 0);
   named_bar_sync(3, 2 * kConsumers);
   if (!has_work) return;
-  if (!xsw && !mbar_wait(bar_x, 0)) { aborted = true; atomicExch(err, 2); }
+  if (!mbar_wait(bar_x, 0)) { aborted = true; atomicExch(err, 2); }
 
   float out[4][2][4];
 #pragma unroll
@@ -760,7 +738,7 @@ bool get_map(const void* ptr, int rows, int inner, int kind, CUtensorMap* out) {
 
 template <typename T, int G>
 int launch_stream(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y,
-                  const QmmPlan& plan, void* ws, cudaStream_t st, int device, int x_swiglu = 0) {
+                  const QmmPlan& plan, void* ws, cudaStream_t st, int device) {
   using C = Cfg<G>;
   CUtensorMap tw, ts, tb;
   if (!get_map(wq, plan.N, plan.K / 2, 0, &tw) || !get_map(sc, plan.N, plan.K / G, 1, &ts) ||
@@ -778,12 +756,10 @@ int launch_stream(const void* x, const void* wq, const void* sc, const void* bi,
   int* pend_ws = (int*)((uint8_t*)ws + counters_bytes(plan.NT));
   float4* pieces = (float4*)((uint8_t*)pend_ws + pend_bytes(plan, device));
   const int grid = plan.slab_cta0[plan.S] / 2;
-  GatherArgs gargs{};
-  gargs.x_swiglu = x_swiglu;
   const bool dependent = pdl_enabled_for_next_launch();
   e = launch_kernel_as(dependent, kern, dim3(grid), dim3(kThreads), C::kSmemBytes, st, tw, ts, tb, (const T*)x,
                        (const T*)bias, (T*)y, pieces, counters, plan, device_error_word(device), dependent ? 1 : 0,
-                       gargs, pend_ws);
+                       GatherArgs{}, pend_ws);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;
@@ -885,38 +861,6 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
     if (t > need) need = t;
   }
   return need;
-}
-
-// y = (silu(gate) * up) . W^T with gate_up = [M, 2K] (gate columns first): the MLP's SwiGLU fused into its down
-// projection.  Streaming kernel only; other shapes return DFLASH_ERR_UNSUPPORTED (run the two steps separately).
-extern "C" int dflash_verify_qmm_swiglu(const void* gate_up, const void* w_q, const void* scales, const void* biases,
-                                        const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
-                                        void* workspace, size_t workspace_bytes, void* stream) {
-  if (!gate_up || !w_q || !scales || !biases || !y) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_swiglu: null operand");
-  if (M < 1 || M > 16 || K < 1 || N < 1) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_swiglu: need 1 <= M <= 16");
-  if (group_size != 32 && group_size != 64 && group_size != 128)
-    return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_swiglu: group_size %d", group_size);
-  if (dtype != DFLASH_BF16 && dtype != DFLASH_F16) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_swiglu: dtype %d", dtype);
-  int device = 0;
-  cudaGetDevice(&device);
-  QmmPlan plan;
-  if (!fast_path_ok(gate_up, w_q, scales, biases, K, group_size) || !make_plan(M, K, N, group_size, device, &plan))
-    return fail(DFLASH_ERR_UNSUPPORTED, "verify_qmm_swiglu: shape not taken by the streaming kernel");
-  const size_t need = plan_workspace(plan, device);
-  if (workspace == nullptr || workspace_bytes < need)
-    return fail(DFLASH_ERR_WORKSPACE, "verify_qmm_swiglu needs %zu workspace bytes, got %zu", need, workspace_bytes);
-  if (((uintptr_t)workspace & 255) != 0) return fail(DFLASH_ERR_MISALIGNED, "workspace must be 256-byte aligned");
-  cudaStream_t st = (cudaStream_t)stream;
-  g_last_impl = 1;
-#define DFLASH_SWIGLU_CASE(TT)                                                                                        \
-  switch (group_size) {                                                                                                \
-    case 32: return launch_stream<TT, 32>(gate_up, w_q, scales, biases, bias, y, plan, workspace, st, device, 1);    \
-    case 64: return launch_stream<TT, 64>(gate_up, w_q, scales, biases, bias, y, plan, workspace, st, device, 1);    \
-    default: return launch_stream<TT, 128>(gate_up, w_q, scales, biases, bias, y, plan, workspace, st, device, 1);   \
-  }
-  if (dtype == DFLASH_BF16) { DFLASH_SWIGLU_CASE(__nv_bfloat16) }
-  DFLASH_SWIGLU_CASE(__half)
-#undef DFLASH_SWIGLU_CASE
 }
 
 extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode) {

@@ -14,7 +14,6 @@ Weights are random-initialised (there are no checkpoints here): this module is t
 from __future__ import annotations
 
 import ctypes
-import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -43,7 +42,6 @@ def _declare():
     d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
     d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_f32, _f32, _i32, _vp])
     d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _ll, _i32, _i32, _i32, _i32, _vp])
-    d("dflash_verify_qmm_swiglu", _i32, [_vp] * 6 + [_i32] * 5 + [_vp, ctypes.c_size_t, _vp])
     d("dflash_attn_prep_dev_offset", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 5 + [_vp, _f32, _f32, _i32, _vp])
     d("dflash_verify_sdpa_dev_len", _i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _ll, _ll, _ll, _ll, _f32,
                                            _i32, _i32, _vp, ctypes.c_size_t, _vp])
@@ -213,7 +211,6 @@ class HybridVerifyModel:
         self.ao = z(cfg.q_heads, T, cfg.head_dim)
         self.offset = 0
         self.steps_dev = z(1, dt=torch.int32)
-        self.fuse_swiglu = os.environ.get("DFLASH_FUSE_SWIGLU", "0") == "1"   # measured 1 % slower: off by default
         self.capture_keys = []         # set_capture_layers(): residual-stream snapshots for the draft model's context feature
         self.captured = None
         self.offset_dev = None         # set by enable_device_offset(): the cache position then lives on the device
@@ -392,17 +389,9 @@ class HybridVerifyModel:
                     self._moe_counts.append(self.moe.n_active.clone())
             else:
                 self._qmm(self.x, L["gate_up"], self.gu)
-                inter = L["gate_up"]["w"].shape[0] // 2
-                Wd = L["down"]
-                if self.fuse_swiglu and Wd["w"].shape[1] * 8 == inter and inter % (8 * cfg.group_size) == 0:
-                    # SwiGLU formed while the down projection loads its activations: one launch less per layer
-                    self._chk(lib.dflash_verify_qmm_swiglu(self.gu.data_ptr(), Wd["w"].data_ptr(), Wd["s"].data_ptr(),
-                                                           Wd["b"].data_ptr(), None, self.delta.data_ptr(), T, inter,
-                                                           Wd["w"].shape[0], cfg.group_size, BF, self.qmm_ws.data_ptr(),
-                                                           self.qmm_ws.numel(), st), "dflash_verify_qmm_swiglu")
-                else:
-                    self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, inter, BF, st), "dflash_swiglu")
-                    self._qmm(self.act, Wd, self.delta)
+                self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
+                          "dflash_swiglu")
+                self._qmm(self.act, L["down"], self.delta)
             delta = self.delta
         self._reduce_add_rmsnorm(delta, self.w["norm"])
         if cfg.layers in self._capture_at:

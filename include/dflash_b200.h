@@ -76,14 +76,6 @@ DFLASH_API size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
 DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases, const void* bias,
                       void* y, int M, int K, int N, int group_size, int dtype, void* workspace,
                       size_t workspace_bytes, void* stream);
-/* The same matmul with the MLP's SwiGLU fused into its activation load: gate_up is dtype[M, 2K] (gate columns first,
- * what the fused gate|up projection produces) and y = (silu(gate) * up) . dequant(w_q)^T, the product rounded to dtype
- * before the matmul exactly as a separate SwiGLU kernel would.  Replaces the MLP tail of mlx-lm's decoder layer around
- * the reference's verify linears (dflash_mlx/verify_linear.py:113-145 is called for gate, up and down separately).
- * Only shapes the streaming kernel takes (K % (8*G) == 0, aligned); others return DFLASH_ERR_UNSUPPORTED. */
-DFLASH_API int dflash_verify_qmm_swiglu(const void* gate_up, const void* w_q, const void* scales, const void* biases,
-                                        const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
-                                        void* workspace, size_t workspace_bytes, void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
 /* Kernel choice for bf16 / group-64 shapes: 0 (default) = by shape: the tcgen05 kernel (dequantised operand in
