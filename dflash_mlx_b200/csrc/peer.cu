@@ -4,16 +4,17 @@
 // (dflash_mlx/runtime.py:449-450); here every row-parallel projection (out_proj, o_proj, down) of a tensor-parallel
 // verify step ends in the same pattern: sum the [T, H] block over the ranks, add it to the residual stream, normalise.
 // One kernel does all three.  One CTA per token row:
-//   1. push    : the CTA copies its row of this rank's partial block into slot `rank` of EVERY rank's inbox (plain
-//                16-byte stores through peer pointers; its own inbox included), then one thread publishes the row with a
-//                system-scope release store of the row's sequence number into each rank's flag array.
-//   2. wait    : it polls its OWN flag array (acquire loads) until every rank's flag for this row carries the sequence
-//                number.  The wait is bounded: after a set number of polls the CTA records an error and skips to the end.
-//   3. reduce  : h_out = h_in + sum over ranks (fixed order, fp32) of the inbox rows; x = rmsnorm(h_out) * w.
-// Rows are independent, so there is no grid-wide step.  Inboxes and flags are double buffered on the parity of the
-// sequence number: a rank can be at most one reduction ahead of a peer (it needs that peer's push to finish its own),
-// so a slot is never overwritten while a peer still reads it.  The sequence numbers live on the device (one per row,
-// advanced by the kernel), so a captured CUDA graph can be replayed.  No multicast, no TMA: plain loads and stores.
+//   1. push    : the CTA writes its row of this rank's partial block into slot `rank` of every OTHER rank's inbox as
+//                8-byte entries {two elements, sequence number} (plain stores through peer pointers).  An 8-byte store
+//                is indivisible, so data and "ready" arrive together: no fence, no separate flag, one NVLink latency.
+//   2. wait    : every thread polls ITS entries of its own inbox until they carry the row's sequence number.  The wait
+//                is bounded: after a set number of polls the row records an error and writes nothing.
+//   3. reduce  : h_out = h_in + sum over ranks (fixed order, fp32) of the rows; x = rmsnorm(h_out) * w.
+// Rows are independent, so there is no grid-wide step.  Inboxes are double buffered on the parity of the sequence
+// number: a rank can be at most one reduction ahead of a peer (it needs that peer's push to finish its own), so a slot
+// is never overwritten while a peer still reads it, and an entry left from two reductions ago carries another number.
+// The sequence numbers live on the device (one per row, behind the "flags" buffer, advanced by the kernel), so a
+// captured CUDA graph can be replayed.  No multicast, no TMA: plain loads and stores.
 #include "common.cuh"
 
 namespace dflash {
@@ -37,14 +38,6 @@ struct PeerArgs {
   int* err;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -64,6 +57,15 @@ __device__ __forceinline__ __nv_bfloat16 fromf<__nv_bfloat16>(float v) { return 
 template <>
 __device__ __forceinline__ __half fromf<__half>(float v) { return __float2half_rn(v); }
 
+__device__ __forceinline__ void st_entry(uint2* p, uint32_t data, uint32_t seq) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_entry(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024) peer_reduce_add_rmsnorm_kernel(const PeerArgs a) {
   pdl_wait();
@@ -71,64 +73,80 @@ __global__ void __launch_bounds__(1024) peer_reduce_add_rmsnorm_kernel(const Pee
   __shared__ float scratch[32];
   __shared__ int s_fail;
   const int row = blockIdx.x, tid = threadIdx.x;
-  constexpr int kMaxV = 2;  // vectors per thread (H <= 8 * 2 * blockDim)
+  constexpr int kMaxV = 2;  // 16-byte vectors per thread (H <= 8 * 2 * blockDim)
   const unsigned seq = a.seq[row] + 1u;  // sequence number of this reduction for this row (never 0)
   const int slot = (int)(seq & 1u);
   if (tid == 0) s_fail = 0;
+  __syncthreads();
+  const size_t epr = (size_t)a.H8 * 4;  // 8-byte entries per row: {two elements, sequence number}
 
-  // 1. push this rank's row to every rank's inbox
-  const size_t slot_row = ((size_t)(slot * a.world + a.rank) * a.T + row) * a.H8;
-  for (int i = tid; i < a.H8; i += blockDim.x) {
+  // 1. push: every 32-bit pair of this rank's row goes to slot `rank` of every OTHER rank's inbox together with the
+  //    sequence number, in one 8-byte store - data and "ready" arrive together, no fence, no separate flag
+  uint4 mine[kMaxV];
+  int nv = 0;
+  for (int i = tid; i < a.H8 && nv < kMaxV; i += blockDim.x, ++nv) {
     const uint4 v = a.delta[(size_t)row * a.H8 + i];
-    for (int p = 0; p < a.world; ++p) a.inbox[p][slot_row + i] = v;
-  }
-  __threadfence_system();  // the row's stores are ordered before the flags below
-  __syncthreads();
-  if (tid < a.world) st_release_sys(&a.flags[tid][(slot * a.world + a.rank) * a.T + row], seq);
-
-  // 2. wait for every rank's row (thread q watches rank q)
-  if (tid < a.world) {
-    const unsigned* f = &a.flags[a.rank][(slot * a.world + tid) * a.T + row];
-    bool ok = false;
-    for (uint32_t it = 0; it < a.wait_polls; ++it) {
-      if (ld_acquire_sys(f) == seq) { ok = true; break; }
-      if (it > 64) __nanosleep(it > 4096 ? 400 : 40);
+    mine[nv] = v;
+    const size_t e0 = ((size_t)(slot * a.world + a.rank) * a.T + row) * epr + (size_t)i * 4;
+    for (int p = 0; p < a.world; ++p) {
+      if (p == a.rank) continue;
+      uint2* dst = (uint2*)a.inbox[p] + e0;
+      st_entry(dst + 0, v.x, seq);
+      st_entry(dst + 1, v.y, seq);
+      st_entry(dst + 2, v.z, seq);
+      st_entry(dst + 3, v.w, seq);
     }
-    if (!ok) { atomicExch(&s_fail, 1); atomicExch(a.err, 21); }
   }
-  __syncthreads();
-  if (tid == 0) a.seq[row] = seq;  // advanced even on failure, so that the ranks stay in step afterwards
-  if (s_fail) return;
 
-  // 3. h_out = h_in + sum of the ranks' rows; x = rmsnorm(h_out) * w
+  // 2. + 3. every thread waits for its own entries of the other ranks' rows (bounded), sums them in rank order in fp32,
+  //    adds the residual; then x = rmsnorm(h_out) * w
   float v[kMaxV][8];
   float ss = 0.f;
-  int nv = 0;
-  const uint4* mine = a.inbox[a.rank];
+  nv = 0;
+  const uint2* inbox = (const uint2*)a.inbox[a.rank];
   for (int i = tid; i < a.H8 && nv < kMaxV; i += blockDim.x, ++nv) {
-    const uint4 hv = a.h_in[(size_t)row * a.H8 + i];
-    const T* hp = (const T*)&hv;
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int q = 0; q < a.world; ++q) {
-      const uint4 d = __ldcg(&mine[((size_t)(slot * a.world + q) * a.T + row) * a.H8 + i]);
-      const T* dp = (const T*)&d;
+      uint32_t w4[4];
+      if (q == a.rank) {
+        w4[0] = mine[nv].x; w4[1] = mine[nv].y; w4[2] = mine[nv].z; w4[3] = mine[nv].w;
+      } else {
+        const uint2* src = inbox + ((size_t)(slot * a.world + q) * a.T + row) * epr + (size_t)i * 4;
+        bool ok = false;
+        for (uint32_t it = 0; it < a.wait_polls; ++it) {
+          const uint2 e0 = ld_entry(src), e1 = ld_entry(src + 1), e2 = ld_entry(src + 2), e3 = ld_entry(src + 3);
+          if (e0.y == seq && e1.y == seq && e2.y == seq && e3.y == seq) {
+            w4[0] = e0.x; w4[1] = e1.x; w4[2] = e2.x; w4[3] = e3.x;
+            ok = true;
+            break;
+          }
+          if (*(volatile int*)&s_fail) break;  // another thread of the row already gave up
+          if (it > 64) __nanosleep(it > 4096 ? 400 : 40);
+        }
+        if (!ok) {
+          if (atomicExch(&s_fail, 1) == 0) atomicExch(a.err, 21);
+          w4[0] = w4[1] = w4[2] = w4[3] = 0u;
+        }
+      }
+      const T* dp = (const T*)w4;
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += tof<T>(dp[j]);
     }
-    T o[8];
+    const uint4 hv = a.h_in[(size_t)row * a.H8 + i];
+    const T* hp = (const T*)&hv;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      o[j] = fromf<T>(tof<T>(hp[j]) + acc[j]);
-      v[nv][j] = tof<T>(o[j]);
+      v[nv][j] = tof<T>(fromf<T>(tof<T>(hp[j]) + acc[j]));  // the residual stream is stored in T
       ss += v[nv][j] * v[nv][j];
     }
-    a.h_out[(size_t)row * a.H8 + i] = *(const uint4*)o;
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) scratch[tid >> 5] = ss;
   __syncthreads();
+  if (tid == 0) a.seq[row] = seq;  // advanced even on failure, so that the ranks stay in step afterwards
+  if (s_fail) return;              // a row that gave up writes nothing
   float tot = (tid & 31) < ((blockDim.x + 31) >> 5) ? scratch[tid & 31] : 0.f;
   tot = warp_sum(tot);
   const float inv = rsqrtf(tot / (float)(a.H8 * 8) + a.eps);
@@ -136,10 +154,14 @@ __global__ void __launch_bounds__(1024) peer_reduce_add_rmsnorm_kernel(const Pee
   for (int i = tid; i < a.H8 && k < kMaxV; i += blockDim.x, ++k) {
     const uint4 ww = a.w[i];
     const T* wp = (const T*)&ww;
-    T o[8];
+    T ho[8], xo[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = fromf<T>(v[k][j] * inv * tof<T>(wp[j]));
-    a.x[(size_t)row * a.H8 + i] = *(const uint4*)o;
+    for (int j = 0; j < 8; ++j) {
+      ho[j] = fromf<T>(v[k][j]);
+      xo[j] = fromf<T>(v[k][j] * inv * tof<T>(wp[j]));
+    }
+    a.h_out[(size_t)row * a.H8 + i] = *(const uint4*)ho;
+    a.x[(size_t)row * a.H8 + i] = *(const uint4*)xo;
   }
 }
 
@@ -150,7 +172,7 @@ using namespace dflash;
 
 extern "C" size_t dflash_peer_inbox_bytes(int world, int T_rows, int H) {
   if (world < 1 || world > kMaxWorld || T_rows < 1 || H < 8 || H % 8 != 0) return 0;
-  return (size_t)2 * world * T_rows * H * 2;
+  return (size_t)2 * world * T_rows * H * 4;  // 8-byte entries {two elements, sequence number}, two slots
 }
 extern "C" size_t dflash_peer_flags_bytes(int world, int T_rows) {
   if (world < 1 || world > kMaxWorld || T_rows < 1) return 0;

@@ -259,8 +259,10 @@ DFLASH_API int dflash_moe_swiglu(const void* gate_up, const float* wdense, const
  * dflash_peer_export (a 64-byte CUDA IPC handle to hand to the other processes) and mapped there with
  * dflash_peer_open.  inbox_ptrs[r] / flag_ptrs[r] are HOST arrays of `world` device pointers: rank r's inbox / flags
  * as visible from this process (its own allocation for r == rank).  The kernel writes this rank's block into every
- * inbox, publishes per-row sequence numbers, waits - at most dflash_peer_set_wait_polls() polls, then it records
- * device error 21 and leaves the row unwritten - for the other ranks' rows and finishes add + norm.
+ * other inbox as 8-byte entries {two elements, sequence number} (data and "ready" in one indivisible store), waits -
+ * at most dflash_peer_set_wait_polls() polls per entry, then it records device error 21 and leaves the row
+ * unwritten - for the other ranks' entries and finishes add + norm.  The flags buffer only holds the per-row sequence
+ * numbers of its owner.
  * Every rank must issue the same sequence of calls.  h_out may alias h_in.  world <= 8, H % 8 == 0, H <= 16384.
  * Plain peer loads / stores only (no multicast). */
 DFLASH_API size_t dflash_peer_inbox_bytes(int world, int T_rows, int H);
