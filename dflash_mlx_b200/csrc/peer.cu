@@ -21,7 +21,9 @@ namespace dflash {
 namespace {
 
 constexpr int kMaxWorld = 8;
-uint32_t g_wait_polls = 1u << 22;  // polls before a row gives up; with the back-off below a few seconds
+uint32_t g_wait_polls = 1u << 22;
+int g_protocol = 0;  // 0: by rank count (entries for <= 2 ranks, flags above), 1: entries, 2: flags
+// (every rank of a job must use the same protocol)  // polls before a row gives up; with the back-off below a few seconds
 
 struct PeerArgs {
   const uint4* delta;        // this rank's partial block [T, H8]
@@ -38,6 +40,14 @@ struct PeerArgs {
   int* err;
 };
 
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -56,6 +66,88 @@ template <>
 __device__ __forceinline__ __nv_bfloat16 fromf<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <>
 __device__ __forceinline__ __half fromf<__half>(float v) { return __float2half_rn(v); }
+
+// Variant for more than two ranks: 16-byte vector pushes, one system-scope fence, one flag per (rank, row) that a single
+// thread per rank polls.  With 8 ranks the 8-byte entries of the kernel below cost more NVLink packets and polling
+// traffic than they save in latency (measured: TP8 6.97 ms with flags, 8.32 ms with entries; TP2 8.91 vs 8.51 ms).
+template <typename T>
+__global__ void __launch_bounds__(1024) peer_reduce_flags_kernel(const PeerArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float scratch[32];
+  __shared__ int s_fail;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  constexpr int kMaxV = 2;  // vectors per thread (H <= 8 * 2 * blockDim)
+  const unsigned seq = a.seq[row] + 1u;  // sequence number of this reduction for this row (never 0)
+  const int slot = (int)(seq & 1u);
+  if (tid == 0) s_fail = 0;
+
+  // 1. push this rank's row to every rank's inbox
+  const size_t slot_row = ((size_t)(slot * a.world + a.rank) * a.T + row) * a.H8;
+  for (int i = tid; i < a.H8; i += blockDim.x) {
+    const uint4 v = a.delta[(size_t)row * a.H8 + i];
+    for (int p = 0; p < a.world; ++p) a.inbox[p][slot_row + i] = v;
+  }
+  __threadfence_system();  // the row's stores are ordered before the flags below
+  __syncthreads();
+  if (tid < a.world) st_release_sys(&a.flags[tid][(slot * a.world + a.rank) * a.T + row], seq);
+
+  // 2. wait for every rank's row (thread q watches rank q)
+  if (tid < a.world) {
+    const unsigned* f = &a.flags[a.rank][(slot * a.world + tid) * a.T + row];
+    bool ok = false;
+    for (uint32_t it = 0; it < a.wait_polls; ++it) {
+      if (ld_acquire_sys(f) == seq) { ok = true; break; }
+      if (it > 64) __nanosleep(it > 4096 ? 400 : 40);
+    }
+    if (!ok) { atomicExch(&s_fail, 1); atomicExch(a.err, 21); }
+  }
+  __syncthreads();
+  if (tid == 0) a.seq[row] = seq;  // advanced even on failure, so that the ranks stay in step afterwards
+  if (s_fail) return;
+
+  // 3. h_out = h_in + sum of the ranks' rows; x = rmsnorm(h_out) * w
+  float v[kMaxV][8];
+  float ss = 0.f;
+  int nv = 0;
+  const uint4* mine = a.inbox[a.rank];
+  for (int i = tid; i < a.H8 && nv < kMaxV; i += blockDim.x, ++nv) {
+    const uint4 hv = a.h_in[(size_t)row * a.H8 + i];
+    const T* hp = (const T*)&hv;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int q = 0; q < a.world; ++q) {
+      const uint4 d = __ldcg(&mine[((size_t)(slot * a.world + q) * a.T + row) * a.H8 + i]);
+      const T* dp = (const T*)&d;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += tof<T>(dp[j]);
+    }
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j] = fromf<T>(tof<T>(hp[j]) + acc[j]);
+      v[nv][j] = tof<T>(o[j]);
+      ss += v[nv][j] * v[nv][j];
+    }
+    a.h_out[(size_t)row * a.H8 + i] = *(const uint4*)o;
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) scratch[tid >> 5] = ss;
+  __syncthreads();
+  float tot = (tid & 31) < ((blockDim.x + 31) >> 5) ? scratch[tid & 31] : 0.f;
+  tot = warp_sum(tot);
+  const float inv = rsqrtf(tot / (float)(a.H8 * 8) + a.eps);
+  int k = 0;
+  for (int i = tid; i < a.H8 && k < kMaxV; i += blockDim.x, ++k) {
+    const uint4 ww = a.w[i];
+    const T* wp = (const T*)&ww;
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = fromf<T>(v[k][j] * inv * tof<T>(wp[j]));
+    a.x[(size_t)row * a.H8 + i] = *(const uint4*)o;
+  }
+}
 
 __device__ __forceinline__ void st_entry(uint2* p, uint32_t data, uint32_t seq) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
@@ -179,6 +271,7 @@ extern "C" size_t dflash_peer_flags_bytes(int world, int T_rows) {
   return ((size_t)2 * world * T_rows * sizeof(unsigned) + 255) / 256 * 256 + (size_t)T_rows * sizeof(unsigned);
 }
 
+extern "C" void dflash_peer_set_protocol(int protocol) { g_protocol = (protocol == 1 || protocol == 2) ? protocol : 0; }
 extern "C" void dflash_peer_set_wait_polls(unsigned polls) { g_wait_polls = polls < 1024u ? 1024u : polls; }
 
 extern "C" int dflash_peer_alloc(size_t bytes, void** dev_ptr) {
@@ -252,8 +345,13 @@ extern "C" int dflash_peer_reduce_add_rmsnorm(const void* delta, void* const* in
   if (threads < 32 * ((world + 31) / 32)) threads = 32;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  if (dtype == DFLASH_BF16) e = launch_kernel(peer_reduce_add_rmsnorm_kernel<__nv_bfloat16>, dim3(T_rows), dim3(threads), 0, st, a);
-  else if (dtype == DFLASH_F16) e = launch_kernel(peer_reduce_add_rmsnorm_kernel<__half>, dim3(T_rows), dim3(threads), 0, st, a);
+  const bool entries = g_protocol == 1 || (g_protocol == 0 && world <= 2);
+  if (dtype == DFLASH_BF16)
+    e = entries ? launch_kernel(peer_reduce_add_rmsnorm_kernel<__nv_bfloat16>, dim3(T_rows), dim3(threads), 0, st, a)
+                : launch_kernel(peer_reduce_flags_kernel<__nv_bfloat16>, dim3(T_rows), dim3(threads), 0, st, a);
+  else if (dtype == DFLASH_F16)
+    e = entries ? launch_kernel(peer_reduce_add_rmsnorm_kernel<__half>, dim3(T_rows), dim3(threads), 0, st, a)
+                : launch_kernel(peer_reduce_flags_kernel<__half>, dim3(T_rows), dim3(threads), 0, st, a);
   else return fail(DFLASH_ERR_BAD_ARG, "peer_reduce_add_rmsnorm: dtype %d (want bf16 or f16)", dtype);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "peer_reduce_add_rmsnorm: %s", cudaGetErrorString(e));

@@ -204,6 +204,7 @@ class PeerReducer:
         _lib.declare("dflash_peer_open", i32, [c.c_char_p, c.POINTER(vp)])
         _lib.declare("dflash_peer_close", i32, [vp])
         _lib.declare("dflash_peer_set_wait_polls", None, [c.c_uint])
+        _lib.declare("dflash_peer_set_protocol", None, [i32])
         _lib.declare("dflash_peer_reduce_add_rmsnorm", i32,
                      [vp, c.POINTER(vp), c.POINTER(vp), i32, i32, vp, vp, vp, vp, i32, i32, c.c_float, i32, vp])
         self._check = _lib.check
@@ -265,6 +266,11 @@ class PeerReducer:
         group = [cls(r, world, rows, hidden, device, _wire=(inboxes, flags)) for r in range(world)]
         group[0]._own = inboxes + flags
         return group
+
+    def set_protocol(self, protocol: int) -> None:
+        """0 = by rank count (default), 1 = 8-byte {data, sequence} entries, 2 = vector pushes + fence + flags.  Process-wide;
+        every rank must choose the same."""
+        self.lib.dflash_peer_set_protocol(int(protocol))
 
     def set_wait_polls(self, polls: int) -> None:
         """Bound of the device-side wait for the other ranks' rows (a poll is roughly half a microsecond)."""

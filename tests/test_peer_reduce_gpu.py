@@ -41,10 +41,12 @@ def _rand(T, H, seed):
     return mk(T, H), mk(T, H), (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
 
 
+@pytest.mark.parametrize("protocol", [1, 2])
 @pytest.mark.parametrize("T,H", [(16, 5120), (16, 2048), (5, 264)])
-def test_single_rank_matches_reference_and_alternates_slots(env, T, H):
+def test_single_rank_matches_reference_and_alternates_slots(env, T, H, protocol):
     _lib, PeerReducer = env
     red = PeerReducer(0, 1, T, H, "cuda")
+    red.set_protocol(protocol)
     try:
         for call in range(3):                      # sequence numbers 1, 2, 3: both inbox slots get used
             h, d, w = _rand(T, H, 10 + call)
@@ -56,13 +58,16 @@ def test_single_rank_matches_reference_and_alternates_slots(env, T, H):
             assert float((x.float() - want_x.float()).abs().max()) <= 1e-2 * float(want_x.float().abs().max())
         assert _lib.lib().dflash_device_error(0) == 0
     finally:
+        red.set_protocol(0)
         red.close()
 
 
-def test_two_ranks_on_one_device_and_give_up_path(env):
+@pytest.mark.parametrize("protocol", [1, 2])
+def test_two_ranks_on_one_device_and_give_up_path(env, protocol):
     _lib, PeerReducer = env
     T, H = 16, 5120
     r0, r1 = PeerReducer.local_group(2, T, H, "cuda")
+    r0.set_protocol(protocol)
     lib = _lib.lib()
     try:
         r0.set_wait_polls(2048)                    # process-wide: a wait that cannot succeed ends in about a millisecond
@@ -87,6 +92,7 @@ def test_two_ranks_on_one_device_and_give_up_path(env):
         assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
     finally:
         r0.set_wait_polls(1 << 22)
+        r0.set_protocol(0)
         r0.close()
 
 
