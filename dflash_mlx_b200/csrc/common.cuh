@@ -36,6 +36,7 @@ namespace tc {
 size_t workspace_bytes(int M, int K, int N, int device, int max_blocks);
 int launch(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K, int N,
            void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks);
+void set_roles(int dequant_warps, int issuing_threads);
 }  // namespace tc
 
 #ifdef __CUDACC__

@@ -899,6 +899,9 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
 
 extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }
 extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
+extern "C" void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads) {
+  tc::set_roles(dequant_warps, issuing_threads);
+}
 
 extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,
                                  const void* bias, void* y, int M, int K, int N, int group_size, int dtype,

@@ -28,11 +28,18 @@ def shard_config(cfg, world: int):
         if v % world != 0:
             raise ValueError(f"{name}={v} is not divisible by {world} ranks")
         setattr(c, name, v // world)
+    # KV heads are split while there are at least as many as ranks, else each is replicated on world / kv_heads
+    # ranks; any other ratio would pair a rank's query heads with a wrong (or missing) KV head.
+    if cfg.kv_heads % world != 0 and world % cfg.kv_heads != 0:
+        raise ValueError(f"kv_heads={cfg.kv_heads} and {world} ranks: one must divide the other")
     c.kv_heads = max(1, cfg.kv_heads // world)
     if c.q_heads % c.kv_heads != 0:
         raise ValueError("query heads per rank must be a multiple of KV heads per rank")
     c.intermediate = _round_up(-(-cfg.intermediate // world), 8 * cfg.group_size)
-    c.vocab = -(-cfg.vocab // world)
+    # equal vocabulary shards: a rank's global token id is its local index + rank * vocab_offset_stride
+    if cfg.vocab % world != 0:
+        raise ValueError(f"vocab={cfg.vocab} is not divisible by {world} ranks (pad lm_head to equal shards)")
+    c.vocab = cfg.vocab // world
     c.embed_rows = cfg.vocab            # the embedding table is replicated
     c.vocab_offset_stride = c.vocab
     c.tp_world = world

@@ -405,7 +405,7 @@ class HybridVerifyModel:
             lg = self.logits.view(-1)[: T * v_local].view(T, v_local)
             vals = lg.gather(1, self.tokens.long()[:, None])[:, 0].float()
             rank = torch.distributed.get_rank()
-            pair = torch.stack([vals, (self.tokens + rank * v_local).float()], dim=1).contiguous()
+            pair = torch.stack([vals, (self.tokens + rank * getattr(cfg, 'vocab_offset_stride', v_local)).float()], dim=1).contiguous()
             allp = torch.empty(world * T, 2, dtype=torch.float32, device=self.dev)
             self.all_gather(allp, pair)
             allp = allp.view(world, T, 2)

@@ -83,6 +83,9 @@ DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
  * mma.sync streaming kernel; 1 = mma.sync kernel always; 2 = tcgen05 kernel wherever it applies.
  * Other dtypes / group sizes always use the mma.sync kernel. */
 DFLASH_API void dflash_verify_qmm_set_impl(int impl);
+/* Tuning knob of the tcgen05 kernel: how many warps dequantise (8, 12 or 16) and how many threads issue MMAs
+ * (2..4).  Other values leave the setting alone.  Results do not depend on it beyond fp32 summation order. */
+DFLASH_API void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
 DFLASH_API int dflash_verify_qmm_last_impl(void);
 /* Introspection for host-side tests (needs no GPU): writes the streaming kernel's work partition for a

@@ -129,3 +129,34 @@ def max_rel_err(y: torch.Tensor, y_ref: torch.Tensor) -> float:
 
 def as_numpy_u32(w_q: torch.Tensor) -> np.ndarray:
     return w_q.cpu().numpy().view(np.uint32)
+
+
+# ---- the reference's own parity cases (tests/test_verify_qmm_parity.py:30-64), made reproducible -------------------
+REAL_MLP_SHAPES = [("gate_proj", 16, 5120, 17408), ("up_proj", 16, 5120, 17408), ("down_proj", 16, 17408, 5120)]
+
+
+def reference_sweep_shapes(n: int = 30, seed: int = 0xDF1A):
+    """The 30 random shapes of the reference's sweep (test_verify_qmm_parity.py:43-53): same generator, same seed,
+    same draw order, so the shapes are the reference's own."""
+    rng = np.random.default_rng(seed)
+    m_levels = [1, 4, 8, 12, 15, 16]
+    shapes = []
+    for i in range(n):
+        m = m_levels[i % len(m_levels)]
+        k = int(rng.integers(2, 40)) * 64
+        nn = int(rng.integers(1, 64)) * 8
+        shapes.append((f"rnd{i:02d}", m, k, nn))
+    return shapes
+
+
+def reference_case_inputs(case_seed: int, m: int, k: int, n: int, group_size: int = 64, dtype=torch.bfloat16):
+    """Inputs of one reference parity case (test_verify_qmm_parity.py:56-64): x, w ~ N(0,1)/sqrt(K) drawn with numpy's
+    default_rng, cast to ``dtype``, the weight quantised from its ``dtype`` value.  The reference seeds each case with
+    Python's ``hash()`` of a tuple holding a str, which changes from process to process; a fixed ``case_seed`` takes
+    its place."""
+    rng = np.random.default_rng(case_seed)
+    scale = 1.0 / np.sqrt(max(k, 1))
+    x = torch.from_numpy((rng.standard_normal((m, k)) * scale).astype(np.float32)).to(dtype)
+    w = torch.from_numpy((rng.standard_normal((n, k)) * scale).astype(np.float32)).to(dtype)
+    w_q, s, b = quantize_affine(w.float(), group_size, 4, out_dtype=dtype)
+    return x, w_q, s, b
