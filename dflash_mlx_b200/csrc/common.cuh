@@ -37,6 +37,8 @@ size_t workspace_bytes(int M, int K, int N, int device, int max_blocks);
 int launch(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K, int N,
            void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks);
 void set_roles(int dequant_warps, int issuing_threads);
+void set_k_parts(int k_parts);
+void set_stamps(void* dev);
 }  // namespace tc
 
 #ifdef __CUDACC__
@@ -62,7 +64,10 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 }
 
 // ---- device helpers -----------------------------------------------------------------------
-constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait gives up (a fraction of a second)
+#ifndef DFLASH_WAIT_LIMIT
+#define DFLASH_WAIT_LIMIT (1u << 22)
+#endif
+constexpr uint32_t kWaitLimit = DFLASH_WAIT_LIMIT;  // polls before a wait gives up (a fraction of a second)
 #ifndef DFLASH_SPIN_POLLS
 #define DFLASH_SPIN_POLLS 2
 #endif
@@ -111,6 +116,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+// The same wait for warps that may wait long next to warps that compute: every poll lets the hardware suspend the thread
+// for up to ~1 us (it resumes as soon as the phase completes), so a waiting warp issues almost nothing.  Bounded:
+// kWaitLimit / 4 polls of at most that long.
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit / 4; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000u)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
@@ -130,6 +152,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+// 3-D tiled TMA load (x innermost), completion counted on an mbarrier, with an L2 cache-policy hint.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
       : "memory");
 }
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.

@@ -619,18 +619,20 @@ __global__ void __launch_bounds__(256) qmm_general_kernel(const T* __restrict__ 
 
 // ------------------------------------------------------------------------------------------
 int g_max_blocks = 0;
-int g_impl = 0;  // 0 = by shape (tcgen05 kernel for the large shapes it is measured faster on), 1 = mma.sync
+int g_k_parts = 0;  // > 0: K is cut into at least this many slabs (dflash_verify_qmm_set_k_parts)
+int g_impl = 0;  // 0 = by shape and dtype (tcgen05 kernel wherever it applies: bf16, group 64, K % 512 == 0), 1 = mma.sync
                  // streaming kernel always, 2 = tcgen05 kernel wherever it applies
-long long g_tc_min_weights = 60ll * 1000 * 1000;  // N*K from which impl 0 picks the tcgen05 kernel
+long long g_tc_min_weights = 0;  // N*K from which impl 0 picks the tcgen05 kernel (measured faster at every size)
 thread_local int g_last_impl = 0;  // 1 = mma.sync streaming kernel, 2 = tcgen05 kernel, 3 = general kernel
 
-bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p) {
+bool make_plan(int M, int K, int N, int G, int device, QmmPlan* p, bool gathered = false) {
   const int BK = 8 * G;
   const int C = K / BK;
   const int csmax = (G == 128 ? 1024 : 2048) / BK;
   p->M = M; p->K = K; p->N = N;
   p->NT = (N + kBN - 1) / kBN;
   p->S = (C + csmax - 1) / csmax;
+  if (!gathered && g_k_parts > p->S) p->S = g_k_parts < C ? g_k_parts : C;  // (the device-side re-plan has no such knob)
   if (p->S > kMaxSlabs || p->NT > kMaxRowTiles) return false;
   for (int i = 0; i <= p->S; ++i) p->slab_chunk0[i] = (int)((long long)i * C / p->S);
   const long long U = (long long)p->NT * C;
@@ -776,7 +778,7 @@ int launch_gather(const void* x, const void* wq, const void* sc, const void* bi,
   cudaGetDevice(&device);
   QmmPlan plan;
   const int K = MODE == 1 ? Kb : n_max * Kb, N = MODE == 1 ? n_max * block_rows : block_rows;
-  if (!make_plan(M, K, N, G, device, &plan)) return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm: shape too large");
+  if (!make_plan(M, K, N, G, device, &plan, true)) return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm: shape too large");
   plan.maxp = C::kSlabKMax / C::BK + 1;  // bound for every number of active slots
   const size_t need = plan_workspace(plan, device);
   if (ws == nullptr || ws_bytes < need)
@@ -815,7 +817,7 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
                int N, int G, void* ws, size_t ws_bytes, cudaStream_t st) {
   int device = 0;
   cudaGetDevice(&device);
-  if ((g_impl == 2 || (g_impl == 0 && (long long)N * K >= g_tc_min_weights && K <= 8192)) && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
+  if ((g_impl == 2 || (g_impl == 0 && (long long)N * K >= g_tc_min_weights)) && G == 64 && sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value && fast_path_ok(x, wq, sc, bi, K, G) &&
       ((uintptr_t)ws & 255) == 0) {
     const int rc = tc::launch(x, wq, sc, bi, bias, y, M, K, N, ws, ws_bytes, st, device, g_max_blocks);
     if (rc <= 0) { g_last_impl = 2; return rc; }
@@ -847,6 +849,10 @@ int launch_any(const void* x, const void* wq, const void* sc, const void* bi, co
 using namespace dflash;
 
 extern "C" void dflash_verify_qmm_set_max_blocks(int max_blocks) { g_max_blocks = max_blocks < 0 ? 0 : max_blocks; }
+extern "C" void dflash_verify_qmm_set_k_parts(int k_parts) {
+  g_k_parts = k_parts < 0 ? 0 : k_parts;
+  tc::set_k_parts(g_k_parts);
+}
 
 extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int group_size) {
   if (M < 1 || K < 1 || N < 1 || (group_size != 32 && group_size != 64 && group_size != 128)) return 0;
@@ -871,7 +877,7 @@ extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, 
   cudaGetDevice(&device);
   QmmPlan plan;
   const int K = mode == 1 ? Kb : n_max * Kb, N = mode == 1 ? n_max * block_rows : block_rows;
-  if (!make_plan(M, K, N, 64, device, &plan)) return 0;
+  if (!make_plan(M, K, N, 64, device, &plan, true)) return 0;
   plan.maxp = Cfg<64>::kSlabKMax / Cfg<64>::BK + 1;
   return plan_workspace(plan, device);
 }
@@ -899,6 +905,7 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
 
 extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }
 extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
+extern "C" void dflash_verify_qmm_set_stamps(void* dev_buffer) { tc::set_stamps(dev_buffer); }
 extern "C" void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads) {
   tc::set_roles(dequant_warps, issuing_threads);
 }

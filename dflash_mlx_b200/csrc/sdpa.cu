@@ -12,6 +12,8 @@
 // and K/V fragments via ldmatrix from XOR-swizzled shared memory), online softmax in fp32 registers, K/V
 // blocks double-buffered with cp.async.  Each CTA writes un-normalised fp32 (O, max, sum) partials.
 // Pass 2: per (head, row) the partials are rescaled by exp2(max_s - max) and summed (kernels.py:595-637).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dflash {
@@ -426,6 +428,7 @@ namespace {
 constexpr size_t kStaticScratchBytes = 32u << 20;
 static __device__ __align__(256) unsigned char g_sdpa_static_scratch[kStaticScratchBytes];
 void* g_static_scratch_ptr[64] = {};  // device address of the array, per device (host code cannot use the symbol itself)
+std::mutex g_static_mu;
 }  // namespace
 
 extern "C" size_t dflash_verify_sdpa_static_capacity(void) { return kStaticScratchBytes; }
@@ -446,15 +449,20 @@ extern "C" int dflash_verify_sdpa_static(const void* q, const void* k, const voi
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
   if (device < 0 || device >= 64) return fail(DFLASH_ERR_UNSUPPORTED, "verify_sdpa_static: device index %d", device);
-  if (g_static_scratch_ptr[device] == nullptr) {
-    // one-time set-up on this device (it is current): resolve the array's device address
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_sdpa_static_scratch);
-    if (e != cudaSuccess || p == nullptr)
-      return fail(DFLASH_ERR_LAUNCH, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
-    g_static_scratch_ptr[device] = p;
+  void* scratch = nullptr;
+  {
+    // one-time set-up on this device (it is current): resolve the array's device address; the lock makes a first
+    // call from two host threads safe
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_scratch_ptr[device] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_sdpa_static_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(DFLASH_ERR_LAUNCH, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+      g_static_scratch_ptr[device] = p;
+    }
+    scratch = g_static_scratch_ptr[device];
   }
   return dflash_verify_sdpa(q, k, v, mask, out, B, Hq, Hk, N, D, k_head_stride, k_seq_stride, v_head_stride,
-                            v_seq_stride, scale, dtype, num_splits, g_static_scratch_ptr[device], kStaticScratchBytes,
-                            stream);
+                            v_seq_stride, scale, dtype, num_splits, scratch, kStaticScratchBytes, stream);
 }

@@ -8,6 +8,7 @@ verify_qmm.py:276-280); both run the same sm_100a kernels, so they agree bit for
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -42,9 +43,34 @@ def _should_use_verify(x: torch.Tensor, group_size: int, bits: int, transpose: b
     return _rows(x) == 16
 
 
+_VARIANTS = {"auto": 0, "mma.sync": 1, "mma2big": 1, "tcgen05": 2, "mma2big_pipe": 2}
+_applied_env = None
+
+
+def _apply_env(lib) -> None:
+    """The reference's tuning variables, read at every call as it does (verify_qmm.py:15-16, 297) and handed to the
+    library when they change: ``DFLASH_VERIFY_VARIANT`` = ``auto`` (kernel by shape), ``mma.sync`` or ``tcgen05``
+    (the reference's own names ``mma2big`` / ``mma2big_pipe`` select the kernel without / with the pipelined
+    K split of the tensor-memory path), ``DFLASH_VERIFY_QMM_KPARTS`` = least number of K slabs.  Unset variables
+    leave whatever ``dflash_verify_qmm_set_impl`` / ``_set_k_parts`` last set."""
+    global _applied_env
+    env = (os.environ.get("DFLASH_VERIFY_VARIANT"), os.environ.get("DFLASH_VERIFY_QMM_KPARTS"))
+    if env == _applied_env:
+        return
+    _applied_env = env
+    variant, kparts = env
+    if variant is not None:
+        if variant not in _VARIANTS:
+            raise ValueError(f"DFLASH_VERIFY_VARIANT={variant!r}: expected one of {sorted(_VARIANTS)}")
+        _lib.declare("dflash_verify_qmm_set_impl", None, [ctypes.c_int])(_VARIANTS[variant])
+    if kparts is not None:
+        _lib.declare("dflash_verify_qmm_set_k_parts", None, [ctypes.c_int])(max(0, int(kparts)))
+
+
 def _launch(x2: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bias, group_size: int,
             out: torch.Tensor) -> None:
     lib = _lib.lib()
+    _apply_env(lib)
     m, k = x2.shape
     n = w.shape[0]
     dev = x2.device

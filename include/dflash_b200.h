@@ -78,14 +78,25 @@ DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* sca
                       size_t workspace_bytes, void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
-/* Kernel choice for bf16 / group-64 shapes: 0 (default) = by shape: the tcgen05 kernel (dequantised operand in
- * tensor memory, accumulator in TMEM) for N*K >= 60e6 with K <= 8192, where it is measured faster, else the
- * mma.sync streaming kernel; 1 = mma.sync kernel always; 2 = tcgen05 kernel wherever it applies.
- * Other dtypes / group sizes always use the mma.sync kernel. */
+/* Tuning knob with the meaning of the reference's DFLASH_VERIFY_QMM_KPARTS (dflash_mlx/verify_qmm.py:297): K is cut
+ * into at least `k_parts` slabs whose partial sums are combined in a fixed order (0 = as few as the kernel's
+ * activation buffer allows, the default). */
+DFLASH_API void dflash_verify_qmm_set_k_parts(int k_parts);
+/* Kernel choice: 0 (default) = the tcgen05 kernel (weights dequantised to bf16 in tensor memory, accumulator in TMEM)
+ * wherever it applies - bf16, group size 64, K % 512 == 0, 16-byte aligned operands - else the mma.sync streaming
+ * kernel; 1 = mma.sync kernel always (exact integer nibbles, scale applied to the accumulator: the variant for error
+ * attribution); 2 = as 0. */
 DFLASH_API void dflash_verify_qmm_set_impl(int impl);
-/* Tuning knob of the tcgen05 kernel: how many warps dequantise (8, 12 or 16) and how many threads issue MMAs
- * (2..4).  Other values leave the setting alone.  Results do not depend on it beyond fp32 summation order. */
+/* Tuning knob of the tcgen05 kernel: how many warps dequantise (8 or 12); the number of threads that
+ * issue MMAs is fixed (6) and the second argument is ignored.  Other values leave the setting alone.  Results do not depend on it beyond fp32 summation order. */
 DFLASH_API void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads);
+/* Measurement aid: with a device buffer of 20 * 8 bytes per thread block (one block per SM) the tcgen05 kernel
+ * records, per block, %globaltimer at entry [0] and exit [1] and the SM clock at entry [2], set-up done [3], activation
+ * slab in shared memory [4], first weight stage landed [5], first operand ready for the tensor core [6], last MMA
+ * issued [7], last accumulators ready [8], last output written [9], exit [10]; cycles issuing thread 0 waited [11] /
+ * issued [12]; cycles dequant warp 0 waited for a stage [13], spent in loads + arithmetic [14], waited for its operand
+ * buffer [15], spent in the TMEM store and hand-over [17].  NULL (default) turns it off. */
+DFLASH_API void dflash_verify_qmm_set_stamps(void* dev_buffer);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
 DFLASH_API int dflash_verify_qmm_last_impl(void);
 /* Introspection for host-side tests (needs no GPU): writes the streaming kernel's work partition for a
