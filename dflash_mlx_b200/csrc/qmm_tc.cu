@@ -59,6 +59,7 @@ constexpr int kEpWarps = 4, kXWarps = 4;
 constexpr int kEp = kEpWarps * 32;
 constexpr int kTileF4 = 512;             // float4 entries of one fp32 partial tile: [token quad][row]
 constexpr int kStages = 4;
+constexpr int kEarlyUnits = 2;           // units whose weights are requested before the wait on the previous kernel
 constexpr int kWBytes = kRows * (kBK / 2);    // 32 KB
 constexpr int kSBBytes = kRows * 16;          // 2 KB
 constexpr int kXOff = kWBytes + 2 * kSBBytes; // the activation tile of a stage: 8 slabs of [16 tok][64 k] bf16, 128B swizzle
@@ -71,6 +72,10 @@ constexpr int kNumBars = 3 * kStages + 2 * kNA + 2;  // full, empty, x_landed, a
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8 * kNumBars + 128;
 constexpr uint32_t kTmemCols = 512;      // operand buffers at columns 0..383, accumulators at 384..479
 constexpr uint32_t kDCol0 = 64 * kNA;
+#ifndef DFLASH_TC_STAGGER_NS
+#define DFLASH_TC_STAGGER_NS 0
+#endif
+constexpr unsigned kStaggerNs = DFLASH_TC_STAGGER_NS;
 constexpr float kPow2Scale = 0x1p101f;   // 2^(133 - 32)
 constexpr float kPow2Scale16 = 0x1p97f;  // the same for a nibble that sits 4 bits higher
 constexpr float kPow2Bias = 0x1p-32f;
@@ -248,7 +253,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               unsigned long long* __restrict__ stamps) {
   using R = Roles<NDQ>;
   // Optional time stamps (dflash_verify_qmm_set_stamps): 16 words per CTA, [0] / [1] = %globaltimer at entry / exit,
-  // [2..10] = this SM's clock at entry, set-up done, previous kernel done (loader), first stage landed, first operand
+  // [2..10] = this SM's clock at entry, set-up done, first activation tile landed, first stage complete, first operand
   // ready for the MMA, last MMA issued, last accumulators ready, last output written, exit.
   unsigned long long* const stamp = stamps ? stamps + (size_t)blockIdx.x * 16 : nullptr;
   auto mark = [&](int i) { if (stamp) stamp[i] = (unsigned long long)clock64(); };
@@ -291,7 +296,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     mbar_init(bar_dfree, kEpWarps);
     mbar_fence_init();
   }
-  if (warp == R::kProducerWarp) tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+  if (warp == R::kProducerWarp) {
+    if (lane == 0) {  // the first TMA request through a tensor map waits for the map itself: fetch all four now
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmS) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    }
+    tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -304,10 +317,13 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (lane == 0) {
       const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
       int stage = 0, nt = nt0, kc = (int)(u_begin % (unsigned)C);
-      // The activation tiles (the previous kernel's output) may only be requested once that kernel has finished:
-      // they run behind the weights until the ring is full of weights, then the wait is taken and they catch up.
-      int xstage = 0, xkc = kc;
+      // x is the previous kernel's output, the weights are nobody's: the weights of the first kEarlyUnits units are
+      // requested at once, then the previous kernel is waited for, then every unit's activation tile is requested with
+      // (right after) its weights.  Requests are served in order, so an activation tile asked for behind the whole ring
+      // of weights would land ~3 us late; behind two units it lands as soon as the MMA could use it.
+      uint32_t par = 1;
       unsigned xu = u_begin;  // next unit whose activation tile is still owed
+      int xstage = 0, xkc = kc;
       auto request_x = [&](unsigned upto) {
         while (xu < upto) {
           const uint32_t xb = bar_xraw + 8 * xstage;
@@ -319,12 +335,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       };
       bool waited = false;
-      uint32_t par = 1;
       for (unsigned u = u_begin; u < u_end; ++u) {
-        if (!waited && u - u_begin == (unsigned)kStages) {
+        if (!waited && u - u_begin == (unsigned)kEarlyUnits) {
           pdl_wait();
           waited = true;
-          request_x(u);  // before the wait below: those units cannot finish without their activations
+          request_x(u);
         }
         if (!mbar_wait_quiet(bar_empty + 8 * stage, par)) { TC_TRACE(11, u - u_begin); atomicCAS(err, 0, 11 | ((int)(u - u_begin) << 8)); break; }
         const uint32_t full = bar_full + 8 * stage, dst = smem_u32(stages + stage * kStageBytes);
@@ -395,12 +410,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // then permuted in place to (0,4,1,5,2,6,3,7), the order in which the dequantised pairs come out.  A thread rewrites
     // its own chunks, so nothing is exchanged.
     const int xt = tid - R::kXWarp0 * 32;  // 0..127
-    if (xt == 0) mark(4);
     bool aborted = false;
     int stage = 0;
     uint32_t par = 0;
     for (unsigned u = u_begin; u < u_end; ++u) {
       if (!aborted && !mbar_wait_quiet(bar_xraw + 8 * stage, par)) { aborted = true; TC_TRACE(17, u - u_begin); atomicCAS(err, 0, 17 | ((int)(u - u_begin) << 8)); }
+      if (xt == 0 && u == u_begin) mark(4);
       uint4* xs = (uint4*)(stages + stage * kStageBytes + kXOff);
       uint4 v[8];
 #pragma unroll
@@ -536,7 +551,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 namespace {
 
 unsigned long long* g_stamps = nullptr;  // dflash_verify_qmm_set_stamps
-int g_ndq = 8;  // dequant warps of the launched instantiation (dflash_verify_qmm_set_tc_roles)
+int g_ndq = 12;  // dequant warps of the launched instantiation (dflash_verify_qmm_set_tc_roles)
 
 bool make_plan(int M, int K, int N, int device, int max_blocks, Plan* p) {
   p->M = M; p->K = K; p->N = N;

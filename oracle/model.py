@@ -24,10 +24,15 @@ from . import sdpa as osd
 
 BF = torch.bfloat16
 
+# False: the stock path (``mx.quantized_matmul``: weights dequantised in fp32).  True: the reference's own verify kernels,
+# which round every dequantised weight to the activation dtype first (dflash_mlx/verify_qmm.py:75) - what a 16-row
+# verify pass runs when DFLASH_VERIFY_QMM=1, and what the tensor-core kernel of this build reproduces.
+KERNEL_ROUNDING = False
+
 
 def _lin(x, W, G):
     """bf16 x @ dequant(W).T -> bf16 (fp32 accumulate)."""
-    return oq.qmm_ref(x, W["w"], W["s"], W["b"], G, out_dtype=BF)
+    return oq.qmm_ref(x, W["w"], W["s"], W["b"], G, out_dtype=BF, kernel_rounding=KERNEL_ROUNDING)
 
 
 def _rms(x, w, eps):

@@ -6,13 +6,23 @@ top-8 + a shared expert of intermediate 512, 16 query / 2 KV heads, context 8192
 vocabulary is cut to 8192 rows to keep the CPU oracle to seconds (the full-width lm_head is covered by the matmul
 tests).  Tolerances: logits max-rel <= 3e-2 (bf16 activations through two layers), greedy tokens identical on every row
 whose top-2 margin in the oracle exceeds that bound (the number of such rows is printed and asserted), first-layer
-tape / state <= 1e-4."""
+tape / state <= 2e-3 (their inputs are bf16 outputs of the input projection: one bf16 ulp of a matmul output moves
+them by that much; the recurrence itself is held to 1e-4 on identical inputs in tests/test_gdn_gpu.py).  The oracle
+dequantises as the reference's verify kernels do (weights rounded to bf16)."""
 import pytest
 import torch
 
 from oracle import model as om
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _verify_kernel_numerics():
+    """The oracle dequantises like the reference's verify kernels (weights rounded to bf16, verify_qmm.py:75)."""
+    old, om.KERNEL_ROUNDING = om.KERNEL_ROUNDING, True
+    yield
+    om.KERNEL_ROUNDING = old
 
 
 def _rel(a, b):
@@ -75,8 +85,8 @@ def test_dense_layers_at_configuration_4_dimensions():
     torch.cuda.synchronize()
     assert _rel(logits, ref_logits) <= 3e-2
     _check_tokens(m, ref_logits, ref_toks, 3e-2)
-    assert _rel(m.tape[0], tapes[0]["tape"]) <= 1e-4
-    assert _rel(m.state[m.cur ^ 1][0], ref_new["state"][0]) <= 1e-4
+    assert _rel(m.tape[0], tapes[0]["tape"]) <= 2e-3
+    assert _rel(m.state[m.cur ^ 1][0], ref_new["state"][0]) <= 2e-3
     # the attention layer's new K rows (q/k norm + RoPE at positions 4096..4111) and V rows in the cache
     assert _rel(m.kcache[0][:, ctx:ctx + 16], ref_new["k"][0][:, ctx:ctx + 16]) <= 2e-2
     assert _rel(m.vcache[0][:, ctx:ctx + 16], ref_new["v"][0][:, ctx:ctx + 16]) <= 2e-2
@@ -103,7 +113,7 @@ def test_moe_layers_at_configuration_5_dimensions():
     ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, ids, clone(caches), ctx, router_logits=injected)
     assert _rel(logits, ref_logits) <= 3e-2
     _check_tokens(m, ref_logits, ref_toks, 3e-2)
-    assert _rel(m.tape[0], tapes[0]["tape"]) <= 1e-4
+    assert _rel(m.tape[0], tapes[0]["tape"]) <= 2e-3
     # and the router itself: the CUDA router logits against the oracle's router matmul on the oracle's activations
     free_logits, _, _, _ = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
     assert _rel(logits, free_logits) <= 6e-2          # a near-tie in a top-8 choice may swap one expert
