@@ -35,7 +35,8 @@ bool pdl_enabled_for_next_launch();
 namespace tc {
 size_t workspace_bytes(int M, int K, int N, int device, int max_blocks);
 int launch(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K, int N,
-           void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks);
+           void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks,
+           const dflash_qmm_epilogue* epilogue = nullptr);
 void set_roles(int dequant_warps, int issuing_threads);
 void set_k_parts(int k_parts);
 void set_stamps(void* dev);

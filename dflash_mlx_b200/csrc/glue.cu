@@ -134,6 +134,41 @@ __global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ ids,
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// The same, plus what the first fused matmul of a step takes instead of a normalised x: scaled[t, :] = h[t, :] * next_w
+// and ssq[t] = sum of h[t, :]^2 (one partial sum per token: in_parts = 1).
+template <typename T>
+__global__ void __launch_bounds__(256) embed_scaled_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                                           const T* __restrict__ next_w, T* __restrict__ h,
+                                                           T* __restrict__ scaled, float* __restrict__ ssq, int H, int V) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float scratch[32];
+  int id = ids[blockIdx.x];
+  id = min(max(id, 0), V - 1);
+  const uint4* src = (const uint4*)(table + (size_t)id * H);
+  const uint4* wv = (const uint4*)next_w;
+  uint4* dst = (uint4*)(h + (size_t)blockIdx.x * H);
+  uint4* dsc = (uint4*)(scaled + (size_t)blockIdx.x * H);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 a = src[i], w = wv[i];
+    uint4 o;
+    const T* ap = (const T*)&a;
+    const T* wp = (const T*)&w;
+    T* op = (T*)&o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = tof<T>(ap[j]);
+      ss += v * v;
+      op[j] = fromf<T>(v * tof<T>(wp[j]));
+    }
+    dst[i] = a;
+    dsc[i] = o;
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) ssq[blockIdx.x] = ss;
+}
+
 // out[t] = index of the first maximum of logits[t, :]  (greedy tokens, runtime.py:90-98)
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int V) {
@@ -497,6 +532,15 @@ extern "C" int dflash_embed(const int* ids, const void* table, void* h, int T_ro
   if (!ids || !table || !h || T_rows < 1 || H % 8 != 0) return fail(DFLASH_ERR_BAD_ARG, "embed: bad argument (H %% 8 == 0)");
   cudaStream_t st = (cudaStream_t)stream;
   DFLASH_DISPATCH(dtype, (launch_kernel(embed_kernel<T>, dim3(T_rows), dim3(256), 0, st, ids, (const T*)table, (T*)h, H, V)));
+}
+
+extern "C" int dflash_embed_scaled(const int* ids, const void* table, const void* next_w, void* h, void* scaled, float* ssq,
+                                   int T_rows, int H, int V, int dtype, void* stream) {
+  if (!ids || !table || !next_w || !h || !scaled || !ssq || T_rows < 1 || T_rows > 16 || H % 8 != 0)
+    return fail(DFLASH_ERR_BAD_ARG, "embed_scaled: bad argument (1..16 rows, H %% 8 == 0)");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (launch_kernel(embed_scaled_kernel<T>, dim3(T_rows), dim3(256), 0, st, ids, (const T*)table, (const T*)next_w,
+                                        (T*)h, (T*)scaled, ssq, H, V)));
 }
 
 extern "C" int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream) {

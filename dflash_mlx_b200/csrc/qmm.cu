@@ -927,6 +927,37 @@ extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* sca
   return fail(DFLASH_ERR_BAD_ARG, "verify_qmm: dtype %d (want bf16 or f16)", dtype);
 }
 
+extern "C" int dflash_verify_qmm_fused_supported(int M, int K, int N, int group_size, int dtype) {
+  return (M >= 1 && M <= 16 && N >= 1 && group_size == 64 && dtype == DFLASH_BF16 && K >= 512 && K % 512 == 0) ? 1 : 0;
+}
+
+extern "C" int dflash_verify_qmm_fused(const void* x, const void* w_q, const void* scales, const void* biases,
+                                       const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
+                                       const dflash_qmm_epilogue* ep, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  if (!x || !w_q || !scales || !biases || !y || !ep) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: null operand");
+  if (!dflash_verify_qmm_fused_supported(M, K, N, group_size, dtype))
+    return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm_fused: needs bf16, group size 64, K %% 512 == 0, M in 1..16 (M=%d K=%d N=%d G=%d)",
+                M, K, N, group_size);
+  if (ep->mode < 0 || ep->mode > 2) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: mode %d", ep->mode);
+  if (ep->in_ssq != nullptr && (ep->in_parts < 1 || !(ep->in_dim > 0.f) || ((uintptr_t)ep->in_ssq & 15) != 0))
+    return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: in_ssq needs in_parts >= 1, in_dim > 0 and 16-byte alignment");
+  if (ep->mode == 1 && !ep->residual) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: mode 1 needs a residual");
+  if (ep->mode == 1 && (const void*)ep->scaled == (const void*)y && ep->scaled) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: scaled aliases y");
+  if (ep->mode == 2 && (N % 2 != 0 || bias != nullptr))
+    return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm_fused: mode 2 needs an even N and no bias");
+  if (ep->mode == 1 && bias != nullptr) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: mode 1 takes no bias");
+  if (!fast_path_ok(x, w_q, scales, biases, K, group_size) || ((uintptr_t)workspace & 255) != 0)
+    return fail(DFLASH_ERR_MISALIGNED, "verify_qmm_fused: operands must be 16-byte, the workspace 256-byte aligned");
+  int device = 0;
+  cudaGetDevice(&device);
+  const int rc = tc::launch(x, w_q, scales, biases, bias, y, M, K, N, workspace, workspace_bytes, (cudaStream_t)stream, device,
+                            g_max_blocks, ep);
+  if (rc > 0) return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm_fused: shape not handled by the tcgen05 kernel");
+  if (rc == 0) g_last_impl = 2;
+  return rc;
+}
+
 extern "C" int dflash_verify_qmm_plan(int M, int K, int N, int group_size, int* out, int capacity) {
   if (!out || (group_size != 32 && group_size != 64 && group_size != 128) || K % (8 * group_size) != 0)
     return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_plan: bad arguments");

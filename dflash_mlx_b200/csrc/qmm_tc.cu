@@ -24,8 +24,8 @@
 // biases (TMA) and the 16 x 512 slice of the activations it multiplies, as the K-major core-matrix tiles the MMA reads.
 // Roles meet only through mbarriers; between dequantisation and MMA the hand-over unit is a PAIR of quantisation
 // groups (128 k) of the 128 rows, held in one of 6 operand buffers of 64 TMEM columns:
-//   producer warp  : TMEM allocation; TMA loads of a unit's weights, scales and biases.
-//   loader warps   : the unit's activations, global (L2) -> registers -> permuted -> shared memory.
+//   producer warp  : TMEM allocation; TMA loads of a unit's weights, scales, biases and 16 x 512 activation slice.
+//   permuter warps : reorder the k of every 8-block of the landed activation slice in place (see above).
 //   dequant warps  : a thread owns ONE weight row (its TMEM lane); the four warps of a slot cover the 128 rows and take
 //                    every kSlots-th pair.  Per pair: wait(stage landed) -> 4 x LDS.128 -> wait(operand buffer free) ->
 //                    AND/FMA -> 2 x tcgen05.st (32 columns each) -> arrive(operand ready).
@@ -57,6 +57,7 @@ constexpr int kG = 64;                   // quantisation group
 constexpr int kBK = 8 * kG;              // k per unit
 constexpr int kEpWarps = 4, kXWarps = 4;
 constexpr int kEp = kEpWarps * 32;
+constexpr int kFin = 2;               // partial tiles whose loads are in flight together in the finalizer
 constexpr int kTileF4 = 512;             // float4 entries of one fp32 partial tile: [token quad][row]
 constexpr int kStages = 4;
 constexpr int kEarlyUnits = 2;           // units whose weights are requested before the wait on the previous kernel
@@ -69,7 +70,11 @@ constexpr int kStageBytes = kXOff + kXTileBytes;
 constexpr int kMaxRowTiles = 16384;
 constexpr int kNA = 6;                   // operand buffers of 64 TMEM columns (one PAIR of quantisation groups each)
 constexpr int kNumBars = 3 * kStages + 2 * kNA + 2;  // full, empty, x_landed, a_ready, a_free, d_ready, d_free
-constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 8 * kNumBars + 128;
+// epilogue scratch: per-token factors (one copy per epilogue warp), one tile of residual values (bf16), one tile of the
+// other CTAs' summed partial sums (fp32)
+constexpr int kEpResOff = 256, kEpOthOff = kEpResOff + 16 * kRows * 2;
+constexpr int kEpSmemBytes = kEpOthOff + 16 * kRows * 4;
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kEpSmemBytes + 8 * kNumBars + 128;
 constexpr uint32_t kTmemCols = 512;      // operand buffers at columns 0..383, accumulators at 384..479
 constexpr uint32_t kDCol0 = 64 * kNA;
 #ifndef DFLASH_TC_STAGGER_NS
@@ -106,6 +111,10 @@ __device__ __forceinline__ void tmem_alloc(uint32_t smem_holder, uint32_t cols) 
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -188,41 +197,157 @@ __device__ __forceinline__ void dequant_group(const uint4& wa, const uint4& wb, 
   }
 }
 
-__device__ __forceinline__ void store_row(const float (&v)[16], __nv_bfloat16* __restrict__ y,
-                                          const __nv_bfloat16* __restrict__ bias, int n, int M, int N) {
-  if (n >= N) return;
-  const float bv = bias ? __bfloat162float(bias[n]) : 0.f;
+// What the epilogue does with a finished row tile (device-side copy of dflash_qmm_epilogue).
+//   mode 0: y = acc * inv (+ bias)
+//   mode 1: y = residual + acc (the residual stream, stored in bf16), scaled = y * next_w, out_ssq[(tile, warp)][token] =
+//           the sum of y^2 over the warp's 32 rows: the next matmul finishes the RMSNorm from these partial sums
+//   mode 2: rows are (gate_j, up_j) interleaved; y[t][j] = silu(gate) * up, both rounded to bf16 first
+// inv[token] = rsqrt(sum_p in_ssq[p][token] / in_dim + eps) when in_ssq is given (x then holds h * norm_weight, not
+// yet divided by the row's RMS: a per-token factor commutes with the matmul), else 1.
+struct Epi {
+  int mode, in_parts;
+  float in_dim, eps;
+  const float* in_ssq;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* next_w;
+  __nv_bfloat16* scaled;
+  float* out_ssq;
+};
+
+// The 16 per-token factors, left in the warp's own 16 floats of shared memory (registers are scarce in this kernel and
+// local memory is slow with nearly all of L1 given to shared memory).  The partial sums are added in a fixed order.
+__device__ __forceinline__ void token_factors(const Epi& e, int lane, float* inv_sm) {
+  if (e.in_ssq == nullptr) {
+    if (lane < 16) inv_sm[lane] = 1.f;
+    __syncwarp();
+    return;
+  }
+  // entry f of the array seen as float4 = tokens 4 (f % 4) .. + 3 of part f / 4; lane l reads f = l, l + 32, ...
+  const float4* src = (const float4*)e.in_ssq;
+  const int n4 = e.in_parts * 4;
+  float4 acc[4];
 #pragma unroll
-  for (int t = 0; t < 16; ++t)
-    if (t < M) y[(size_t)t * N + n] = __float2bfloat16_rn(v[t] + bv);
+  for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int f0 = lane; f0 < n4; f0 += 128) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = f0 + 32 * u < n4 ? ld_cg_f4(src + f0 + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+  }
+  float4 s = make_float4((acc[0].x + acc[1].x) + (acc[2].x + acc[3].x), (acc[0].y + acc[1].y) + (acc[2].y + acc[3].y),
+                         (acc[0].z + acc[1].z) + (acc[2].z + acc[3].z), (acc[0].w + acc[1].w) + (acc[2].w + acc[3].w));
+#pragma unroll
+  for (int m = 4; m <= 16; m <<= 1) {
+    s.x += __shfl_xor_sync(0xffffffffu, s.x, m); s.y += __shfl_xor_sync(0xffffffffu, s.y, m);
+    s.z += __shfl_xor_sync(0xffffffffu, s.z, m); s.w += __shfl_xor_sync(0xffffffffu, s.w, m);
+  }
+  const float rd = 1.f / e.in_dim;
+  if (lane < 4) {  // lane q holds the token quad q
+    inv_sm[4 * lane + 0] = rsqrtf(s.x * rd + e.eps); inv_sm[4 * lane + 1] = rsqrtf(s.y * rd + e.eps);
+    inv_sm[4 * lane + 2] = rsqrtf(s.z * rd + e.eps); inv_sm[4 * lane + 3] = rsqrtf(s.w * rd + e.eps);
+  }
+  __syncwarp();
 }
 
-// The epilogue warp that took the last ticket of its 32-row slice of row tile nt sums that slice's partial tiles in
-// piece order (fixed: deterministic); thread r owns row r.  The loads of up to four partial tiles are in flight together.
-__device__ __noinline__ void finalize_slice(const Plan& plan, const float4* pieces, __nv_bfloat16* __restrict__ y,
-                                               const __nv_bfloat16* __restrict__ bias, int nt, int np, int r) {
+// Row n's residual values of the 16 tokens go to shared memory ([token][row of the tile], read back by the same thread)
+// before the accumulators are waited for.
+__device__ __forceinline__ void prefetch_row(const Epi& e, int n, int r, int M, int N, unsigned short* res_sm) {
+  if (e.mode != 1) return;
+  const unsigned short* rs = (const unsigned short*)e.residual;
+  unsigned short v[16];
+#pragma unroll
+  for (int t = 0; t < 16; ++t) v[t] = (n < N && t < M) ? rs[(size_t)t * N + n] : (unsigned short)0;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) res_sm[t * kRows + r] = v[t];
+}
+
+// One finished row (all 16 tokens) of row tile nt: v = the accumulators.  Called by whole warps (modes 1 and 2 exchange
+// values between the lanes); lanes whose row lies beyond N take part without storing.
+__device__ __forceinline__ void finish_row(const Epi& e, const Plan& plan, float (&v)[16], const float* inv_sm,
+                                           const unsigned short* res_sm, __nv_bfloat16* y,
+                                           const __nv_bfloat16* __restrict__ bias, int nt, int r, int lane) {
+  const int n = nt * kRows + r, M = plan.M, N = plan.N;
+  const bool live = n < N;
+  if (e.mode == 0) {
+    if (!live) return;
+    const float bv = bias ? __bfloat162float(bias[n]) : 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+      if (t < M) y[(size_t)t * N + n] = __float2bfloat16_rn(v[t] * inv_sm[t] + bv);
+    return;
+  }
+  if (e.mode == 1) {
+    const float next_w = (e.next_w != nullptr && live) ? __bfloat162float(e.next_w[n]) : 1.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float res = __uint_as_float((uint32_t)res_sm[t * kRows + r] << 16);
+      const __nv_bfloat16 hb = __float2bfloat16_rn(res + v[t] * inv_sm[t]);
+      const float h = __bfloat162float(hb);
+      v[t] = 0.f;
+      if (live && t < M) {
+        y[(size_t)t * N + n] = hb;
+        if (e.scaled != nullptr) e.scaled[(size_t)t * N + n] = __float2bfloat16_rn(h * next_w);
+        v[t] = h * h;
+      }
+    }
+    if (e.out_ssq != nullptr) {
+      // 16 sums over the 32 lanes in 16 exchanges: every step halves the values a lane carries
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int keep = 8 >> s, m = 16 >> s;
+        const bool up = (lane & m) != 0;
+#pragma unroll
+        for (int i = 0; i < keep; ++i) {
+          const float send = up ? v[i] : v[i + keep];
+          const float mine = up ? v[i + keep] : v[i];
+          v[i] = mine + __shfl_xor_sync(0xffffffffu, send, m);
+        }
+      }
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+      const int t = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+      if ((lane & 1) == 0) e.out_ssq[(size_t)(nt * 4 + (r >> 5)) * 16 + t] = v[0];
+    }
+    return;
+  }
+  // mode 2: lane pairs hold (gate, up) of output column n / 2; the even lane finishes tokens 0..7, the odd one 8..15
+  const int I = N >> 1, j = n >> 1;
+  const bool odd = (lane & 1) != 0;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    const float mine = __bfloat162float(__float2bfloat16_rn(v[t] * inv_sm[t]));
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+    const float g = odd ? other : mine, u = odd ? mine : other;
+    const bool my_token = odd ? (t >= 8) : (t < 8);
+    if (live && my_token && t < M) y[(size_t)t * I + j] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+  }
+}
+
+// v += the partial tiles [from, to) of row tile nt, in that order (thread r owns row r); the loads of kFin tiles are
+// in flight together.
+__device__ __forceinline__ void sum_pieces(const Plan& plan, const float4* pieces, int nt, int from, int to, int r,
+                                           float (&o)[16]) {
   float4 v[4];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int p0 = 0; p0 < np; p0 += 4) {
-    float4 a[4][4];
+  for (int q = 0; q < 4; ++q) v[q] = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+  for (int p0 = from; p0 < to; p0 += kFin) {
+    float4 a[kFin][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (p0 + i < np) {
+    for (int i = 0; i < kFin; ++i)
+      if (p0 + i < to) {
         const float4* src = &pieces[((size_t)(p0 + i) * plan.NT + nt) * kTileF4 + r];
 #pragma unroll
         for (int q = 0; q < 4; ++q) a[i][q] = ld_cg_f4(src + q * kRows);
       }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (p0 + i < np) {
+    for (int i = 0; i < kFin; ++i)
+      if (p0 + i < to) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) { v[q].x += a[i][q].x; v[q].y += a[i][q].y; v[q].z += a[i][q].z; v[q].w += a[i][q].w; }
       }
   }
-  const float o[16] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w,
-                       v[2].x, v[2].y, v[2].z, v[2].w, v[3].x, v[3].y, v[3].z, v[3].w};
-  store_row(o, y, bias, nt * kRows + r, plan.M, plan.N);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { o[4 * q] = v[q].x; o[4 * q + 1] = v[q].y; o[4 * q + 2] = v[q].z; o[4 * q + 3] = v[q].w; }
 }
 
 #ifdef DFLASH_TC_TRACE
@@ -238,7 +363,15 @@ struct Roles {
   static constexpr int kMma = 6;                               // issuing threads: 3 pair classes x 2 groups of the pair
   static constexpr int kEpWarp0 = NDQ, kXWarp0 = NDQ + kEpWarps, kProducerWarp = kXWarp0 + kXWarps;
   static constexpr int kMmaWarp = kProducerWarp + 1;
-  static constexpr int kThreads = (kMmaWarp + kMma) * 32;
+  static constexpr int kWarps = (kMmaWarp + kMma + 3) / 4 * 4;  // whole warpgroups (the last warp has no role)
+  static constexpr int kThreads = kWarps * 32;
+  // Registers per thread.  The kernel starts with kRegLaunch everywhere (what __launch_bounds__ lets the compiler use);
+  // setmaxnreg then moves registers from the warpgroups that only issue requests to the ones that do arithmetic.  A
+  // warpgroup's four warps sit on the four SM sub-partitions, so the budget is per sub-partition: one warp of each.
+  static constexpr int kRegLaunch = (65536 / kThreads) / 8 * 8;
+  static constexpr int kRegDq = NDQ == 12 ? 80 : 104, kRegEp = 104, kRegX = 56, kRegCtl = 48;  // no spills (ptxas -v)
+  static_assert((NDQ / 4) * kRegDq + kRegEp + kRegX + 2 * kRegCtl <= (kWarps / 4) * kRegLaunch,
+                "setmaxnreg.inc would wait for registers that never come");
   static constexpr int kSlots = NDQ / 4;                       // pairs being dequantised at the same time
   static constexpr int kClasses = 3;                           // pair classes of the issuing threads (p mod 3)
   static_assert(kNA % kSlots == 0 && kNA % kClasses == 0, "a ring buffer must belong to one slot and one pair class");
@@ -248,9 +381,9 @@ template <int NDQ>
 __global__ void __launch_bounds__(Roles<NDQ>::kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmX,
-              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, float4* __restrict__ pieces,
-              unsigned* __restrict__ counters, const __grid_constant__ Plan plan, int* __restrict__ err,
-              unsigned long long* __restrict__ stamps) {
+              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* y, float4* __restrict__ pieces,
+              unsigned* __restrict__ counters, const __grid_constant__ Plan plan,
+              const __grid_constant__ Epi epi, int* __restrict__ err, unsigned long long* __restrict__ stamps) {
   using R = Roles<NDQ>;
   // Optional time stamps (dflash_verify_qmm_set_stamps): 16 words per CTA, [0] / [1] = %globaltimer at entry / exit,
   // [2..10] = this SM's clock at entry, set-up done, first activation tile landed, first stage complete, first operand
@@ -266,7 +399,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stages = smem;
-  uint64_t* bars = (uint64_t*)(stages + kStages * kStageBytes);
+  uint8_t* ep_smem = stages + kStages * kStageBytes;
+  uint64_t* bars = (uint64_t*)(ep_smem + kEpSmemBytes);
   uint32_t* tmem_holder = (uint32_t*)(bars + kNumBars);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_full = bar0, bar_empty = bar_full + 8 * kStages, bar_xraw = bar_empty + 8 * kStages;
@@ -282,7 +416,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const unsigned npairs = (u_end - u_begin) * 4u;
   const int nt0 = (int)(u_begin / (unsigned)C), nt1 = (int)((u_end - 1) / (unsigned)C);
 
-  if (tid == 0) {
+  // Producer state (one thread): the next stage to fill and the unit it takes.
+  int p_stage = 0, p_nt = nt0, p_kc = (int)(u_begin % (unsigned)C);
+  uint32_t p_par = 1;
+  unsigned p_u = u_begin;
+  uint64_t pol_stream = 0, pol_keep = 0;
+  auto request_weights = [&]() {  // the weights, scales and biases of unit p_u into stage p_stage
+    const uint32_t full = bar_full + 8 * p_stage, dst = smem_u32(stages + p_stage * kStageBytes);
+    mbar_arrive_expect_tx(full, kTmaBytes);
+    tma_load_2d(dst, &tmW, p_kc * (kBK / 2), p_nt * kRows, full, pol_stream);
+    tma_load_2d(dst + kRows * 128, &tmW, p_kc * (kBK / 2) + 128, p_nt * kRows, full, pol_stream);
+    tma_load_2d(dst + kWBytes, &tmS, p_kc * 8, p_nt * kRows, full, pol_keep);
+    tma_load_2d(dst + kWBytes + kSBBytes, &tmB, p_kc * 8, p_nt * kRows, full, pol_keep);
+    if (++p_stage == kStages) { p_stage = 0; p_par ^= 1; }
+    if (++p_kc == C) { p_kc = 0; ++p_nt; }
+    ++p_u;
+  };
+  if (warp == R::kProducerWarp && lane == 0) {
+    // The producer thread sets the barriers up itself and asks for the first units' weights at once (they are written by
+    // no kernel): the requests are on their way while the rest of the block is still being set up.
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar_full + 8 * i, 1 + kXWarps);      // the TMA bytes and the loader warps' activation tile
       mbar_init(bar_empty + 8 * i, 16 + R::kMma);    // every (pair, 32-row slice) read, every issuing thread's MMAs done
@@ -295,35 +447,29 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     mbar_init(bar_dready, R::kMma);      // one tcgen05.commit per issuing thread
     mbar_init(bar_dfree, kEpWarps);
     mbar_fence_init();
+    pol_stream = l2_policy_evict_first();
+    pol_keep = l2_policy_evict_last();
+    while (p_u < u_end && p_u - u_begin < (unsigned)kEarlyUnits) request_weights();
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
   }
-  if (warp == R::kProducerWarp) {
-    if (lane == 0) {  // the first TMA request through a tensor map waits for the map itself: fetch all four now
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmS) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
-    }
-    tmem_alloc(smem_u32(tmem_holder), kTmemCols);
-  }
+  if (warp == R::kWarps - 1) tmem_alloc(smem_u32(tmem_holder), kTmemCols);  // the warp without a role owns the tensor memory
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_holder;
   if (tid == 0) mark(3);
 
+  if (warp >= R::kProducerWarp) reg_dec<R::kRegCtl>();  // two warpgroups: producer, issuing warps, one idle warp
   if (warp == R::kProducerWarp) {
     // ======================= TMA producer =======================
     // Weights are written by no kernel, so they are requested at once, before the wait on the previous kernel.
     if (lane == 0) {
-      const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-      int stage = 0, nt = nt0, kc = (int)(u_begin % (unsigned)C);
-      // x is the previous kernel's output, the weights are nobody's: the weights of the first kEarlyUnits units are
-      // requested at once, then the previous kernel is waited for, then every unit's activation tile is requested with
-      // (right after) its weights.  Requests are served in order, so an activation tile asked for behind the whole ring
-      // of weights would land ~3 us late; behind two units it lands as soon as the MMA could use it.
-      uint32_t par = 1;
+      // x is the previous kernel's output: once the early units' weights are requested (above), the previous kernel is
+      // waited for, then every unit's activation tile is requested with (right after) its weights.  Requests are served
+      // in order, so an activation tile asked for behind the whole ring of weights would land ~3 us late; behind two
+      // units it lands as soon as the MMA could use it.
       unsigned xu = u_begin;  // next unit whose activation tile is still owed
-      int xstage = 0, xkc = kc;
+      int xstage = 0, xkc = (int)(u_begin % (unsigned)C);
       auto request_x = [&](unsigned upto) {
         while (xu < upto) {
           const uint32_t xb = bar_xraw + 8 * xstage;
@@ -334,32 +480,17 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           ++xu;
         }
       };
-      bool waited = false;
-      for (unsigned u = u_begin; u < u_end; ++u) {
-        if (!waited && u - u_begin == (unsigned)kEarlyUnits) {
-          pdl_wait();
-          waited = true;
-          request_x(u);
-        }
-        if (!mbar_wait_quiet(bar_empty + 8 * stage, par)) { TC_TRACE(11, u - u_begin); atomicCAS(err, 0, 11 | ((int)(u - u_begin) << 8)); break; }
-        const uint32_t full = bar_full + 8 * stage, dst = smem_u32(stages + stage * kStageBytes);
-        mbar_arrive_expect_tx(full, kTmaBytes);
-        tma_load_2d(dst, &tmW, kc * (kBK / 2), nt * kRows, full, pol_stream);
-        tma_load_2d(dst + kRows * 128, &tmW, kc * (kBK / 2) + 128, nt * kRows, full, pol_stream);
-        tma_load_2d(dst + kWBytes, &tmS, kc * 8, nt * kRows, full, pol_keep);
-        tma_load_2d(dst + kWBytes + kSBBytes, &tmB, kc * 8, nt * kRows, full, pol_keep);
-        if (++stage == kStages) { stage = 0; par ^= 1; }
-        if (++kc == C) { kc = 0; ++nt; }
-        if (waited) request_x(u + 1);
-      }
-      if (!waited) {
-        pdl_wait();
-        request_x(u_end);
+      pdl_wait();
+      request_x(p_u);
+      while (p_u < u_end) {
+        if (!mbar_wait_quiet(bar_empty + 8 * p_stage, p_par)) { TC_TRACE(11, p_u - u_begin); atomicCAS(err, 0, 11 | ((int)(p_u - u_begin) << 8)); break; }
+        request_weights();
+        request_x(p_u);
       }
     }
   } else if (warp >= R::kMmaWarp) {
     // ======================= MMA issue =======================
-    if (lane == 0) {
+    if (lane == 0 && warp < R::kMmaWarp + R::kMma) {
       const int me = warp - R::kMmaWarp;
       const int half = me & 1, cls = me >> 1;
       bool aborted = false;
@@ -409,6 +540,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // layout the MMA reads); the k order inside every 8-block (one 16-byte chunk, which the swizzle moves as a whole) is
     // then permuted in place to (0,4,1,5,2,6,3,7), the order in which the dequantised pairs come out.  A thread rewrites
     // its own chunks, so nothing is exchanged.
+    reg_dec<R::kRegX>();
     const int xt = tid - R::kXWarp0 * 32;  // 0..127
     bool aborted = false;
     int stage = 0;
@@ -434,6 +566,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     }
   } else if (warp < NDQ) {
     // ======================= dequantisers =======================
+    reg_inc<R::kRegDq>();
     const int r = ((warp & 3) << 5) | lane;  // TMEM lane = weight row inside the tile
     const uint32_t lane_base = (uint32_t)((warp & 3) << 5) << 16;
     bool aborted = false;
@@ -479,14 +612,50 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     }
   } else {
     // ======================= epilogue =======================
+    reg_inc<R::kRegEp>();
     const int r = ((warp & 3) << 5) | lane;  // TMEM lane = weight row inside the tile
     const uint32_t lane_base = (uint32_t)((warp & 3) << 5) << 16;
     const int etid = tid - R::kEpWarp0 * 32;  // 0..127
     bool aborted = false;
     pdl_wait();      // these warps write what a later kernel reads and the previous kernel may still read
     pdl_trigger();
+    float* const inv_sm = (float*)ep_smem + (warp & 3) * 16;
+    unsigned short* const res_sm = (unsigned short*)(ep_smem + kEpResOff);
+    token_factors(epi, lane, inv_sm);
     for (int nt = nt0; nt <= nt1; ++nt) {
       const int seg = nt - nt0;
+      prefetch_row(epi, nt * kRows + r, r, M, N, res_sm);
+      int first_cta = 0;
+      const int total = tile_pieces(plan, nt, &first_cta);  // CTAs that share row tile nt
+      // A row tile cut over several CTAs is summed from fp32 partial tiles by the tile's FIRST CTA, as (p1 + p2 + ...) +
+      // p0 with p0 its own part, which never leaves its registers.  The tile is the end of that CTA's span and the start
+      // (or the whole) of the others', so the others are normally done long before: the first CTA waits for their
+      // arrivals and sums their parts BEFORE it waits for its own accumulators, which leaves only "add and store" on the
+      // kernel's tail.  The others store their part and signal with a release-add; they never wait, so the waits cannot
+      // form a cycle (every CTA is resident: at most one per SM is launched).
+      float* const oth_sm = (float*)(ep_smem + kEpOthOff);  // [token][row], written and read by the same thread
+      const bool owner = total > 1 && bl == first_cta;
+      if (owner) {
+        unsigned c = 0;
+        if (lane == 0) {
+          const unsigned* ctr = &counters[nt * 4 + (warp & 3)];
+          for (unsigned spins = 0; !aborted; ++spins) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(ctr) : "memory");
+            if (c == (unsigned)(total - 1)) break;
+            if (spins >= kWaitLimit) { TC_TRACE(18, nt); atomicCAS(err, 0, 18 | (nt << 8)); break; }
+            __nanosleep(64);
+          }
+        }
+        c = __shfl_sync(0xffffffffu, c, 0);
+        __syncwarp();  // lane 0's acquire before the other lanes' loads
+        if (c != (unsigned)(total - 1)) aborted = true;
+        float acc[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) acc[t] = 0.f;
+        if (!aborted) sum_pieces(plan, pieces, nt, 1, total, r, acc);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) oth_sm[t * kRows + r] = acc[t];
+      }
       if (!aborted && !mbar_wait_quiet(bar_dready, (uint32_t)(seg & 1))) { aborted = true; TC_TRACE(14, seg); atomicCAS(err, 0, 14 | (seg << 8)); }
       tc_fence_after();
       if (etid == 0 && nt == nt1) mark(8);
@@ -510,26 +679,21 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (lane == 0) mbar_arrive(bar_dfree);
 #pragma unroll
       for (int t = 0; t < 16; ++t) out[t] *= kPow2Out;
-      int first_cta = 0;
-      const int total = tile_pieces(plan, nt, &first_cta);  // CTAs that share row tile nt
-      if (total > 1) {
-        // Every warp looks after its own 32 rows: partial tile -> ticket of (tile, slice) -> the warp that takes the
-        // last one sums the slice.  No block-wide barrier; the ticket is one acquire-release atomic.
+      if (total > 1 && !owner) {
         float4* base = &pieces[((size_t)(bl - first_cta) * NT + nt) * kTileF4 + r];
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd)
           base[qd * kRows] = make_float4(out[4 * qd], out[4 * qd + 1], out[4 * qd + 2], out[4 * qd + 3]);
         __syncwarp();  // orders the 32 lanes' stores before lane 0's release
-        unsigned t = 0;
         if (lane == 0)
-          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(&counters[nt * 4 + (warp & 3)]) : "memory");
-        t = __shfl_sync(0xffffffffu, t, 0);  // and lane 0's acquire before the other lanes' loads
-        if (t == (unsigned)(total - 1)) {
-          finalize_slice(plan, pieces, y, bias, nt, total, r);
-          if (lane == 0) counters[nt * 4 + (warp & 3)] = 0;  // ready for the next launch
-        }
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&counters[nt * 4 + (warp & 3)]) : "memory");
       } else {
-        store_row(out, y, bias, nt * kRows + r, M, N);
+        if (owner) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) out[t] = oth_sm[t * kRows + r] + out[t];
+        }
+        finish_row(epi, plan, out, inv_sm, res_sm, y, bias, nt, r, lane);
+        if (owner && lane == 0) counters[nt * 4 + (warp & 3)] = 0;  // every other part has arrived: ready for the next launch
       }
       if (etid == 0 && nt == nt1) mark(9);
     }
@@ -538,7 +702,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   // every warp ends here: the tensor memory goes back before the CTA exits
   tc_fence_before();
   __syncthreads();
-  if (warp == R::kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+  if (warp == R::kWarps - 1) tmem_dealloc(tmem, kTmemCols);
   if (stamp && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -559,7 +723,9 @@ bool make_plan(int M, int K, int N, int device, int max_blocks, Plan* p) {
   p->NT = (N + kRows - 1) / kRows;
   if (p->NT > kMaxRowTiles || p->C < 1) return false;
   const long long U = (long long)p->NT * p->C;
-  long long ctas = max_blocks > 0 ? max_blocks : sm_count(device);
+  // never more CTAs than SMs: a tile's first CTA waits for the others' parts, so all of them must be resident
+  long long ctas = sm_count(device);
+  if (max_blocks > 0 && max_blocks < ctas) ctas = max_blocks;
   if (ctas > U) ctas = U;
   if ((U + 1) * ctas >= (1ll << 31)) return false;  // the kernel's span arithmetic is 32-bit
   p->ctas = (int)ctas;
@@ -634,16 +800,21 @@ bool get_map(const void* ptr, int a, int b, int kind, CUtensorMap* out) {
 template <int NDQ>
 cudaError_t launch_variant(int grid, cudaStream_t st, int device, const CUtensorMap& tw, const CUtensorMap& ts,
                            const CUtensorMap& tb, const CUtensorMap& tx, const void* bias, void* y, float4* pieces,
-                           unsigned* counters, const Plan& plan) {
+                           unsigned* counters, const Plan& plan, const Epi& epi) {
   auto kern = qmm_tc_kernel<NDQ>;
   static bool attr_done[64] = {};
   if (!attr_done[device & 63]) {
     cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e0 != cudaSuccess) return e0;
+    // the kernel's setmaxnreg budget assumes the block was given kRegLaunch registers per thread
+    cudaFuncAttributes fa;
+    e0 = cudaFuncGetAttributes(&fa, kern);
+    if (e0 != cudaSuccess) return e0;
+    if (fa.numRegs != Roles<NDQ>::kRegLaunch) return cudaErrorLaunchOutOfResources;
     attr_done[device & 63] = true;
   }
   return launch_kernel(kern, dim3(grid), dim3(Roles<NDQ>::kThreads), kSmemBytes, st, tw, ts, tb, tx,
-                       (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, pieces, counters, plan,
+                       (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, pieces, counters, plan, epi,
                        device_error_word(device), g_stamps);
 }
 
@@ -686,8 +857,14 @@ size_t workspace_bytes(int M, int K, int N, int device, int max_blocks) {
 
 // Returns DFLASH_OK, a negative status, or +1 when this shape is not handled here (the caller then runs qmm.cu).
 int launch(const void* x, const void* wq, const void* sc, const void* bi, const void* bias, void* y, int M, int K, int N,
-           void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks) {
+           void* ws, size_t ws_bytes, cudaStream_t st, int device, int max_blocks, const dflash_qmm_epilogue* ep) {
   if (K % kBK != 0) return 1;
+  Epi epi = {};
+  if (ep != nullptr) {
+    epi.mode = ep->mode; epi.in_parts = ep->in_parts; epi.in_dim = ep->in_dim; epi.eps = ep->eps;
+    epi.in_ssq = ep->in_ssq; epi.residual = (const __nv_bfloat16*)ep->residual;
+    epi.next_w = (const __nv_bfloat16*)ep->next_w; epi.scaled = (__nv_bfloat16*)ep->scaled; epi.out_ssq = ep->out_ssq;
+  }
   Plan plan;
   if (!make_plan(M, K, N, device, max_blocks, &plan)) return 1;
   CUtensorMap tw, ts, tb, tx;
@@ -701,8 +878,8 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
   const int grid = plan.ctas;
   cudaError_t e;
-  if (g_ndq == 12) e = launch_variant<12>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan);
-  else e = launch_variant<8>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan);
+  if (g_ndq == 12) e = launch_variant<12>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi);
+  else e = launch_variant<8>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm_tc launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;

@@ -26,6 +26,12 @@ _vp, _i32, _f32, _ll = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong
 _declared = False
 
 
+class QmmEpilogue(_c.Structure):
+    """``dflash_qmm_epilogue`` of the C ABI (what a fused matmul does with its finished rows)."""
+    _fields_ = [("mode", _i32), ("in_parts", _i32), ("in_dim", _f32), ("eps", _f32), ("in_ssq", _vp), ("residual", _vp),
+                ("next_w", _vp), ("scaled", _vp), ("out_ssq", _vp)]
+
+
 def _declare():
     global _declared
     if _declared:
@@ -45,6 +51,9 @@ def _declare():
     d("dflash_attn_prep_dev_offset", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 5 + [_vp, _f32, _f32, _i32, _vp])
     d("dflash_verify_sdpa_dev_len", _i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _ll, _ll, _ll, _ll, _f32,
                                            _i32, _i32, _vp, ctypes.c_size_t, _vp])
+    d("dflash_verify_qmm_fused_supported", _i32, [_i32] * 5)
+    d("dflash_verify_qmm_fused", _i32, [_vp] * 6 + [_i32] * 5 + [_c.POINTER(QmmEpilogue), _vp, _c.c_size_t, _vp])
+    d("dflash_embed_scaled", _i32, [_vp] * 6 + [_i32] * 4 + [_vp])
     _declared = True
 
 
@@ -171,7 +180,11 @@ class HybridVerifyModel:
     """Preallocated verify-step engine.  ``tp_world`` > 1 runs one tensor-parallel shard (heads, the MLP's
     intermediate dimension and the vocabulary are split; ``all_reduce`` sums the row-parallel outputs)."""
 
-    def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None, peer=None):
+    def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None, peer=None,
+                 fused: Optional[bool] = None, release_unfused: bool = False):
+        """``fused`` (default: wherever it applies, environment ``DFLASH_STEP_FUSED=0`` turns it off): RMSNorms, residual
+        adds and SwiGLU run inside the matmuls' epilogues.  The gate|up rows are then kept interleaved in a copy;
+        ``release_unfused`` drops the caller's original from ``weights`` to give the memory back."""
         _declare()
         self.cfg, self.w, self.dev = cfg, weights, torch.device(device)
         self.lib = _lib.lib()
@@ -242,6 +255,59 @@ class HybridVerifyModel:
                                                                     cfg.head_dim, 0)
             self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
         self.launches_per_step = 0
+        self._setup_fused(fused, release_unfused)
+
+    # ---- fused epilogues -------------------------------------------------------------------------------
+    def _setup_fused(self, fused, release_unfused):
+        """The dense single-GPU step runs as a chain of matmuls: in_norm / post_norm / final norm are split into a
+        column scale (applied by the producer of the residual stream) and a per-token factor (applied by the consumer
+        matmul to its accumulators), the residual add is the producer's epilogue and SwiGLU the gate|up epilogue."""
+        import os
+        cfg, T = self.cfg, self.cfg.block
+        ok = self.moe is None and self.all_reduce is None and self.peer is None and getattr(cfg, "tp_world", 1) == 1
+        if ok:
+            mats = [self.w["lm_head"]]
+            for L in self.w["layers"]:
+                mats += [L[n] for n in ("proj", "o_proj", "out_proj", "gate_up", "down") if n in L]
+            ok = all(self.lib.dflash_verify_qmm_fused_supported(T, W["w"].shape[1] * 8, W["w"].shape[0], cfg.group_size,
+                                                                _lib.BF16) == 1 for W in mats)
+        if fused is None:
+            fused = ok and os.environ.get("DFLASH_STEP_FUSED", "1") != "0"
+        elif fused and not ok:
+            raise ValueError("the fused step needs a dense, unsharded model whose matmuls are bf16 / group 64 / K % 512 == 0")
+        self.fused = bool(fused)
+        if not self.fused:
+            return
+        H = cfg.hidden
+        self.hw = torch.zeros(T, H, dtype=torch.bfloat16, device=self.dev)           # h * (weight of the next norm)
+        parts = 4 * ((H + 127) // 128)
+        self.ssq = [torch.zeros(parts, 16, dtype=torch.float32, device=self.dev) for _ in range(2)]
+        self.ssq_parts = parts
+        self.gate_up_il = []
+        for L in self.w["layers"]:
+            W = L["gate_up"]
+            n = W["w"].shape[0]
+            order = torch.arange(n, device=W["w"].device).view(2, n // 2).t().reshape(-1)   # gate_0, up_0, gate_1, ...
+            self.gate_up_il.append({k: W[k].index_select(0, order).contiguous() for k in ("w", "s", "b")})
+            if release_unfused:
+                L["gate_up"] = None
+
+    def _qmm_fused(self, x, W, out, ep: QmmEpilogue):
+        n, k = W["w"].shape[0], W["w"].shape[1] * 8
+        st = self.lib.dflash_verify_qmm_fused(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
+                                              out.data_ptr(), self.cfg.block, k, n, self.cfg.group_size, _lib.BF16,
+                                              _c.byref(ep), self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
+        self._chk(st, "dflash_verify_qmm_fused")
+
+    def _ep_in(self, which, parts, mode=0):
+        """Epilogue of a matmul whose x is ``hw``: finishes the RMSNorm from the partial sums in ``ssq[which]``."""
+        return QmmEpilogue(mode=mode, in_parts=parts, in_dim=float(self.cfg.hidden), eps=self.cfg.eps,
+                           in_ssq=self.ssq[which].data_ptr())
+
+    def _ep_residual(self, next_w, which):
+        """Epilogue of a matmul that adds into the residual stream and prepares the next norm (``ssq[which]``)."""
+        return QmmEpilogue(mode=1, residual=self.h.data_ptr(), next_w=next_w.data_ptr(), scaled=self.hw.data_ptr(),
+                           out_ssq=self.ssq[which].data_ptr())
 
     # ---- helpers -------------------------------------------------------------------------------------
     def _k_of(self, name, default):
@@ -317,16 +383,28 @@ class HybridVerifyModel:
         self._last_ids = ids
         st, BF = self._st(), _lib.BF16
         cur, nxt = self.cur, self.cur ^ 1
-        self._chk(lib.dflash_embed(ids.data_ptr(), self.w["embed"].data_ptr(), self.h.data_ptr(), T, cfg.hidden,
-                                   self.w["embed"].shape[0], BF, st), "dflash_embed")
+        fused = self.fused
+        layers = self.w["layers"]
+        if fused:
+            self._chk(lib.dflash_embed_scaled(ids.data_ptr(), self.w["embed"].data_ptr(), layers[0]["in_norm"].data_ptr(),
+                                              self.h.data_ptr(), self.hw.data_ptr(), self.ssq[0].data_ptr(), T, cfg.hidden,
+                                              self.w["embed"].shape[0], BF, st), "dflash_embed_scaled")
+            in_parts = 1          # partial sums behind ssq[0]: one per token from the embedding, then one per 32 columns
+        else:
+            self._chk(lib.dflash_embed(ids.data_ptr(), self.w["embed"].data_ptr(), self.h.data_ptr(), T, cfg.hidden,
+                                       self.w["embed"].shape[0], BF, st), "dflash_embed")
         delta = None
         ig = ia = 0
         N = self.offset + T
-        for i, L in enumerate(self.w["layers"]):
-            self._reduce_add_rmsnorm(delta, L["in_norm"])
+        for i, L in enumerate(layers):
+            if not fused:
+                self._reduce_add_rmsnorm(delta, L["in_norm"])
             if i in self._capture_at:          # h now holds the hidden state after layer i-1 (key i; key 0 = embeddings)
                 self.captured[self._capture_at[i]].copy_(self.h)
-            self._qmm(self.x, L["proj"], self.proj)
+            if fused:
+                self._qmm_fused(self.hw, L["proj"], self.proj, self._ep_in(0, in_parts))
+            else:
+                self._qmm(self.x, L["proj"], self.proj)
             if cfg.is_attention(i):
                 ld = L["proj"]["w"].shape[0]
                 k_off = 2 * cfg.q_heads * cfg.head_dim
@@ -355,7 +433,10 @@ class HybridVerifyModel:
                 self.launches_per_step += 1      # partials + combine
                 self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix_attn.data_ptr(),
                                                self.mix_attn.shape[1], T, cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
-                self._qmm(self.mix_attn, L["o_proj"], self.delta)
+                if fused:
+                    self._qmm_fused(self.mix_attn, L["o_proj"], self.h, self._ep_residual(L["post_norm"], 1))
+                else:
+                    self._qmm(self.mix_attn, L["o_proj"], self.delta)
                 ia += 1
             else:
                 ld = L["proj"]["w"].shape[0]
@@ -377,8 +458,18 @@ class HybridVerifyModel:
                 self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
                                                    self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
                           "dflash_gated_rmsnorm")
-                self._qmm(self.mix_gdn, L["out_proj"], self.delta)
+                if fused:
+                    self._qmm_fused(self.mix_gdn, L["out_proj"], self.h, self._ep_residual(L["post_norm"], 1))
+                else:
+                    self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
+            if fused:
+                # post_norm -> gate|up -> SwiGLU -> down -> residual add -> the next layer's (or the final) norm
+                self._qmm_fused(self.hw, self.gate_up_il[i], self.act, self._ep_in(1, self.ssq_parts, mode=2))
+                nxt_w = layers[i + 1]["in_norm"] if i + 1 < len(layers) else self.w["norm"]
+                self._qmm_fused(self.act, L["down"], self.h, self._ep_residual(nxt_w, 0))
+                in_parts = self.ssq_parts
+                continue
             self._reduce_add_rmsnorm(self.delta, L["post_norm"])
             if self.moe is not None:
                 # router -> top-k -> gate|up of the active experts -> weighted SwiGLU -> down summed over the experts
@@ -393,10 +484,14 @@ class HybridVerifyModel:
                           "dflash_swiglu")
                 self._qmm(self.act, L["down"], self.delta)
             delta = self.delta
-        self._reduce_add_rmsnorm(delta, self.w["norm"])
+        if not fused:
+            self._reduce_add_rmsnorm(delta, self.w["norm"])
         if cfg.layers in self._capture_at:
             self.captured[self._capture_at[cfg.layers]].copy_(self.h)
-        self._qmm(self.x, self.w["lm_head"], self.logits)
+        if fused:
+            self._qmm_fused(self.hw, self.w["lm_head"], self.logits, self._ep_in(0, in_parts))
+        else:
+            self._qmm(self.x, self.w["lm_head"], self.logits)
         v_local = self.w["lm_head"]["w"].shape[0]
         self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
         if self.all_gather is not None:
@@ -437,17 +532,31 @@ class HybridVerifyModel:
         return self.logits
 
     def qmm_launch_list(self):
-        """(x, W, out) of every matmul of a step, in launch order (used to time the matmuls alone)."""
+        """(x, W, out, epilogue) of every matmul of a step, in launch order (used to time the matmuls alone);
+        ``epilogue`` is None for a plain matmul."""
         out = []
-        for i, L in enumerate(self.w["layers"]):
-            out.append((self.x, L["proj"], self.proj))
-            out.append((self.mix_attn, L["o_proj"], self.delta) if self.cfg.is_attention(i) else (self.mix_gdn, L["out_proj"], self.delta))
+        fused = self.fused
+        layers = self.w["layers"]
+        in_parts = 1
+        for i, L in enumerate(layers):
+            attn = self.cfg.is_attention(i)
+            mix, Wo = (self.mix_attn, L["o_proj"]) if attn else (self.mix_gdn, L["out_proj"])
+            if fused:
+                nxt_w = layers[i + 1]["in_norm"] if i + 1 < len(layers) else self.w["norm"]
+                out.append((self.hw, L["proj"], self.proj, self._ep_in(0, in_parts)))
+                out.append((mix, Wo, self.h, self._ep_residual(L["post_norm"], 1)))
+                out.append((self.hw, self.gate_up_il[i], self.act, self._ep_in(1, self.ssq_parts, mode=2)))
+                out.append((self.act, L["down"], self.h, self._ep_residual(nxt_w, 0)))
+                in_parts = self.ssq_parts
+                continue
+            out.append((self.x, L["proj"], self.proj, None))
+            out.append((mix, Wo, self.delta, None))
             if self.moe is not None:
-                out.append((self.x, L["router"], self.router_logits[i]))   # the expert matmuls are not in this list
+                out.append((self.x, L["router"], self.router_logits[i], None))   # the expert matmuls are not in this list
             else:
-                out.append((self.x, L["gate_up"], self.gu))
-                out.append((self.act, L["down"], self.delta))
-        out.append((self.x, self.w["lm_head"], self.logits))
+                out.append((self.x, L["gate_up"], self.gu, None))
+                out.append((self.act, L["down"], self.delta, None))
+        out.append((self.hw if fused else self.x, self.w["lm_head"], self.logits, self._ep_in(0, in_parts) if fused else None))
         return out
 
     def run_experts_only(self):
@@ -456,14 +565,18 @@ class HybridVerifyModel:
             self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
 
     def run_qmm_only(self):
-        for x, W, o in self.qmm_launch_list():
-            self._qmm(x, W, o)
+        """Every matmul of a step, with its epilogue, and nothing else (timing aid; the residual stream is overwritten)."""
+        for x, W, o, ep in self.qmm_launch_list():
+            if ep is None:
+                self._qmm(x, W, o)
+            else:
+                self._qmm_fused(x, W, o, ep)
 
     def algorithmic_bytes(self):
         """Algorithmic HBM bytes of one step: every matmul's operands, KV read, GDN state read+write, tapes."""
         cfg, T, G = self.cfg, self.cfg.block, self.cfg.group_size
         qmm = 0
-        for x, W, o in self.qmm_launch_list():
+        for x, W, o, _ep in self.qmm_launch_list():
             n, k = W["w"].shape[0], W["w"].shape[1] * 8
             qmm += n * k // 2 + 2 * n * (k // G) * 2 + T * k * 2 + T * n * 2
         N = self.offset + T

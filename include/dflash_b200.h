@@ -76,6 +76,37 @@ DFLASH_API size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
 DFLASH_API int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases, const void* bias,
                       void* y, int M, int K, int N, int group_size, int dtype, void* workspace,
                       size_t workspace_bytes, void* stream);
+/* verify_qmm with the neighbouring element-wise work of a verify step folded into its epilogue, so that a decoder
+ * layer is a chain of matmuls with no small kernels between them (the reference leaves these to MLX's lazy graph:
+ * `rms_norm`, the residual `+` and `swiglu` around every quantised linear, mlx-lm's decoder layer as hooked by
+ * dflash_mlx/runtime.py:351-452 and :515-613).  Only for shapes dflash_verify_qmm_fused_supported() accepts (bf16,
+ * group size 64, K % 512 == 0); anything else is refused, nothing falls back.
+ *   mode 0  y[M,N] = acc * inv (+ bias)
+ *   mode 1  y = residual + acc, stored in bf16 (`residual` may be y itself: the residual stream is updated in
+ *           place); scaled[M,N] = y * next_w[N] (NULL: not written); out_ssq[4*ceil(N/128)][16] floats (NULL: not
+ *           written) = partial sums of y^2 per token, one per 32-row slice.  `scaled` and `out_ssq` are what the next
+ *           matmul takes as x / in_ssq: together they are the RMSNorm that follows, never materialised.
+ *   mode 2  the weight rows are interleaved (gate_0, up_0, gate_1, up_1, ...); y[M,N/2] = silu(gate) * up with gate
+ *           and up rounded to bf16 first, as the unfused sequence does.
+ *   in_ssq  NULL, or float[in_parts][16] partial sums of squares of the un-normalised input tokens (16-byte aligned):
+ *           inv[t] = rsqrt(sum_p in_ssq[p][t] / in_dim + eps) multiplies the accumulators (x then is `scaled` of a
+ *           mode-1 call: a per-token factor commutes with the matmul).  Partial sums are added in a fixed order. */
+typedef struct dflash_qmm_epilogue {
+  int mode;
+  int in_parts;
+  float in_dim;
+  float eps;
+  const float* in_ssq;
+  const void* residual;
+  const void* next_w;
+  void* scaled;
+  float* out_ssq;
+} dflash_qmm_epilogue;
+DFLASH_API int dflash_verify_qmm_fused_supported(int M, int K, int N, int group_size, int dtype);
+DFLASH_API int dflash_verify_qmm_fused(const void* x, const void* w_q, const void* scales, const void* biases,
+                                       const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
+                                       const dflash_qmm_epilogue* epilogue, void* workspace, size_t workspace_bytes,
+                                       void* stream);
 /* Tuning/testing knob: caps the number of thread blocks the fast kernel uses (0 = one per SM). */
 DFLASH_API void dflash_verify_qmm_set_max_blocks(int max_blocks);
 /* Tuning knob with the meaning of the reference's DFLASH_VERIFY_QMM_KPARTS (dflash_mlx/verify_qmm.py:297): K is cut
@@ -90,12 +121,10 @@ DFLASH_API void dflash_verify_qmm_set_impl(int impl);
 /* Tuning knob of the tcgen05 kernel: how many warps dequantise (8 or 12); the number of threads that
  * issue MMAs is fixed (6) and the second argument is ignored.  Other values leave the setting alone.  Results do not depend on it beyond fp32 summation order. */
 DFLASH_API void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads);
-/* Measurement aid: with a device buffer of 20 * 8 bytes per thread block (one block per SM) the tcgen05 kernel
- * records, per block, %globaltimer at entry [0] and exit [1] and the SM clock at entry [2], set-up done [3], activation
- * slab in shared memory [4], first weight stage landed [5], first operand ready for the tensor core [6], last MMA
- * issued [7], last accumulators ready [8], last output written [9], exit [10]; cycles issuing thread 0 waited [11] /
- * issued [12]; cycles dequant warp 0 waited for a stage [13], spent in loads + arithmetic [14], waited for its operand
- * buffer [15], spent in the TMEM store and hand-over [17].  NULL (default) turns it off. */
+/* Measurement aid: with a device buffer of 16 * 8 bytes per thread block (one block per SM) the tcgen05 kernel
+ * records, per block, %globaltimer at entry [0] and exit [1] and the SM clock at entry [2], set-up done [3], first
+ * activation tile landed [4], first pipeline stage complete [5], first operand ready for the tensor core [6], last MMA
+ * issued [7], last accumulators ready [8], last output written [9], exit [10].  NULL (default) turns it off. */
 DFLASH_API void dflash_verify_qmm_set_stamps(void* dev_buffer);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
 DFLASH_API int dflash_verify_qmm_last_impl(void);
@@ -188,6 +217,11 @@ DFLASH_API int dflash_add_rmsnorm(const void* h_in, const void* delta, const voi
 DFLASH_API int dflash_swiglu(const void* gate_up, void* y, int T_rows, int I, int dtype, void* stream);
 /* h[t,:] = table[ids[t],:]  (embed_tokens, runtime.py:788). */
 DFLASH_API int dflash_embed(const int* ids, const void* table, void* h, int T_rows, int H, int V, int dtype, void* stream);
+/* dflash_embed plus the inputs of a dflash_verify_qmm_fused call that applies the first layer's RMSNorm:
+ * scaled[t,:] = h[t,:] * next_w[:], ssq[t] = sum of h[t,:]^2 (float[16], entries T_rows..15 are left alone:
+ * zero them once; in_parts = 1). */
+DFLASH_API int dflash_embed_scaled(const int* ids, const void* table, const void* next_w, void* h, void* scaled, float* ssq,
+                                   int T_rows, int H, int V, int dtype, void* stream);
 /* out[t] = first index of the maximum of logits[t,:]  (greedy_tokens_with_mask, runtime.py:90-98). */
 DFLASH_API int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream);
 /* GatedDeltaNet layer between its input projections and the recurrence (runtime.py:368-403).

@@ -85,8 +85,10 @@ def test_dense_layers_at_configuration_4_dimensions():
     torch.cuda.synchronize()
     assert _rel(logits, ref_logits) <= 3e-2
     _check_tokens(m, ref_logits, ref_toks, 3e-2)
-    assert _rel(m.tape[0], tapes[0]["tape"]) <= 2e-3
-    assert _rel(m.state[m.cur ^ 1][0], ref_new["state"][0]) <= 2e-3
+    # the fused step rounds the normed input at another place (bf16(h * w) instead of bf16(h * inv * w)): 1.5e-2 there
+    tol0 = 1.5e-2 if m.fused else 2e-3
+    assert _rel(m.tape[0], tapes[0]["tape"]) <= tol0
+    assert _rel(m.state[m.cur ^ 1][0], ref_new["state"][0]) <= tol0
     # the attention layer's new K rows (q/k norm + RoPE at positions 4096..4111) and V rows in the cache
     assert _rel(m.kcache[0][:, ctx:ctx + 16], ref_new["k"][0][:, ctx:ctx + 16]) <= 2e-2
     assert _rel(m.vcache[0][:, ctx:ctx + 16], ref_new["v"][0][:, ctx:ctx + 16]) <= 2e-2

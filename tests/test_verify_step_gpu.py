@@ -63,7 +63,10 @@ def test_logits_tokens_and_rollback(setup):
     assert torch.equal(m.tokens.cpu()[sure], ref_toks[sure])
     # per-layer tape and forward state
     for l, tp in enumerate(tapes):
-        tol = 2e-3 if l == 0 else 2e-2   # layer 0: identical inputs, but one bf16 ulp of a projection output shows
+        # layer 0: identical inputs, but one bf16 ulp of a projection output shows; the fused step applies the input norm as
+        # a column scale before and a token factor after the matmul, so its x is rounded at another place (bf16(h * w)
+        # instead of bf16(h * inv * w)): 2^-9 relative per element of x instead of bit-equal inputs
+        tol = (1e-2 if m.fused else 2e-3) if l == 0 else 2e-2
         assert _rel(m.tape[l], tp["tape"]) <= tol, l
         assert _rel(m.state[m.cur ^ 1][l], ref_new["state"][l]) <= tol, l
     assert _rel(m.tape_qkv[0], tapes[0]["qkv"]) <= 1e-2          # a bf16 matmul output: ulp-level differences
@@ -75,10 +78,41 @@ def test_logits_tokens_and_rollback(setup):
     assert m.cur == snap_cur ^ 1 and m.offset == ctx + n_acc + 1 and not m._armed
     for l, tp in enumerate(tapes):
         want = og.tape_replay_ref(tp["tape"][None], tp["k"][None], tp["g"][None], caches["state"][l][None], steps=n_acc + 1)[0]
-        assert _rel(m.state[m.cur][l], want) <= (2e-3 if l == 0 else 2e-2), l
+        assert _rel(m.state[m.cur][l], want) <= ((1e-2 if m.fused else 2e-3) if l == 0 else 2e-2), l
         conv = og.rebuild_conv_state(caches["conv"][l][None], tp["qkv"][None], n_acc + 1, cfg.conv_kernel)[0]
         if l == 0:
             assert _rel(m.conv[m.cur][l], conv) <= 1e-2
+
+
+def test_fused_epilogues_against_the_unfused_step(setup):
+    """The step whose norms, residual adds and SwiGLU run inside the matmul epilogues against the same step built from
+    separate kernels: same greedy tokens wherever the margin is clear, logits within the step's bf16 bound."""
+    from dflash_mlx_b200.verify_step import HybridVerifyModel, weights_to
+    cfg, W, caches, ids, ctx, m_default = setup
+    assert m_default.fused
+    outs = []
+    for fused in (True, False):
+        m = HybridVerifyModel(cfg, weights_to(W, "cuda"), "cuda", fused=fused)
+        for l in range(len(caches["state"])):
+            m.state[m.cur][l].copy_(caches["state"][l])
+            m.conv[m.cur][l].copy_(caches["conv"][l])
+        for l in range(len(caches["k"])):
+            m.kcache[l].copy_(caches["k"][l])
+            m.vcache[l].copy_(caches["v"][l])
+        m.offset = ctx
+        logits = m.verify(ids.cuda()).float().clone()
+        torch.cuda.synchronize()
+        outs.append((logits, m.tokens.clone(), m.h.clone(), m.launches_per_step))
+        if not fused:      # the unfused step's first layer sees bit-equal inputs: held to the tighter bound
+            clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+            _, _, _, tapes = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
+            assert _rel(m.tape[0], tapes[0]["tape"]) <= 2e-3
+    (lf, tf, hf, nf), (lu, tu, hu, nu) = outs
+    assert nf < nu - 2 * cfg.layers
+    assert _rel(lf, lu) <= 3e-2 and _rel(hf, hu) <= 3e-2
+    top2 = lu.topk(2, dim=-1).values
+    sure = (top2[:, 0] - top2[:, 1]) > 3e-2 * lu.abs().max()
+    assert torch.equal(tf[sure], tu[sure])
 
 
 def test_device_side_accept_length_and_full_accept(setup):
