@@ -3,7 +3,8 @@
 
     python bench.py --gpus N --steps K --warmup W [--workload qmm_cfg1|replay|sdpa] [--impl reference]
 
-Prints ONE JSON line (rank 0).  See DESIGN.md ("Measurement") for what every field means.
+Prints ONE JSON line (rank 0): the metric, its roofline (dominant kernel timed alone), the end-to-end figure through
+the public API with host buffers, sampled clocks, a CPU baseline and, on one GPU, the single-op lines `extra`.
 Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
   qmm_cfg1  x bf16 [16,4096] . int4-g64 W [12288,4096]^T.  A step = one pass over a pool of weight
             matrices larger than L2 (so every launch streams its weights from HBM).
@@ -26,6 +27,10 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes (read + write) per algorithmic byte of the tcgen05 matmul, from an ncu capture of single launches
+# (profiles/qmm_tc_gate_up.md); None = not captured for this build
+QMM_TC_TRAFFIC_RATIO = None
+QMM_TC_TRAFFIC_SOURCE = "not captured for this build"
 
 
 def measured_peaks():
@@ -158,33 +163,30 @@ class QmmWorkload:
         us_per_launch = ms_per_step * 1e3 / self.launches_per_step
         achieved = self.per_launch_bytes / us_per_launch / 1e3
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": 28.50e6 if self.world == 1 else None, "peak_source": peak_src, "kernel": "qmm_stream_kernel",
+                "traffic": QMM_TC_TRAFFIC_RATIO * self.per_launch_bytes if (self.world == 1 and QMM_TC_TRAFFIC_RATIO) else None,
+                "traffic_source": QMM_TC_TRAFFIC_SOURCE, "peak_source": peak_src, "kernel": "qmm_tc_kernel (tcgen05)",
                 "algorithmic_bytes_per_launch": self.per_launch_bytes, "us_per_launch": us_per_launch}
 
-    def cpu_baseline(self, budget_s=12.0):
-        """The C restatement of the stock CPU path (oracle/qmm_ref.c) on all host cores, same shape."""
+    def cpu_sample(self):
+        """The C restatement of the stock CPU path (oracle/qmm_ref.c) on all host cores, same shape: one evaluation =
+        one full-size call."""
         import torch
         from oracle import qmm as oq
-        from oracle.build_ref import load
-        out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "oracle" / "_build" / "native")))
-        try:
-            lib, kind_note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
-        except Exception:
-            lib, kind_note = load(native=False), "gcc -O3 -fopenmp"
+        lib, kind_note = load_oracle_lib()
         wq, s, b = oq.random_quantized(self.N, self.K, seed=1, group_size=self.G)
         x = self.x_host.clone()
         y = torch.empty(self.M, self.N, dtype=torch.float32)
         args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), self.M, self.K, self.N, self.G)
-        lib.qmm_ref(*args)
-        times, t_end = [], time.perf_counter() + budget_s
-        while len(times) < 30 and (time.perf_counter() < t_end or len(times) < 3):
+        keep = (wq, s, b, x, y)
+
+        def evaluate():
             t0 = time.perf_counter()
             lib.qmm_ref(*args)
-            times.append(time.perf_counter() - t0)
-        times.sort()
-        return {"value": times[len(times) // 2] * 1e6, "unit": "us", "cores": int(lib.qmm_ref_threads()),
-                "kind": "port", "sample": f"{len(times)} full-size calls (M=16,K=4096,N=12288), median; {kind_note}; "
-                                          "MLX unavailable on this box: CPU baseline = C restatement of the stock qmm"}
+            return (time.perf_counter() - t0) * 1e6, None, keep
+
+        return evaluate, {"unit": "us", "cores": int(lib.qmm_ref_threads()), "kind": "port",
+                          "sample": f"full-size calls (M=16,K=4096,N=12288); {kind_note}; MLX unavailable on this box: CPU "
+                                    "baseline = C restatement of the stock qmm"}
 
 
 class DenseStepWorkload:
@@ -213,7 +215,18 @@ class DenseStepWorkload:
             cfg.moe_e_lo, cfg.moe_e_hi, cfg.moe_shared_here = rank * per, (rank + 1) * per, rank == 0
         self.cfg = cfg
         with torch.cuda.device(device):
-            weights = init_weights(cfg, 0xDF1D + rank, device, replicated_seed=0xDF1D if world > 1 else None)
+            if world > 1:
+                # ONE seeded model, the same on every rank, cut into this rank's shard (heads, MLP columns, vocabulary,
+                # experts): the ranks together compute the single-GPU model
+                from dflash_mlx_b200.parallel import shard_weights
+                full_w = init_weights(full, 0xDF1D, device)
+                cfg, weights = shard_weights(full, full_w, rank, world)
+                self.cfg = cfg
+                del full_w
+                torch.cuda.empty_cache()
+            else:
+                weights = init_weights(cfg, 0xDF1D, device)
+        self.weights = weights
         ar, ag = make_collectives(world)
         # row-parallel sums: the fused peer-memory kernel (default) or NCCL all-reduce + add/norm (DFLASH_TP_REDUCE=nccl)
         peer, self.reduce_mode = None, "none"
@@ -255,6 +268,53 @@ class DenseStepWorkload:
     def aux_step(self):
         self.model.run_qmm_only()
 
+    def self_check(self):
+        """Greedy tokens of the timed step against a second formulation of the same step on the same weights and caches:
+        N > 1: row-parallel sums by NCCL all-reduce + separate add/norm kernels instead of the fused peer-memory kernel;
+        N = 1: separate norm / residual / SwiGLU kernels instead of the matmul epilogues.  Both keep the residual stream
+        in bf16 and round at different places, and the difference grows with depth like a random walk (measured on the
+        random-init model: 2 % of the largest logit after 4 layers, 5 % after 16, 9 % after 64), so the bound is 3e-2 (the
+        4-layer bound the tests hold against the oracle) x sqrt(layers / 4): the logits must agree within it, and the
+        greedy tokens on every row whose top-2 margin exceeds it.  Every rank calls it."""
+        import torch
+        from dflash_mlx_b200.verify_step import HybridVerifyModel
+        from dflash_mlx_b200.parallel import make_collectives
+        world, dev = self.world, self.device
+        if world > 1:
+            ar, ag = make_collectives(world)
+            other = HybridVerifyModel(self.cfg, self.weights, dev, all_reduce=ar, all_gather=ag, peer=None)
+            what = "peer-memory reduce vs NCCL all-reduce"
+        else:
+            if not self.model.fused:
+                return {"match": True, "compared": "the unfused step is the timed one"}
+            other = HybridVerifyModel(self.cfg, self.weights, dev, fused=False)
+            what = "fused matmul epilogues vs separate kernels"
+        other.prefill_synthetic(self.CONTEXT, 0xDF1D)
+        la = self.model.verify(self.ids).float()
+        ta = self.model.tokens.clone()
+        lb = other.verify(self.ids).float()
+        tb = other.tokens.clone()
+        torch.cuda.synchronize()
+        top2 = lb.topk(2, dim=-1).values                       # this rank's vocabulary shard
+        amax = lb.abs().max().reshape(1)
+        if world > 1:
+            import torch.distributed as dist
+            allt = [torch.empty_like(top2) for _ in range(world)]
+            dist.all_gather(allt, top2.contiguous())
+            top2 = torch.cat(allt, dim=1).topk(2, dim=-1).values
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+        bound = 3e-2 * max(1.0, (self.cfg.layers / 4.0) ** 0.5)
+        dev_max = (la - lb).abs().max().reshape(1)
+        if world > 1:
+            dist.all_reduce(dev_max, op=dist.ReduceOp.MAX)
+        rel = float(dev_max / amax)
+        clear = (top2[:, 0] - top2[:, 1]) > bound * amax
+        same = ta == tb
+        del other
+        return {"match": bool(torch.all(same | ~clear)) and rel <= bound, "equal_rows": int(same.sum()),
+                "clear_rows": int(clear.sum()), "rows": int(same.numel()), "logits_rel_err": rel, "bound": bound,
+                "compared": what}
+
     def e2e_step(self):
         self.model.verify_captured(self.ids_host)        # pinned host ids -> device inside the call
         self.tok_host.copy_(self.model.tokens, non_blocking=True)
@@ -278,16 +338,18 @@ class DenseStepWorkload:
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 # DRAM bytes per launch, scaled from the ncu captures of both kernels (read + write = 0.99 x the
                 # algorithmic bytes for the mma.sync kernel on configuration 1, 1.03 x for the tcgen05 kernel on gate|up)
-                "traffic": 1.01 * per_launch if self.world == 1 else None,
-                "traffic_source": "ncu captures of single launches, scaled by algorithmic bytes",
+                "traffic": QMM_TC_TRAFFIC_RATIO * per_launch if (self.world == 1 and QMM_TC_TRAFFIC_RATIO) else None,
+                "traffic_source": QMM_TC_TRAFFIC_SOURCE,
                 "peak_source": peak_src,
-                "kernel": "verify matmul = qmm_stream_kernel (mma.sync) + qmm_tc_kernel (tcgen05; shapes with N*K >= 60e6, K <= 8192)",
+                "kernel": "qmm_tc_kernel (tcgen05 int4 matmul: every matmul of the step, with its norm / residual / SwiGLU "
+                          "epilogue when the step is fused)",
+                "fused_epilogues": bool(getattr(self.model, "fused", False)),
                 "launches_per_step": self.n_qmm, "algorithmic_bytes_per_launch": per_launch,
                 "us_per_launch": us_per_launch, "matmul_share_of_step": aux_ms / ms_per_step,
                 "whole_step_gbps": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9}
 
-    def cpu_baseline(self, budget_s=25.0):
-        return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s)
+    def cpu_sample(self):
+        return dense_step_cpu_sample(self.full_cfg, self.CONTEXT)
 
 
 class MoeStepWorkload(DenseStepWorkload):
@@ -318,9 +380,9 @@ class MoeStepWorkload(DenseStepWorkload):
                 "matmul_share_of_step": aux_ms / ms_per_step,
                 "whole_step_gbps": self.bytes["total"] / (ms_per_step * 1e-3) / 1e9}
 
-    def cpu_baseline(self, budget_s=25.0):
+    def cpu_sample(self):
         slots = int(round(self.bytes.get("active_expert_slots_per_layer", 0) * self.cfg.layers))
-        return dense_step_cpu_baseline(self.full_cfg, self.CONTEXT, budget_s, expert_slots=slots)
+        return dense_step_cpu_sample(self.full_cfg, self.CONTEXT, expert_slots=slots)
 
 
 class ReplayWorkload:
@@ -391,20 +453,21 @@ class ReplayWorkload:
                 "peak_source": peak_src, "kernel": "gdn_kernel<RECORD=false>", "algorithmic_bytes_per_launch": self.per_launch_bytes,
                 "us_per_launch": us}
 
-    def cpu_baseline(self, budget_s=10.0):
+    def cpu_sample(self):
         import torch
         from oracle import gdn as og
         torch.set_num_threads(os.cpu_count() or 1)
         c = og.make_gdn_case(seed=1)
         tape = torch.randn(1, 16, 32, 128)
-        ts = []
-        for _ in range(4):
+
+        def evaluate():
             t0 = time.perf_counter()
             og.tape_replay_ref(tape, c["k"], c["g"], c["state"], steps=self.STEPS)
-            ts.append(time.perf_counter() - t0)
-        return {"value": min(ts[1:]) * self.LAYERS * 1e6, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": "one layer with the torch restatement of _tape_replay_ops (best of 3) x 48 layers; "
-                          "MLX unavailable on this box"}
+            return (time.perf_counter() - t0) * self.LAYERS * 1e6, None, None
+
+        return evaluate, {"unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                          "sample": "one layer with the torch restatement of _tape_replay_ops x 48 layers; MLX unavailable "
+                                    "on this box"}
 
 
 class SdpaWorkload:
@@ -465,36 +528,64 @@ class SdpaWorkload:
                 "peak_source": peak_src, "kernel": "sdpa_partials_kernel (+ combine)",
                 "algorithmic_bytes_per_launch": self.per_launch_bytes, "us_per_launch": us}
 
-    def cpu_baseline(self, budget_s=10.0):
+    def cpu_sample(self):
         import torch
         from oracle import sdpa as osd
         torch.set_num_threads(os.cpu_count() or 1)
         q, k, v, sc = osd.make_sdpa_case(self.N, seed=1)
-        ts = []
-        for _ in range(4):
+
+        def evaluate():
             t0 = time.perf_counter()
             osd.sdpa_ref(q, k, v, sc)
-            ts.append(time.perf_counter() - t0)
-        return {"value": min(ts[1:]) * 1e6, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": "dense-softmax torch restatement, best of 3; MLX unavailable on this box"}
+            return (time.perf_counter() - t0) * 1e6, None, None
+
+        return evaluate, {"unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                          "sample": "dense-softmax torch restatement; MLX unavailable on this box"}
 
 
-def dense_step_cpu_baseline(cfg, context, budget_s=25.0, expert_slots=0):
-    """CPU path of one dense verify step on all host cores, from a bounded sample: every distinct linear shape
-    is timed with the C restatement of the stock qmm (oracle/qmm_ref.c), the GDN recurrence and the attention
-    with the torch oracle on one layer each; the step time is sum(count x time).  Element-wise glue is left out
-    (it favours the CPU number)."""
+def load_oracle_lib():
+    from oracle.build_ref import load
+    out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "oracle" / "_build" / "native")))
+    try:
+        return load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
+    except Exception:
+        return load(native=False), "gcc -O3 -fopenmp"
+
+
+def run_cpu_sample(sample, warmup, steps, budget_s):
+    """`warmup` untimed evaluations, then up to `steps` timed ones (fewer if `budget_s` runs out; at least one): the
+    median is the value.  Says how many ran."""
+    evaluate, meta = sample
+    for _ in range(max(1, warmup)):
+        evaluate()
+    vals, parts, t_end = [], None, time.perf_counter() + budget_s
+    while len(vals) < steps and (not vals or time.perf_counter() < t_end):
+        v, p, _ = evaluate()
+        vals.append(v)
+        parts = p if p is not None else parts
+    order = sorted(vals)
+    out = dict(meta)
+    out["value"] = order[len(order) // 2]
+    out["evaluations"] = len(vals)
+    out["warmup_evaluations"] = max(1, warmup)
+    out["spread"] = [order[0], order[-1]]
+    out["sample"] = "median of %d timed evaluations after %d untimed; one evaluation = %s" % (len(vals), max(1, warmup), meta["sample"])
+    if parts:
+        out["parts_ms_last"] = parts
+    return out
+
+
+def dense_step_cpu_sample(cfg, context, expert_slots=0):
+    """CPU path of one verify step on all host cores as a bounded sample: one evaluation runs every distinct linear
+    shape once with the C restatement of the stock qmm (oracle/qmm_ref.c) and one GDN recurrence and one attention with
+    the torch oracle; its value is sum(count x time) over the step.  Element-wise glue is left out (it favours the CPU
+    number).  Operands are made once."""
     import torch
     from oracle import gdn as og
     from oracle import qmm as oq
     from oracle import sdpa as osd
-    from oracle.build_ref import load
     torch.set_num_threads(os.cpu_count() or 1)
-    out_dir = Path(os.environ.get("DFLASH_ORACLE_BUILD", str(ROOT / "oracle" / "_build" / "native")))
-    try:
-        lib, note = load(native=True, out_dir=out_dir), "gcc -O3 -march=native -fopenmp"
-    except Exception:
-        lib, note = load(native=False), "gcc -O3 -fopenmp"
+    lib, note = load_oracle_lib()
     n_attn = sum(cfg.is_attention(i) for i in range(cfg.layers))
     n_gdn = cfg.layers - n_attn
     H, I, G, T = cfg.hidden, cfg.intermediate, cfg.group_size, cfg.block
@@ -509,62 +600,66 @@ def dense_step_cpu_baseline(cfg, context, budget_s=25.0, expert_slots=0):
                    ("expert_down", H, cfg.moe_inter, slots, 2)]
     else:
         shapes += [("gate_up", 2 * I, H, cfg.layers, T), ("down", H, I, cfg.layers, T)]
-    total, parts = 0.0, {}
-    reps = 3 if budget_s >= 20 else 2
+    ops = []
     for name, n, k, count, rows in shapes:
         if count == 0:
             continue
         wq, s, b = oq.random_quantized(n, k, seed=7, group_size=G)
         x = torch.randn(rows, k).bfloat16()
         y = torch.empty(rows, n, dtype=torch.float32)
-        args = (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), rows, k, n, G)
-        lib.qmm_ref(*args)
-        ts = []
-        for _ in range(reps):
+        ops.append((name, count, (x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), rows, k, n, G),
+                    (wq, s, b, x, y)))
+    c = og.make_gdn_case(seed=1, T=T, Hk=cfg.gdn_k_heads, Hv=cfg.gdn_v_heads, Dk=cfg.gdn_dk, Dv=cfg.gdn_dv)
+    q, k_, v, sc = osd.make_sdpa_case(context + T, seed=2, Hq=cfg.q_heads, Hk=cfg.kv_heads, D=cfg.head_dim)
+
+    def evaluate():
+        total, parts = 0.0, {}
+        for name, count, args, _keep in ops:
             t0 = time.perf_counter()
             lib.qmm_ref(*args)
-            ts.append(time.perf_counter() - t0)
-        parts[name] = min(ts)
-        total += count * min(ts)
-    c = og.make_gdn_case(seed=1, T=T, Hk=cfg.gdn_k_heads, Hv=cfg.gdn_v_heads, Dk=cfg.gdn_dk, Dv=cfg.gdn_dv)
-    t0 = time.perf_counter()
-    og.gated_delta_with_tape_ref(c["q"], c["k"], c["v"], c["g"], c["beta"], c["state"])
-    parts["gdn_recurrence"] = time.perf_counter() - t0
-    total += n_gdn * parts["gdn_recurrence"]
-    q, k_, v, sc = osd.make_sdpa_case(context + T, seed=2, Hq=cfg.q_heads, Hk=cfg.kv_heads, D=cfg.head_dim)
-    t0 = time.perf_counter()
-    osd.sdpa_ref(q, k_, v, sc)
-    parts["attention"] = time.perf_counter() - t0
-    total += n_attn * parts["attention"]
-    return {"value": total * 1e6, "unit": "us", "cores": int(lib.qmm_ref_threads()), "kind": "port",
-            "sample": "sum over the step of count x time of each distinct op (every linear shape with the C qmm, best of "
-                      f"{reps}; one GDN recurrence and one attention with the torch oracle); {note}; MLX unavailable on "
-                      "this box: CPU baseline = restatement of the stock path",
-            "parts_ms": {k2: round(v2 * 1e3, 3) for k2, v2 in parts.items()}}
+            parts[name] = time.perf_counter() - t0
+            total += count * parts[name]
+        t0 = time.perf_counter()
+        og.gated_delta_with_tape_ref(c["q"], c["k"], c["v"], c["g"], c["beta"], c["state"])
+        parts["gdn_recurrence"] = time.perf_counter() - t0
+        total += n_gdn * parts["gdn_recurrence"]
+        t0 = time.perf_counter()
+        osd.sdpa_ref(q, k_, v, sc)
+        parts["attention"] = time.perf_counter() - t0
+        total += n_attn * parts["attention"]
+        return total * 1e6, {k2: round(v2 * 1e3, 3) for k2, v2 in parts.items()}, None
+
+    return evaluate, {"unit": "us", "cores": int(lib.qmm_ref_threads()), "kind": "port",
+                      "sample": "sum over the step of count x time of each distinct op (every linear shape once with the C "
+                                f"qmm; one GDN recurrence and one attention with the torch oracle); {note}; MLX unavailable "
+                                "on this box: CPU baseline = restatement of the stock path"}
 
 
 WORKLOADS = {"qmm_cfg1": QmmWorkload, "dense_step_cfg4": DenseStepWorkload, "moe_step_cfg5": MoeStepWorkload,
              "gdn_replay_cfg2": ReplayWorkload,
              "verify_sdpa_cfg3": SdpaWorkload}
 DEFAULT_WORKLOAD = "dense_step_cfg4"
+EXTRA_WORKLOADS = ("qmm_cfg1", "gdn_replay_cfg2")      # reported under "extra" by the default one-GPU run
+wl_extra_holder = []
 
 
 def run_reference_arm(args, rank, world):
-    """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
+    """The reference's CPU implementation of the path on this box's host cores (rank 0 only; MLX is not installable
+    here, so it is the oracle port).  --warmup untimed evaluations of the bounded sample, then --steps timed ones (fewer
+    if 150 s run out): `steps` in the line is the number that ran, the value their median."""
     if rank != 0:
         return
     cls = WORKLOADS[args.workload]
-    budget = max(6.0, min(60.0, 2.0 * (args.steps + args.warmup)))
     if cls is QmmWorkload:
         import torch
         w = cls.__new__(cls)
         w.torch = torch
         w.x_host = torch.randn(cls.M, cls.K, generator=torch.Generator().manual_seed(0xDF1A)).bfloat16()
         w.world, w.n_local = 1, cls.N
-        cb = w.cpu_baseline(budget_s=budget)
+        sample = w.cpu_sample()
         config = {"workload": cls.name, "M": cls.M, "K": cls.K, "N": cls.N, "group_size": cls.G}
     elif cls in (ReplayWorkload, SdpaWorkload):
-        cb = cls.__new__(cls).cpu_baseline(budget_s=budget)
+        sample = cls.__new__(cls).cpu_sample()
         config = {"workload": cls.name}
     else:
         from dflash_mlx_b200.verify_step import HybridConfig
@@ -575,14 +670,16 @@ def run_reference_arm(args, rank, world):
         if moe:
             E, picks = cfg.moe_experts, cfg.block * cfg.moe_top_k
             slots = int(round(cfg.layers * (E * (1.0 - (1.0 - 1.0 / E) ** picks) + 1)))
-        cb = dense_step_cpu_baseline(cfg, cls.CONTEXT, budget, expert_slots=slots)
+        sample = dense_step_cpu_sample(cfg, cls.CONTEXT, expert_slots=slots)
         config = {"workload": cls.name, "layers": cfg.layers, "hidden": cfg.hidden, "context": cls.CONTEXT,
                   "block": cfg.block, "vocab": cfg.vocab}
         if moe:
             config["experts"] = "%d top-%d + shared, inter %d; %d active (expert, layer) pairs assumed" % (
                 cfg.moe_experts, cfg.moe_top_k, cfg.moe_inter, slots)
+    cb = run_cpu_sample(sample, args.warmup, args.steps, budget_s=150.0)
     line = {"impl": "reference", "metric": cls.metric, "value": cb["value"], "unit": cls.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
+            "steps": cb["evaluations"], "steps_requested": args.steps, "warmup": cb["warmup_evaluations"],
+            "ms_per_step": cb["value"] / 1e3,
             "higher_is_better": cls.higher_is_better, "scaling": cls.scaling, "vs_baseline": None, "dtype": cls.dtype,
             "data": "synthetic", "config": config, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -597,6 +694,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the single-op lines that ride along on one GPU")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense step with fewer layers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -676,6 +774,24 @@ def main():
         e2e_s = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
 
+    check = wl.self_check() if hasattr(wl, "self_check") else None
+
+    # ---- on one GPU: the single-op lines of the other configurations ride along (short runs) ----
+    extra = {}
+    if world == 1 and not args.no_extra and args.workload == DEFAULT_WORKLOAD:
+        peak, peak_src = measured_peaks()
+        for name in EXTRA_WORKLOADS:
+            del wl_extra_holder[:]
+            torch.cuda.empty_cache()
+            w2 = WORKLOADS[name](rank, world, device)
+            wl_extra_holder.append(w2)
+            k2 = max(5, args.steps // 2)
+            ms2 = time_graph(w2.step, k2, 3)
+            extra[name] = {"metric": w2.metric, "value": w2.value_from_ms(ms2), "unit": w2.unit, "steps": k2, "warmup": 3,
+                           "dtype": w2.dtype, "config": w2.config, "roofline": w2.roofline(ms2, None, peak, peak_src),
+                           "gpu_launches": w2.launches_per_step * k2}
+        del wl_extra_holder[:]
+
     from dflash_mlx_b200 import _lib
     dev_err = _lib.lib().dflash_device_error(local_rank)
 
@@ -690,8 +806,13 @@ def main():
                         "d2h_bytes_per_step": wl.d2h_bytes, "calls": calls},
                 "gpu_launches": wl.launches_per_step * args.steps,
                 "clocks": clocks, "device_error": dev_err}
+        if check is not None:
+            line["tp_tokens_match" if world > 1 else "fused_tokens_match"] = check["match"]
+            line["self_check"] = check
+        if extra:
+            line["extra"] = extra
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = wl.cpu_baseline()
+            line["cpu_baseline"] = run_cpu_sample(wl.cpu_sample(), 1, 5, budget_s=20.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         # CUDA graphs that captured NCCL kernels are still alive here; tearing the process group down under them can

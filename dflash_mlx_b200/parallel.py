@@ -77,6 +77,17 @@ def _rows(Wq, idx):
     return {"w": Wq["w"][idx].contiguous(), "s": Wq["s"][idx].contiguous(), "b": Wq["b"][idx].contiguous()}
 
 
+def _rows_padded(Wq, idx, n_rows):
+    """Rows ``idx`` followed by zero rows (zero codes, scales and biases: they produce exact zeros) up to ``n_rows``."""
+    out = {}
+    for k in ("w", "s", "b"):
+        t = Wq[k][idx]
+        if n_rows > t.shape[0]:
+            t = torch.cat([t, torch.zeros(n_rows - t.shape[0], t.shape[1], dtype=t.dtype, device=t.device)], dim=0)
+        out[k] = t
+    return out
+
+
 def _cols(Wq, k0, k1, group_size, pad_to=None):
     """Row-parallel slice of a quantised linear: input columns [k0, k1) (multiples of the group size), optionally
     zero-padded on the right to ``pad_to`` columns (zero codes, zero scale and bias)."""
@@ -99,16 +110,17 @@ def _arange(a, b, device):
 def shard_weights(cfg, W, rank: int, world: int):
     """Cuts rank ``rank``'s tensor-parallel shard out of a full set of weights (the dict ``init_weights`` makes).
     Returns ``(local_cfg, local_weights)``.  Requires head counts divisible by ``world`` and an MLP intermediate
-    whose per-rank share is a multiple of 8 quantisation groups."""
+    whose per-rank share is a whole number of quantisation groups; the share is padded with zero rows (gate|up) and
+    zero columns (down) up to the multiple of 8 groups that ``shard_config`` gives the local shape."""
     lc = shard_config(cfg, world)
     if world == 1:
         return lc, W
     G, dev = cfg.group_size, W["norm"].device
     moe = getattr(cfg, "moe_experts", 0) > 0
-    if not moe and (cfg.intermediate % world != 0 or (cfg.intermediate // world) % (8 * G) != 0):
-        raise ValueError("shard_weights needs intermediate/world to be a multiple of 8 groups")
+    if not moe and (cfg.intermediate % world != 0 or (cfg.intermediate // world) % G != 0):
+        raise ValueError("shard_weights needs intermediate/world to be a whole number of quantisation groups")
     I, Il = cfg.intermediate, cfg.intermediate // world
-    lc.intermediate = Il
+    Ilp = lc.intermediate                      # padded local width (a multiple of 8 groups)
     if moe:
         # expert parallel: a contiguous range of routed experts per rank, the shared expert on rank 0, router replicated
         if cfg.moe_experts % world != 0:
@@ -131,8 +143,10 @@ def shard_weights(cfg, W, rank: int, world: int):
                                        lc.moe_e_lo, lc.moe_e_hi, lc.moe_shared_here)
             o.update(router=L["router"], experts_gate_up=gu_l, experts_down=dn_l)
         else:
-            gu_idx = torch.cat([_arange(rank * Il, (rank + 1) * Il, dev), _arange(I + rank * Il, I + (rank + 1) * Il, dev)])
-            o.update(gate_up=_rows(L["gate_up"], gu_idx), down=_cols(L["down"], rank * Il, (rank + 1) * Il, G))
+            gate = _rows_padded(L["gate_up"], _arange(rank * Il, (rank + 1) * Il, dev), Ilp)
+            up = _rows_padded(L["gate_up"], _arange(I + rank * Il, I + (rank + 1) * Il, dev), Ilp)
+            o.update(gate_up={k: torch.cat([gate[k], up[k]], dim=0).contiguous() for k in ("w", "s", "b")},
+                     down=_cols(L["down"], rank * Il, (rank + 1) * Il, G, pad_to=Ilp))
         if cfg.is_attention(i):
             idx = torch.cat([_arange(hq0 * 2 * D, hq1 * 2 * D, dev),
                              _arange(2 * Hq * D + kv0 * D, 2 * Hq * D + kv1 * D, dev),

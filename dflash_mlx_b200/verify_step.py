@@ -53,6 +53,8 @@ def _declare():
                                            _i32, _i32, _vp, ctypes.c_size_t, _vp])
     d("dflash_verify_qmm_fused_supported", _i32, [_i32] * 5)
     d("dflash_verify_qmm_fused", _i32, [_vp] * 6 + [_i32] * 5 + [_c.POINTER(QmmEpilogue), _vp, _c.c_size_t, _vp])
+    d("dflash_gdn_layer_supported", _i32, [_i32] * 8)
+    d("dflash_gdn_layer", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 14 + [_ll] + [_i32] * 6 + [_f32, _i32, _i32, _vp])
     d("dflash_embed_scaled", _i32, [_vp] * 6 + [_i32] * 4 + [_vp])
     _declared = True
 
@@ -255,6 +257,12 @@ class HybridVerifyModel:
                                                                     cfg.head_dim, 0)
             self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
         self.launches_per_step = 0
+        import os
+        # DFLASH_GDN_FUSED=1: one launch per GatedDeltaNet layer between its projections instead of three (fewer launches,
+        # but measured slower inside a step: its long blocks delay the next matmul's start)
+        self.gdn_fused = (os.environ.get("DFLASH_GDN_FUSED", "0") == "1" and bool(self.gdn_layers) and
+                          self.lib.dflash_gdn_layer_supported(T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv,
+                                                              cfg.conv_kernel, _lib.BF16, _lib.F32) == 1)
         self._setup_fused(fused, release_unfused)
 
     # ---- fused epilogues -------------------------------------------------------------------------------
@@ -443,21 +451,30 @@ class HybridVerifyModel:
                 z_off = cfg.conv_dim
                 b_off = z_off + cfg.gdn_v_heads * cfg.gdn_dv
                 a_off = b_off + cfg.gdn_v_heads
-                self._chk(lib.dflash_gdn_prep(self.proj.data_ptr(), ld, z_off, b_off, a_off, self.conv[cur][ig].data_ptr(),
-                                              L["conv_w"].data_ptr(), None, L["A_log"].data_ptr(), L["dt_bias"].data_ptr(),
-                                              self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
-                                              self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), self.conv[nxt][ig].data_ptr(),
-                                              self.tape_qkv[ig].data_ptr(), T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
-                                              cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, st), "dflash_gdn_prep")
-                self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
-                                                      self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
-                                                      self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
-                                                      self.gy.data_ptr(), self.tape[ig].data_ptr(), 1, T, cfg.gdn_k_heads,
-                                                      cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF, _lib.F32, st),
-                          "dflash_gdn_forward_tape")
-                self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
-                                                   self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
-                          "dflash_gated_rmsnorm")
+                if self.gdn_fused:
+                    self._chk(lib.dflash_gdn_layer(
+                        self.proj.data_ptr(), ld, z_off, b_off, a_off, self.conv[cur][ig].data_ptr(), L["conv_w"].data_ptr(),
+                        None, L["A_log"].data_ptr(), L["dt_bias"].data_ptr(), L["g_norm"].data_ptr(),
+                        self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(), self.tape[ig].data_ptr(),
+                        self.tape_k[ig].data_ptr(), self.tape_g[ig].data_ptr(), self.conv[nxt][ig].data_ptr(),
+                        self.tape_qkv[ig].data_ptr(), self.mix_gdn.data_ptr(), self.mix_gdn.shape[1], T, cfg.gdn_k_heads,
+                        cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, _lib.F32, st), "dflash_gdn_layer")
+                else:
+                    self._chk(lib.dflash_gdn_prep(self.proj.data_ptr(), ld, z_off, b_off, a_off, self.conv[cur][ig].data_ptr(),
+                                                  L["conv_w"].data_ptr(), None, L["A_log"].data_ptr(), L["dt_bias"].data_ptr(),
+                                                  self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
+                                                  self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), self.conv[nxt][ig].data_ptr(),
+                                                  self.tape_qkv[ig].data_ptr(), T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
+                                                  cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, st), "dflash_gdn_prep")
+                    self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
+                                                          self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
+                                                          self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
+                                                          self.gy.data_ptr(), self.tape[ig].data_ptr(), 1, T, cfg.gdn_k_heads,
+                                                          cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF, _lib.F32, st),
+                              "dflash_gdn_forward_tape")
+                    self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
+                                                       self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
+                              "dflash_gated_rmsnorm")
                 if fused:
                     self._qmm_fused(self.mix_gdn, L["out_proj"], self.h, self._ep_residual(L["post_norm"], 1))
                 else:

@@ -237,6 +237,22 @@ DFLASH_API int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_
 /* out[t, hv*Dv+d] = rms_norm(y[t,hv,:])[d] * w[d] * silu(z[t,hv,d]), z read from proj at z_off (runtime.py:445). */
 DFLASH_API int dflash_gated_rmsnorm(const void* y, const void* proj, long long ld, int z_off, const void* w, void* out,
                                     int T_rows, int Hv, int Dv, float eps, int dtype, void* stream);
+/* dflash_gdn_prep + dflash_gdn_forward_tape + dflash_gated_rmsnorm of one GatedDeltaNet layer in ONE launch (same
+ * arithmetic in the same order; the last norm's sum of squares is added per 16 rows, so `out` may differ from the
+ * three-call sequence in the last bf16 bit; state, tapes and conv window are bit-identical).  Arguments as in those
+ * calls: proj/ld/offsets, conv window in / out, conv weights, A_log, dt_bias, g_norm_w [Dv]; state_in/out fp32
+ * [Hv,Dv,Dk]; tape fp32 [T,Hv,Dv], tape_k bf16 [T,Hk,Dk], tape_g fp32 [T,Hv], qkv_tape [T,conv_dim]; out [T,out_ld]
+ * receives norm(y) * g_norm_w * silu(z), the input of the output projection (runtime.py:368-445).
+ * Only where dflash_gdn_layer_supported() says 1 (bf16, fp32 state, Dk = 128, Dv % 16 == 0 and <= 128, T_rows <= 16,
+ * conv kernel <= 8); anything else is refused. */
+DFLASH_API int dflash_gdn_layer_supported(int T_rows, int Hk, int Hv, int Dk, int Dv, int conv_kernel, int dtype,
+                                          int state_dtype);
+DFLASH_API int dflash_gdn_layer(const void* proj, long long ld, int z_off, int b_off, int a_off, const void* conv_state,
+                                const void* conv_w, const void* conv_b, const float* A_log, const float* dt_bias,
+                                const void* g_norm_w, const void* state_in, void* state_out, float* tape, void* tape_k,
+                                float* tape_g, void* new_conv_state, void* qkv_tape, void* out, long long out_ld,
+                                int T_rows, int Hk, int Hv, int Dk, int Dv, int conv_kernel, float eps, int dtype,
+                                int state_dtype, void* stream);
 /* Gated attention layer between its projections and the attention kernel (runtime.py:527-555).
  * proj row = [(query D | gate D) x Hq | k Hk*D at k_off | v Hk*D at v_off].  q,k get a per-head RMSNorm with weights
  * and a rotary embedding of the first rope_dims channels (half-split pairing) at position offset + t; q is written as

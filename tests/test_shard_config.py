@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from dflash_mlx_b200 import parallel
-from dflash_mlx_b200.verify_step import HybridConfig
+from dflash_mlx_b200.verify_step import HybridConfig, init_weights
 
 
 def _cfg(**kw):
@@ -61,3 +61,31 @@ def test_vocab_shards_tile_the_vocabulary_and_kv_pairing():
         k_rows = W["layers"][3]["proj"]["w"][2 * Hq * D + kv * D: 2 * Hq * D + (kv + 1) * D]
         assert torch.equal(proj[2 * lc.q_heads * D: 2 * lc.q_heads * D + D], k_rows)
     assert torch.equal(torch.cat(rows), W["lm_head"]["w"])
+
+
+def test_mlp_share_is_padded_with_exact_zeros():
+    """intermediate / ranks need not be a multiple of 8 groups: gate|up gets zero rows, down zero columns, so the padded
+    shard computes exactly what the unpadded one would (the dense model's 17408 over 4 or 8 ranks)."""
+    from oracle import qmm as oq
+    cfg = _cfg(intermediate=1280, layers=1, attn_every=4)      # 1280 / 2 = 640 = 10 groups -> padded to 1024
+    W = init_weights(cfg, 3, "cpu")
+    world = 2
+    x = torch.randn(4, cfg.hidden, generator=torch.Generator().manual_seed(1)).bfloat16()
+    full_gu = oq.qmm_ref(x, W["layers"][0]["gate_up"]["w"], W["layers"][0]["gate_up"]["s"], W["layers"][0]["gate_up"]["b"],
+                         64, out_dtype=torch.float32)
+    I = cfg.intermediate
+    act = (torch.nn.functional.silu(full_gu[:, :I]) * full_gu[:, I:]).bfloat16()
+    D = W["layers"][0]["down"]
+    want = oq.qmm_ref(act, D["w"], D["s"], D["b"], 64, out_dtype=torch.float32)
+    total = torch.zeros_like(want)
+    for r in range(world):
+        lc, lw = parallel.shard_weights(cfg, W, r, world)
+        assert lc.intermediate == 1024
+        gu, dn = lw["layers"][0]["gate_up"], lw["layers"][0]["down"]
+        assert gu["w"].shape[0] == 2 * 1024 and dn["w"].shape[1] * 8 == 1024
+        assert not gu["w"][640:1024].any() and not gu["s"][640:1024].any() and not gu["w"][1024 + 640:].any()
+        y = oq.qmm_ref(x, gu["w"], gu["s"], gu["b"], 64, out_dtype=torch.float32)
+        a = (torch.nn.functional.silu(y[:, :1024]) * y[:, 1024:]).bfloat16()
+        assert not a[:, 640:].any()
+        total += oq.qmm_ref(a, dn["w"], dn["s"], dn["b"], 64, out_dtype=torch.float32)
+    assert torch.allclose(total, want, rtol=1e-4, atol=1e-4)
