@@ -323,6 +323,8 @@ struct AttnPrepArgs {
   int T, Hq, Hk, D, rope_dims, offset;
   float eps, rope_base;
   const int* offset_dev;  // when not NULL the cache offset is read on the device
+  int capacity;           // rows per head the caches hold: a position at or beyond it is not stored
+  int* err;               // device error word (code 31: cache position out of range)
 };
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
@@ -334,7 +336,12 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
   const int t = idx / heads, h = idx % heads;
   const T* row = (const T*)a.proj + (size_t)t * a.ld;
   const int pos = (a.offset_dev ? *a.offset_dev : a.offset) + t;
+  // A stale or mis-advanced device offset must not become a store into a neighbouring allocation: the row is dropped
+  // and the device error word says so (the queries are still written: they live in their own buffer).
+  const bool in_cache = pos >= 0 && pos < a.capacity;
+  if (!in_cache && lane == 0 && h >= a.Hq) atomicCAS(a.err, 0, 31 | (t << 8));
   if (h >= a.Hq + a.Hk) {  // value head: plain copy into the cache
+    if (!in_cache) return;
     const int hk = h - a.Hq - a.Hk;
     T* dst = (T*)a.vcache + (size_t)hk * a.cache_head_stride + (size_t)pos * a.D;
     for (int d = lane; d < a.D; d += 32) dst[d] = row[a.v_off + hk * a.D + d];
@@ -362,7 +369,7 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
       sincos(theta, &sn, &cs);
       o = d < half ? x * (float)cs - xp * (float)sn : xp * (float)sn + x * (float)cs;
     }
-    dst[d] = fromf<T>(o);
+    if (is_q || in_cache) dst[d] = fromf<T>(o);
   }
 }
 
@@ -578,12 +585,18 @@ extern "C" int dflash_gated_rmsnorm(const void* y, const void* proj, long long l
 static int attn_prep_impl(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
                           const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
                           int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
-                          int dtype, void* stream, const int* offset_dev) {
+                          int dtype, void* stream, const int* offset_dev, int capacity) {
   if (!proj || !q_norm_w || !k_norm_w || !q || !kcache || !vcache) return fail(DFLASH_ERR_BAD_ARG, "attn_prep: null operand");
   if (T_rows < 1 || rope_dims < 0 || rope_dims > D || rope_dims % 2 != 0 || offset < 0)
     return fail(DFLASH_ERR_BAD_SHAPE, "attn_prep: bad rope_dims/offset");
+  if (capacity < 1 || (long long)capacity * D > cache_head_stride)
+    return fail(DFLASH_ERR_BAD_SHAPE, "attn_prep: cache capacity %d does not fit the head stride", capacity);
+  if (!offset_dev && offset + T_rows > capacity)
+    return fail(DFLASH_ERR_BAD_SHAPE, "attn_prep: rows %d..%d exceed the cache capacity %d", offset, offset + T_rows - 1, capacity);
+  int device = 0;
+  cudaGetDevice(&device);
   AttnPrepArgs a{proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride,
-                 T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base, offset_dev};
+                 T_rows, Hq, Hk, D, rope_dims, offset, eps, rope_base, offset_dev, capacity, device_error_word(device)};
   const int n = T_rows * (Hq + 2 * Hk);
   cudaStream_t st = (cudaStream_t)stream;
   DFLASH_DISPATCH(dtype, (launch_kernel(attn_prep_kernel<T>, dim3((n + 3) / 4), dim3(128), 0, st, a)));
@@ -591,19 +604,20 @@ static int attn_prep_impl(const void* proj, long long ld, int k_off, int v_off, 
 
 extern "C" int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
                                 const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
-                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
-                                int dtype, void* stream) {
+                                int cache_capacity, int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps,
+                                float rope_base, int dtype, void* stream) {
   return attn_prep_impl(proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride, T_rows, Hq, Hk, D,
-                        rope_dims, offset, eps, rope_base, dtype, stream, nullptr);
+                        rope_dims, offset, eps, rope_base, dtype, stream, nullptr, cache_capacity);
 }
 
 extern "C" int dflash_attn_prep_dev_offset(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
                                            const void* k_norm_w, void* q, void* kcache, void* vcache,
-                                           long long cache_head_stride, int T_rows, int Hq, int Hk, int D, int rope_dims,
-                                           const int* offset_dev, float eps, float rope_base, int dtype, void* stream) {
+                                           long long cache_head_stride, int cache_capacity, int T_rows, int Hq, int Hk,
+                                           int D, int rope_dims, const int* offset_dev, float eps, float rope_base,
+                                           int dtype, void* stream) {
   if (!offset_dev) return fail(DFLASH_ERR_BAD_ARG, "attn_prep_dev_offset: offset_dev is NULL");
   return attn_prep_impl(proj, ld, k_off, v_off, q_norm_w, k_norm_w, q, kcache, vcache, cache_head_stride, T_rows, Hq, Hk, D,
-                        rope_dims, 0, eps, rope_base, dtype, stream, offset_dev);
+                        rope_dims, 0, eps, rope_base, dtype, stream, offset_dev, cache_capacity);
 }
 
 extern "C" int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,

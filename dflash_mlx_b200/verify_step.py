@@ -46,9 +46,9 @@ def _declare():
     d("dflash_argmax", _i32, [_vp, _vp, _i32, _i32, _i32, _vp])
     d("dflash_gdn_prep", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 12 + [_i32] * 6 + [_f32, _i32, _vp])
     d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
-    d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_f32, _f32, _i32, _vp])
+    d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 7 + [_f32, _f32, _i32, _vp])
     d("dflash_attn_post", _i32, [_vp, _vp, _ll, _vp, _ll, _i32, _i32, _i32, _i32, _vp])
-    d("dflash_attn_prep_dev_offset", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 5 + [_vp, _f32, _f32, _i32, _vp])
+    d("dflash_attn_prep_dev_offset", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 6 + [_vp, _f32, _f32, _i32, _vp])
     d("dflash_verify_sdpa_dev_len", _i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _ll, _ll, _ll, _ll, _f32,
                                            _i32, _i32, _vp, ctypes.c_size_t, _vp])
     d("dflash_verify_qmm_fused_supported", _i32, [_i32] * 5)
@@ -327,6 +327,15 @@ class HybridVerifyModel:
     def _st(self):
         return torch.cuda.current_stream(self.dev).cuda_stream
 
+    def check_device_error(self, where: str) -> None:
+        """Reads (and clears) the device-side status word - a kernel that gave up on a bounded wait, or a cache position
+        out of range - and raises.  Synchronises the device: called where the host synchronises anyway."""
+        idx = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
+        code = self.lib.dflash_device_error(idx)
+        if code != 0:
+            raise _lib.DFlashError(f"{where}: device error word {code & 0xFF} (detail {code >> 8}): a kernel abandoned a bounded "
+                                   "wait or refused an out-of-range cache position; the results of the last steps are not valid")
+
     def _chk(self, st, what):
         self.launches_per_step += 1
         _lib.check(st, what)
@@ -421,8 +430,9 @@ class HybridVerifyModel:
                 if dev_off:   # cache position and KV length are read on the device: the captured step serves every cycle
                     self._chk(lib.dflash_attn_prep_dev_offset(
                         self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(), L["k_norm"].data_ptr(),
-                        self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), hs, T, cfg.q_heads,
-                        cfg.kv_heads, cfg.head_dim, cfg.rope_dims, self.offset_dev.data_ptr(), cfg.eps, cfg.rope_base, BF, st),
+                        self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), hs, cfg.max_context, T,
+                        cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_dims, self.offset_dev.data_ptr(), cfg.eps,
+                        cfg.rope_base, BF, st),
                         "dflash_attn_prep_dev_offset")
                     self._chk(lib.dflash_verify_sdpa_dev_len(
                         self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), self.ao.data_ptr(), 1,
@@ -432,8 +442,9 @@ class HybridVerifyModel:
                 else:
                     self._chk(lib.dflash_attn_prep(self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(),
                                                    L["k_norm"].data_ptr(), self.aq.data_ptr(), self.kcache[ia].data_ptr(),
-                                                   self.vcache[ia].data_ptr(), hs, T, cfg.q_heads, cfg.kv_heads, cfg.head_dim,
-                                                   cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st), "dflash_attn_prep")
+                                                   self.vcache[ia].data_ptr(), hs, cfg.max_context, T, cfg.q_heads, cfg.kv_heads,
+                                                   cfg.head_dim, cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st),
+                              "dflash_attn_prep")
                     self._chk(lib.dflash_verify_sdpa(self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(),
                                                      None, self.ao.data_ptr(), 1, cfg.q_heads, cfg.kv_heads, N, cfg.head_dim,
                                                      hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
@@ -534,6 +545,7 @@ class HybridVerifyModel:
         with torch.cuda.stream(side):
             self.verify(self.ids_static)
             torch.cuda.synchronize(self.dev)
+            self.check_device_error("capture (eager pass)")
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=side):
                 self.verify(self.ids_static)
@@ -619,6 +631,7 @@ class HybridVerifyModel:
             ids = torch.zeros(self.cfg.block, dtype=torch.int32, device=self.dev)
         self.verify(ids)
         torch.cuda.synchronize(self.dev)
+        self.check_device_error("moe_active_slots")
         counts = [int(c) for c in self._moe_counts]
         self._moe_counts = None
         self._armed = armed
@@ -656,6 +669,7 @@ class HybridVerifyModel:
     def sync_offset(self) -> int:
         """Reads the device-side position back (synchronises) and tightens ``self.offset`` to it."""
         self.offset = int(self.offset_dev.item())
+        self.check_device_error("sync_offset")
         return self.offset
 
     def cycle(self, block_ids: torch.Tensor) -> torch.Tensor:

@@ -256,11 +256,12 @@ DFLASH_API int dflash_gdn_layer(const void* proj, long long ld, int z_off, int b
 /* Gated attention layer between its projections and the attention kernel (runtime.py:527-555).
  * proj row = [(query D | gate D) x Hq | k Hk*D at k_off | v Hk*D at v_off].  q,k get a per-head RMSNorm with weights
  * and a rotary embedding of the first rope_dims channels (half-split pairing) at position offset + t; q is written as
- * [Hq,T,D]; k and v are appended to the caches [Hk, capacity, D] (cache_head_stride elements per head) at row offset+t. */
+ * [Hq,T,D]; k and v are appended to the caches [Hk, cache_capacity, D] (cache_head_stride >= cache_capacity * D
+ * elements per head) at row offset+t.  offset + T_rows > cache_capacity is refused. */
 DFLASH_API int dflash_attn_prep(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
                                 const void* k_norm_w, void* q, void* kcache, void* vcache, long long cache_head_stride,
-                                int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps, float rope_base,
-                                int dtype, void* stream);
+                                int cache_capacity, int T_rows, int Hq, int Hk, int D, int rope_dims, int offset, float eps,
+                                float rope_base, int dtype, void* stream);
 /* out[t*out_ld + hq*D+d] = o[hq,t,d] * sigmoid(gate[t,hq,d])  (runtime.py:611-612); out_ld >= Hq*D. */
 DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, void* out, long long out_ld, int T_rows,
                                 int Hq, int D, int dtype, void* stream);
@@ -268,14 +269,16 @@ DFLASH_API int dflash_attn_post(const void* o, const void* proj, long long ld, v
 /* ---------------------------------------------------------------------------------------------
  * Variants whose cache position lives on the DEVICE, so that one captured CUDA graph serves every speculative cycle
  * (the reference re-reads its Python-side cache offset each cycle, dflash_mlx/runtime.py:546-550, 878-907; a graph
- * cannot).  dflash_attn_prep_dev_offset = dflash_attn_prep with the offset read from *offset_dev (the caller keeps
- * offset + T within the cache capacity).  dflash_verify_sdpa_dev_len = dflash_verify_sdpa (no mask array) whose KV
+ * cannot).  dflash_attn_prep_dev_offset = dflash_attn_prep with the offset read from *offset_dev; a row whose
+ * position falls outside [0, cache_capacity) is NOT stored and the device error word is set to 31 | row << 8
+ * (dflash_device_error): a stale device scalar cannot write into a neighbouring allocation.  dflash_verify_sdpa_dev_len = dflash_verify_sdpa (no mask array) whose KV
  * length is min(*n_dev, N_max): the split-KV geometry and the workspace are those of N_max, splits beyond the actual
  * length contribute nothing. */
 DFLASH_API int dflash_attn_prep_dev_offset(const void* proj, long long ld, int k_off, int v_off, const void* q_norm_w,
                                            const void* k_norm_w, void* q, void* kcache, void* vcache,
-                                           long long cache_head_stride, int T_rows, int Hq, int Hk, int D, int rope_dims,
-                                           const int* offset_dev, float eps, float rope_base, int dtype, void* stream);
+                                           long long cache_head_stride, int cache_capacity, int T_rows, int Hq, int Hk,
+                                           int D, int rope_dims, const int* offset_dev, float eps, float rope_base,
+                                           int dtype, void* stream);
 DFLASH_API int dflash_verify_sdpa_dev_len(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk,
                                           int N_max, const int* n_dev, int D, long long k_head_stride,
                                           long long k_seq_stride, long long v_head_stride, long long v_seq_stride,
