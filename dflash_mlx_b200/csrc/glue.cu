@@ -169,14 +169,57 @@ __global__ void __launch_bounds__(256) embed_scaled_kernel(const int* __restrict
   if (threadIdx.x == 0) ssq[blockIdx.x] = ss;
 }
 
+// Acceptance and commit of one speculative cycle in one launch (runtime.py:101-108 and 878-907,
+// recurrent_rollback_cache.py:148-171): n = number of leading positions where the drafted tokens block_ids[1..] equal the
+// target's greedy tokens posterior[0..]; steps = n + 1 (positions to commit); the cache position advances by steps; and
+// every GatedDeltaNet layer's conv window becomes rows steps .. steps+keep-1 of [old window ; this step's qkv rows].
+// Every block recomputes n (a few compares); block 0 writes the scalars.  One block per (layer, window row).
+template <typename T>
+__global__ void __launch_bounds__(256) accept_commit_kernel(const int* __restrict__ block_ids, const int* __restrict__ posterior,
+                                                            int n_tokens, int* n_accepted, int* steps, int* offset,
+                                                            int* kv_len, int kv_len_extra, const T* __restrict__ conv_old,
+                                                            const T* __restrict__ qkv_tape, T* __restrict__ conv_new,
+                                                            int layers, int tape_rows, int keep, int conv_dim) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int s_n;
+  if (threadIdx.x == 0) {
+    int n = 0;
+    while (n < n_tokens - 1 && block_ids[n + 1] == posterior[n]) ++n;
+    s_n = n;
+    if (blockIdx.x == 0) {
+      *n_accepted = n;
+      *steps = n + 1;
+      if (offset != nullptr) {
+        const int o = *offset + n + 1;
+        *offset = o;
+        if (kv_len != nullptr) *kv_len = o + kv_len_extra;
+      }
+    }
+  }
+  __syncthreads();
+  if (layers <= 0 || keep <= 0) return;
+  const int st = s_n + 1;
+  const int l = blockIdx.x / keep, r = blockIdx.x % keep;
+  const int src = st + r;  // row of [old window (keep rows) ; qkv rows]
+  const T* from = src < keep ? conv_old + ((size_t)l * keep + src) * conv_dim
+                             : qkv_tape + ((size_t)l * tape_rows + (src - keep)) * conv_dim;
+  T* to = conv_new + ((size_t)l * keep + r) * conv_dim;
+  for (int c = threadIdx.x; c < conv_dim; c += blockDim.x) to[c] = from[c];
+}
+
 // out[t] = index of the first maximum of logits[t, :]  (greedy tokens, runtime.py:90-98)
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int V) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, const uint8_t* __restrict__ suppress,
+                                                      int* __restrict__ out, int V) {
   pdl_wait();
   pdl_trigger();
   __shared__ float sv[32];
   __shared__ int si[32];
   const T* row = logits + (size_t)blockIdx.x * V;
+  // a suppressed token's logit counts as -1e9 rounded to the logits' type (greedy_tokens_with_mask, runtime.py:90-98)
+  const float floor_v = tof<T>(fromf<T>(-1e9f));
+  auto value = [&](float v, int idx) { return (suppress != nullptr && suppress[idx] != 0) ? floor_v : v; };
   float best = -INFINITY;
   int bi = 0x7fffffff;
   // 16-byte loads over the aligned middle of the row, scalar head and tail
@@ -184,7 +227,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
   const int h0 = head < V ? head : V;
   const int nvec = (V - h0) / 8;
   for (int i = threadIdx.x; i < h0; i += blockDim.x) {
-    const float v = tof<T>(row[i]);
+    const float v = value(tof<T>(row[i]), i);
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
   const uint4* rv = (const uint4*)(row + h0);
@@ -193,13 +236,13 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
     const T* ap = (const T*)&a;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float v = tof<T>(ap[j]);
       const int idx = h0 + 8 * i + j;
+      const float v = value(tof<T>(ap[j]), idx);
       if (v > best || (v == best && idx < bi)) { best = v; bi = idx; }
     }
   }
   for (int i = h0 + 8 * nvec + threadIdx.x; i < V; i += blockDim.x) {
-    const float v = tof<T>(row[i]);
+    const float v = value(tof<T>(row[i]), i);
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
 #pragma unroll
@@ -553,7 +596,28 @@ extern "C" int dflash_embed_scaled(const int* ids, const void* table, const void
 extern "C" int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream) {
   if (!logits || !out || T_rows < 1 || V < 1) return fail(DFLASH_ERR_BAD_ARG, "argmax: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (launch_kernel(argmax_kernel<T>, dim3(T_rows), dim3(1024), 0, st, (const T*)logits, out, V)));
+  DFLASH_DISPATCH(dtype, (launch_kernel(argmax_kernel<T>, dim3(T_rows), dim3(1024), 0, st, (const T*)logits, (const uint8_t*)nullptr, out, V)));
+}
+
+extern "C" int dflash_argmax_masked(const void* logits, const uint8_t* suppress, int* out, int T_rows, int V, int dtype,
+                                    void* stream) {
+  if (!logits || !out || T_rows < 1 || V < 1) return fail(DFLASH_ERR_BAD_ARG, "argmax_masked: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  DFLASH_DISPATCH(dtype, (launch_kernel(argmax_kernel<T>, dim3(T_rows), dim3(1024), 0, st, (const T*)logits, suppress, out, V)));
+}
+
+extern "C" int dflash_accept_commit(const int* block_ids, const int* posterior, int n_tokens, int* n_accepted, int* steps,
+                                    int* offset, int* kv_len, int kv_len_extra, const void* conv_old, const void* qkv_tape,
+                                    void* conv_new, int layers, int tape_rows, int keep, int conv_dim, int dtype, void* stream) {
+  if (!block_ids || !posterior || !n_accepted || !steps || n_tokens < 1 || n_tokens > 64)
+    return fail(DFLASH_ERR_BAD_ARG, "accept_commit: bad argument (1..64 tokens)");
+  if (layers > 0 && (!conv_old || !qkv_tape || !conv_new || keep < 0 || conv_dim < 1 || tape_rows < n_tokens || conv_old == conv_new))
+    return fail(DFLASH_ERR_BAD_ARG, "accept_commit: bad conv window arguments");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rows = layers > 0 ? layers * (keep > 0 ? keep : 1) : 1;
+  DFLASH_DISPATCH(dtype, (launch_kernel(accept_commit_kernel<T>, dim3(rows), dim3(256), 0, st, block_ids, posterior, n_tokens,
+                                        n_accepted, steps, offset, kv_len, kv_len_extra, (const T*)conv_old, (const T*)qkv_tape,
+                                        (T*)conv_new, layers, tape_rows, keep, conv_dim)));
 }
 
 extern "C" int dflash_gdn_prep(const void* proj, long long ld, int z_off, int b_off, int a_off, const void* conv_state,

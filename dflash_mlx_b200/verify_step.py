@@ -44,6 +44,8 @@ def _declare():
     d("dflash_swiglu", _i32, [_vp, _vp, _i32, _i32, _i32, _vp])
     d("dflash_embed", _i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp])
     d("dflash_argmax", _i32, [_vp, _vp, _i32, _i32, _i32, _vp])
+    d("dflash_argmax_masked", _i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp])
+    d("dflash_accept_commit", _i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp])
     d("dflash_gdn_prep", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 12 + [_i32] * 6 + [_f32, _i32, _vp])
     d("dflash_gated_rmsnorm", _i32, [_vp, _vp, _ll, _i32, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp])
     d("dflash_attn_prep", _i32, [_vp, _ll, _i32, _i32] + [_vp] * 5 + [_ll] + [_i32] * 7 + [_f32, _f32, _i32, _vp])
@@ -224,6 +226,8 @@ class HybridVerifyModel:
         self.vcache = z(La, cfg.kv_heads, cfg.max_context, cfg.head_dim)
         self.aq = z(cfg.q_heads, T, cfg.head_dim)
         self.ao = z(cfg.q_heads, T, cfg.head_dim)
+        self.aq_short = z(cfg.q_heads, T, cfg.head_dim)   # packed queries / outputs of a block shorter than `block`
+        self._T = T
         self.offset = 0
         self.steps_dev = z(1, dt=torch.int32)
         self.capture_keys = []         # set_capture_layers(): residual-stream snapshots for the draft model's context feature
@@ -303,7 +307,7 @@ class HybridVerifyModel:
     def _qmm_fused(self, x, W, out, ep: QmmEpilogue):
         n, k = W["w"].shape[0], W["w"].shape[1] * 8
         st = self.lib.dflash_verify_qmm_fused(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
-                                              out.data_ptr(), self.cfg.block, k, n, self.cfg.group_size, _lib.BF16,
+                                              out.data_ptr(), self._T, k, n, self.cfg.group_size, _lib.BF16,
                                               _c.byref(ep), self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
         self._chk(st, "dflash_verify_qmm_fused")
 
@@ -344,7 +348,7 @@ class HybridVerifyModel:
         n, k = W["w"].shape[0], W["w"].shape[1] * 8
         # `out` is flat storage: the result is written as a contiguous [T, n] array at its start
         st = self.lib.dflash_verify_qmm(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
-                                        out.data_ptr(), self.cfg.block, k, n, self.cfg.group_size, _lib.BF16,
+                                        out.data_ptr(), self._T, k, n, self.cfg.group_size, _lib.BF16,
                                         self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
         self._chk(st, "dflash_verify_qmm")
 
@@ -367,7 +371,7 @@ class HybridVerifyModel:
 
     def _add_rmsnorm(self, delta, w):
         st = self.lib.dflash_add_rmsnorm(self.h.data_ptr(), _lib.ptr(delta), w.data_ptr(), self.h.data_ptr(),
-                                         self.x.data_ptr(), self.cfg.block, self.cfg.hidden, self.cfg.eps, _lib.BF16, self._st())
+                                         self.x.data_ptr(), self._T, self.cfg.hidden, self.cfg.eps, _lib.BF16, self._st())
         self._chk(st, "dflash_add_rmsnorm")
 
     def prefill_synthetic(self, context_len: int, seed: int) -> None:
@@ -387,14 +391,22 @@ class HybridVerifyModel:
         del prefix_len
         self._armed = True
 
-    def verify(self, ids: torch.Tensor) -> torch.Tensor:
-        """Enqueues the whole step for ``ids`` (int32 CUDA, ``block`` tokens); returns the logits buffer
-        ``[block, vocab]``.  Greedy tokens are left in ``self.tokens``."""
-        cfg, lib, T = self.cfg, self.lib, self.cfg.block
-        if ids.dtype != torch.int32 or not ids.is_cuda or ids.numel() != T:
-            raise ValueError(f"ids must be {T} int32 tokens on the CUDA device")
-        if self.offset + T > cfg.max_context:
+    def verify(self, ids: torch.Tensor, suppress_token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Enqueues the whole step for ``ids`` (int32 CUDA, 1 .. ``block`` tokens: the block length is the draft's,
+        runtime.py:1676-1678, 910-951); returns the logits ``[len(ids), vocab]``.  Greedy tokens are left in
+        ``self.tokens[:len(ids)]``; ``suppress_token_mask`` (bool / uint8 ``[vocab]``, CUDA) removes tokens from the
+        greedy choice as ``greedy_tokens_with_mask`` does (runtime.py:90-98)."""
+        cfg, lib, TB = self.cfg, self.lib, self.cfg.block
+        T = int(ids.numel())
+        if ids.dtype != torch.int32 or not ids.is_cuda or T < 1 or T > TB:
+            raise ValueError(f"ids must be 1..{TB} int32 tokens on the CUDA device")
+        if self.offset + TB > cfg.max_context:
             raise ValueError("KV cache capacity exceeded")
+        if T != TB and self.moe is not None:
+            raise NotImplementedError("blocks shorter than the configured one are not wired through the expert block")
+        if suppress_token_mask is not None and getattr(cfg, "tp_world", 1) > 1:
+            raise NotImplementedError("suppress_token_mask with a vocabulary-parallel lm_head: pass each rank its slice")
+        self._T = T
         dev_off = self.offset_dev is not None
         self.launches_per_step = 0
         self._last_ids = ids
@@ -412,7 +424,7 @@ class HybridVerifyModel:
                                        self.w["embed"].shape[0], BF, st), "dflash_embed")
         delta = None
         ig = ia = 0
-        N = self.offset + T
+        N = self.offset + TB      # keys the attention counts (see the attention branch for blocks shorter than TB)
         for i, L in enumerate(layers):
             if not fused:
                 self._reduce_add_rmsnorm(delta, L["in_norm"])
@@ -427,13 +439,20 @@ class HybridVerifyModel:
                 k_off = 2 * cfg.q_heads * cfg.head_dim
                 v_off = k_off + cfg.kv_heads * cfg.head_dim
                 hs = cfg.max_context * cfg.head_dim
+                # The attention kernel always takes `block` query rows, row r at position N - block + r.  A shorter
+                # block is run as the first T of `block` rows: the queries go through a packed scratch into rows 0..T-1
+                # (the other rows keep stale queries, whose outputs are not read), and N counts `block` new keys - the
+                # rows behind the real ones hold stale cache rows, visible only to those unused query rows.
+                aq = self.aq if T == TB else self.aq_short
                 if dev_off:   # cache position and KV length are read on the device: the captured step serves every cycle
                     self._chk(lib.dflash_attn_prep_dev_offset(
                         self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(), L["k_norm"].data_ptr(),
-                        self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), hs, cfg.max_context, T,
+                        aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), hs, cfg.max_context, T,
                         cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_dims, self.offset_dev.data_ptr(), cfg.eps,
                         cfg.rope_base, BF, st),
                         "dflash_attn_prep_dev_offset")
+                    if T != TB:
+                        self.aq[:, :T].copy_(self.aq_short.view(-1)[: cfg.q_heads * T * cfg.head_dim].view(cfg.q_heads, T, cfg.head_dim))
                     self._chk(lib.dflash_verify_sdpa_dev_len(
                         self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(), self.ao.data_ptr(), 1,
                         cfg.q_heads, cfg.kv_heads, cfg.max_context, self.kvlen_dev.data_ptr(), cfg.head_dim, hs, cfg.head_dim,
@@ -441,16 +460,22 @@ class HybridVerifyModel:
                         "dflash_verify_sdpa_dev_len")
                 else:
                     self._chk(lib.dflash_attn_prep(self.proj.data_ptr(), ld, k_off, v_off, L["q_norm"].data_ptr(),
-                                                   L["k_norm"].data_ptr(), self.aq.data_ptr(), self.kcache[ia].data_ptr(),
+                                                   L["k_norm"].data_ptr(), aq.data_ptr(), self.kcache[ia].data_ptr(),
                                                    self.vcache[ia].data_ptr(), hs, cfg.max_context, T, cfg.q_heads, cfg.kv_heads,
                                                    cfg.head_dim, cfg.rope_dims, self.offset, cfg.eps, cfg.rope_base, BF, st),
                               "dflash_attn_prep")
+                    if T != TB:
+                        self.aq[:, :T].copy_(self.aq_short.view(-1)[: cfg.q_heads * T * cfg.head_dim].view(cfg.q_heads, T, cfg.head_dim))
                     self._chk(lib.dflash_verify_sdpa(self.aq.data_ptr(), self.kcache[ia].data_ptr(), self.vcache[ia].data_ptr(),
                                                      None, self.ao.data_ptr(), 1, cfg.q_heads, cfg.kv_heads, N, cfg.head_dim,
                                                      hs, cfg.head_dim, hs, cfg.head_dim, cfg.head_dim ** -0.5, BF, 0,
                                                      self.sdpa_ws.data_ptr(), self.sdpa_ws.numel(), st), "dflash_verify_sdpa")
                 self.launches_per_step += 1      # partials + combine
-                self._chk(lib.dflash_attn_post(self.ao.data_ptr(), self.proj.data_ptr(), ld, self.mix_attn.data_ptr(),
+                ao = self.ao
+                if T != TB:
+                    ao = self.aq_short       # reused as the packed [heads, T, D] output
+                    ao.view(-1)[: cfg.q_heads * T * cfg.head_dim].view(cfg.q_heads, T, cfg.head_dim).copy_(self.ao[:, :T])
+                self._chk(lib.dflash_attn_post(ao.data_ptr(), self.proj.data_ptr(), ld, self.mix_attn.data_ptr(),
                                                self.mix_attn.shape[1], T, cfg.q_heads, cfg.head_dim, BF, st), "dflash_attn_post")
                 if fused:
                     self._qmm_fused(self.mix_attn, L["o_proj"], self.h, self._ep_residual(L["post_norm"], 1))
@@ -521,21 +546,30 @@ class HybridVerifyModel:
         else:
             self._qmm(self.x, self.w["lm_head"], self.logits)
         v_local = self.w["lm_head"]["w"].shape[0]
-        self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
+        if suppress_token_mask is not None:
+            m8 = suppress_token_mask.to(device=self.dev, dtype=torch.uint8).contiguous()
+            if m8.numel() != v_local:
+                raise ValueError("suppress_token_mask must have one entry per vocabulary item")
+            self._mask_keepalive = m8
+            self._chk(lib.dflash_argmax_masked(self.logits.data_ptr(), m8.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st),
+                      "dflash_argmax_masked")
+        else:
+            self._chk(lib.dflash_argmax(self.logits.data_ptr(), self.tokens.data_ptr(), T, v_local, BF, st), "dflash_argmax")
         if self.all_gather is not None:
             # vocabulary-parallel greedy token: every rank contributes (best logit, global index) per row
             world = getattr(cfg, "tp_world", 1)
             lg = self.logits.view(-1)[: T * v_local].view(T, v_local)
-            vals = lg.gather(1, self.tokens.long()[:, None])[:, 0].float()
+            toks = self.tokens[:T]
+            vals = lg.gather(1, toks.long()[:, None])[:, 0].float()
             rank = torch.distributed.get_rank()
-            pair = torch.stack([vals, (self.tokens + rank * getattr(cfg, 'vocab_offset_stride', v_local)).float()], dim=1).contiguous()
+            pair = torch.stack([vals, (toks + rank * getattr(cfg, 'vocab_offset_stride', v_local)).float()], dim=1).contiguous()
             allp = torch.empty(world * T, 2, dtype=torch.float32, device=self.dev)
             self.all_gather(allp, pair)
             allp = allp.view(world, T, 2)
             best = allp[..., 0].max(dim=0).values
             idx = torch.where(allp[..., 0] == best[None], allp[..., 1], torch.full_like(allp[..., 1], 3e8)).min(dim=0).values
-            self.tokens.copy_(idx.to(torch.int32))
-        return self.logits[:, :v_local] if v_local == self.logits.shape[1] else self.logits.view(-1)[: T * v_local].view(T, v_local)
+            self.tokens[:T].copy_(idx.to(torch.int32))
+        return self.logits.view(-1)[: T * v_local].view(T, v_local)
 
     def capture(self) -> None:
         """Captures one verify pass at the current KV offset into a CUDA graph (replayed by verify_captured)."""
@@ -664,6 +698,7 @@ class HybridVerifyModel:
         becomes an upper bound (each cycle adds a full block) until ``sync_offset`` reads the true value back."""
         self.offset_dev = torch.tensor([self.offset], dtype=torch.int32, device=self.dev)
         self.kvlen_dev = torch.tensor([self.offset + self.cfg.block], dtype=torch.int32, device=self.dev)
+        self.n_acc_dev = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._cycle_graphs = {}
 
     def sync_offset(self) -> int:
@@ -672,23 +707,37 @@ class HybridVerifyModel:
         self.check_device_error("sync_offset")
         return self.offset
 
-    def cycle(self, block_ids: torch.Tensor) -> torch.Tensor:
-        """One speculative cycle for ``block_ids`` = [staged token, 15 drafted tokens] (int32 CUDA): verify pass, greedy
-        posterior, accepted length (runtime.py:101-108), rollback of the recurrent caches to the accepted prefix and
-        advance of the cache position by accepted + 1 - all enqueued, nothing synchronises.  Returns the accepted
-        length as a 1-element int32 CUDA tensor; the posterior tokens are in ``self.tokens``."""
+    def cycle(self, block_ids: torch.Tensor, suppress_token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One speculative cycle for ``block_ids`` = [staged token, drafted tokens] (int32 CUDA, 1 .. ``block`` of them):
+        verify pass, greedy posterior, accepted length (runtime.py:101-108), rollback of the recurrent caches to the
+        accepted prefix and advance of the cache position by accepted + 1 - all enqueued, nothing synchronises.
+        Acceptance, the new position and every layer's conv window are ONE launch (``dflash_accept_commit``), the states
+        one more (``dflash_tape_replay`` with the step count read on the device).  Returns the accepted length as a
+        1-element int32 CUDA tensor; the posterior tokens are in ``self.tokens``."""
         if self.offset_dev is None:
             raise RuntimeError("call enable_device_offset() first")
-        T = self.cfg.block
+        cfg, TB = self.cfg, self.cfg.block
+        T = int(block_ids.numel())
         self.arm_rollback()
-        self.verify(block_ids)
-        n_acc = self.match_acceptance_length(block_ids[1:], self.tokens).reshape(1)
-        self.rollback(n_acc, drafted_tokens=T - 1)
-        self.offset_dev.add_(n_acc + 1)
-        self.kvlen_dev.copy_(self.offset_dev + T)
-        self.offset += T                       # upper bound of the position (see sync_offset)
-        self.n_accepted_dev = n_acc
-        return n_acc
+        self.verify(block_ids, suppress_token_mask)
+        cur, nxt = self.cur, self.cur ^ 1
+        Lg, keep = len(self.gdn_layers), cfg.conv_kernel - 1
+        st = self.lib.dflash_accept_commit(block_ids.data_ptr(), self.tokens.data_ptr(), T, self.n_acc_dev.data_ptr(),
+                                           self.steps_dev.data_ptr(), self.offset_dev.data_ptr(), self.kvlen_dev.data_ptr(), TB,
+                                           self.conv[cur].data_ptr(), self.tape_qkv.data_ptr(), self.conv[nxt].data_ptr(), Lg, TB,
+                                           keep, cfg.conv_dim, _lib.BF16, self._st())
+        _lib.check(st, "dflash_accept_commit")
+        if Lg:
+            st = self.lib.dflash_tape_replay(self.tape.data_ptr(), self.tape_k.data_ptr(), self.tape_g.data_ptr(), None,
+                                             self.state[cur].data_ptr(), self.state[nxt].data_ptr(), Lg, TB, TB,
+                                             self.steps_dev.data_ptr(), cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv,
+                                             0, _lib.BF16, _lib.F32, self._st())
+            _lib.check(st, "dflash_tape_replay")
+        self.cur = nxt
+        self._armed = False
+        self.offset += TB                      # upper bound of the position (see sync_offset)
+        self.n_accepted_dev = self.n_acc_dev
+        return self.n_acc_dev
 
     def cycle_captured(self, block_ids: torch.Tensor) -> torch.Tensor:
         """``cycle`` as ONE graph launch.  A graph is captured per parity of the double-buffered recurrent state (the

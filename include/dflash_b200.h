@@ -224,6 +224,20 @@ DFLASH_API int dflash_embed_scaled(const int* ids, const void* table, const void
                                    int T_rows, int H, int V, int dtype, void* stream);
 /* out[t] = first index of the maximum of logits[t,:]  (greedy_tokens_with_mask, runtime.py:90-98). */
 DFLASH_API int dflash_argmax(const void* logits, int* out, int T_rows, int V, int dtype, void* stream);
+/* The same with the reference's suppress_token_mask: suppress[v] != 0 (uint8[V], device; NULL = none) makes token v's
+ * logit count as -1e9 rounded to the logits' type, as `mx.where(mask, floor, logits)` does (runtime.py:90-98). */
+DFLASH_API int dflash_argmax_masked(const void* logits, const uint8_t* suppress, int* out, int T_rows, int V, int dtype,
+                                    void* stream);
+/* Acceptance and commit of one speculative cycle on the device, one launch (runtime.py:101-108, 878-907;
+ * recurrent_rollback_cache.py:148-171).  block_ids[n_tokens] = [staged token, drafted tokens]; posterior[n_tokens] =
+ * the target's greedy tokens.  *n_accepted = number of leading drafted tokens that match, *steps = *n_accepted + 1;
+ * if offset != NULL: *offset += *steps and (kv_len != NULL) *kv_len = *offset + kv_len_extra.  For each of `layers`
+ * GatedDeltaNet layers conv_new[l] ([keep, conv_dim]) = rows steps..steps+keep-1 of [conv_old[l] ; qkv_tape[l]]
+ * (qkv_tape is [layers, tape_rows, conv_dim]).  layers = 0 skips the conv part.  All pointers are device memory. */
+DFLASH_API int dflash_accept_commit(const int* block_ids, const int* posterior, int n_tokens, int* n_accepted, int* steps,
+                                    int* offset, int* kv_len, int kv_len_extra, const void* conv_old, const void* qkv_tape,
+                                    void* conv_new, int layers, int tape_rows, int keep, int conv_dim, int dtype,
+                                    void* stream);
 /* GatedDeltaNet layer between its input projections and the recurrence (runtime.py:368-403).
  * proj[t, 0:conv_dim] = qkv (q heads | k heads | v heads), z at z_off, b and a (Hv columns each) at b_off, a_off;
  * ld = row stride of proj in elements.  conv_state [Kc-1, conv_dim], conv_w [conv_dim, Kc] (tap j multiplies row t+j

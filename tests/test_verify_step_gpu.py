@@ -286,3 +286,116 @@ def test_hidden_state_capture_for_the_draft_model(setup):
     assert torch.equal(feat[:, : cfg.hidden], m.captured[1]) and torch.equal(feat[:, cfg.hidden:], m.captured[2])
     m.set_capture_layers(())
     m._armed = False
+
+
+def _fresh_model(cfg, Wc, caches, ctx):
+    from dflash_mlx_b200.verify_step import HybridVerifyModel
+    m = HybridVerifyModel(cfg, Wc, "cuda")
+    for l in range(len(caches["state"])):
+        m.state[0][l].copy_(caches["state"][l]); m.conv[0][l].copy_(caches["conv"][l])
+    for l in range(len(caches["k"])):
+        m.kcache[l].copy_(caches["k"][l]); m.vcache[l].copy_(caches["v"][l])
+    m.cur, m.offset = 0, ctx
+    return m
+
+
+def test_device_cycle_against_the_oracle_cycle():
+    """One whole cycle on the device (verify, greedy posterior, acceptance, state replay, conv window, position: the
+    accept/commit kernel + the replay kernel) against the same cycle computed by the CPU oracle alone
+    (runtime.py:101-108, 878-907; recurrent_rollback_cache.py:148-171)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import weights_to
+    cfg, W, caches, ids, ctx = small_case()
+    Wc = weights_to(W, "cuda")
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    T = cfg.block
+    for want in (0, 4, 15):
+        # drafted tokens that agree with the oracle's greedy tokens on the first `want` positions
+        block = ids.clone()
+        for _ in range(want + 1):
+            _, toks, _, _ = om.verify_step_ref(cfg, W, block, clone(caches), ctx)
+            n_now = int(om.match_acceptance_length(block[1:], toks))
+            if n_now >= want:
+                break
+            block[n_now + 1] = toks[n_now]
+        ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, block, clone(caches), ctx)
+        n_ref = int(om.match_acceptance_length(block[1:], ref_toks))
+        if n_ref > want and want < T - 1:
+            block[want + 1] = (ref_toks[want] + 1) % cfg.vocab
+            ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, block, clone(caches), ctx)
+            n_ref = int(om.match_acceptance_length(block[1:], ref_toks))
+        m = _fresh_model(cfg, Wc, caches, ctx)
+        m.enable_device_offset()
+        n_dev = m.cycle(block.cuda())
+        torch.cuda.synchronize()
+        # rows whose greedy choice is clear must agree; then the accepted length can only differ through an unclear row
+        rl = ref_logits.float()
+        top2 = rl.topk(2, dim=-1).values
+        sure = (top2[:, 0] - top2[:, 1]) > 3e-2 * rl.abs().max()
+        assert torch.equal(m.tokens.cpu()[sure], ref_toks[sure])
+        if bool(sure[: n_ref + 1].all()):
+            assert int(n_dev) == n_ref
+        n = int(n_dev)
+        assert int(m.offset_dev) == ctx + n + 1 and int(m.kvlen_dev) == ctx + n + 1 + T
+        for l, tp in enumerate(tapes):
+            want_state = og.tape_replay_ref(tp["tape"][None], tp["k"][None], tp["g"][None], caches["state"][l][None], steps=n + 1)[0]
+            assert _rel(m.state[m.cur][l], want_state) <= (1e-2 if l == 0 else 2e-2), l
+            conv = og.rebuild_conv_state(caches["conv"][l][None], tp["qkv"][None], n + 1, cfg.conv_kernel)[0]
+            if l == 0:
+                assert _rel(m.conv[m.cur][l], conv) <= 1e-2
+        m.check_device_error("test")
+
+
+@pytest.mark.parametrize("T_short", [1, 5, 12])
+def test_blocks_shorter_than_the_configured_one(T_short):
+    """The block length is the draft's (runtime.py:1676-1678): 1 .. block tokens go through the same kernels."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import weights_to
+    cfg, W, caches, ids, ctx = small_case()
+    clone = lambda c: {k: [t.clone() for t in v] for k, v in c.items()}  # noqa: E731
+    short = ids[:T_short].clone()
+    ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, short, clone(caches), ctx)
+    m = _fresh_model(cfg, weights_to(W, "cuda"), caches, ctx)
+    m.arm_rollback()
+    logits = m.verify(short.cuda())
+    torch.cuda.synchronize()
+    assert logits.shape == (T_short, cfg.vocab)
+    assert _rel(logits, ref_logits) <= 3e-2
+    rl = ref_logits.float()
+    top2 = rl.topk(2, dim=-1).values
+    sure = (top2[:, 0] - top2[:, 1]) > 3e-2 * rl.abs().max()
+    assert torch.equal(m.tokens.cpu()[:T_short][sure], ref_toks[sure])
+    for l, tp in enumerate(tapes):
+        assert _rel(m.tape[l][:T_short], tp["tape"]) <= (1e-2 if l == 0 else 2e-2), l
+    # the attention layer appended exactly T_short rows at the right positions
+    assert _rel(m.kcache[0][:, ctx:ctx + T_short], ref_new["k"][0][:, ctx:ctx + T_short]) <= 2e-2
+    # commit 1 + accepted positions of the short block (host path)
+    n_acc = min(2, T_short - 1)
+    m.rollback(n_acc, drafted_tokens=T_short - 1)
+    torch.cuda.synchronize()
+    assert m.offset == ctx + n_acc + 1
+    want = og.tape_replay_ref(tapes[0]["tape"][None], tapes[0]["k"][None], tapes[0]["g"][None], caches["state"][0][None],
+                              steps=n_acc + 1)[0]
+    assert _rel(m.state[m.cur][0], want) <= 1e-2
+    m.check_device_error("test")
+
+
+def test_suppressed_tokens_are_never_the_greedy_choice(setup):
+    """greedy_tokens_with_mask (runtime.py:90-98): masked logits count as -1e9 in the logits' type."""
+    cfg, W, caches, ids, ctx, m = setup
+    m.arm_rollback()
+    plain = m.verify(ids.cuda()).float().clone()
+    toks_plain = m.tokens.clone()
+    mask = torch.zeros(cfg.vocab, dtype=torch.bool, device="cuda")
+    mask[toks_plain.long()] = True                  # suppress every row's winner
+    mask[::7] = True
+    m.arm_rollback()
+    logits = m.verify(ids.cuda(), suppress_token_mask=mask)
+    torch.cuda.synchronize()
+    assert torch.equal(logits.float(), plain)       # the logits themselves are untouched
+    floor = torch.tensor(-1e9, dtype=torch.bfloat16, device="cuda").float()
+    want = torch.where(mask[None, :], floor, logits.float()).argmax(dim=-1).to(torch.int32)
+    assert torch.equal(m.tokens, want)
+    assert not bool(mask[m.tokens.long()].any())
