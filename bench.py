@@ -451,7 +451,7 @@ class ReplayWorkload:
         us = ms_per_step * 1e3 / self.launches_per_step
         ach = self.per_launch_bytes / us / 1e3
         return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                "peak_source": peak_src, "kernel": "gdn_kernel<RECORD=false>", "algorithmic_bytes_per_launch": self.per_launch_bytes,
+                "peak_source": peak_src, "kernel": "tape_replay_pipe_kernel (persistent blocks, bulk-copy pipeline, packed fp32 pair arithmetic)", "algorithmic_bytes_per_launch": self.per_launch_bytes,
                 "us_per_launch": us}
 
     def cpu_sample(self):

@@ -9,6 +9,9 @@
 // and the two per-step row reductions are warp shuffles.  A CTA of 4 warps owns 16 rows of one (batch, head);
 // the step inputs of that head (q, k, gate as fp32, v rows, beta) are staged in shared memory 16 steps at a time.
 // The kernels are pure streaming (state in + state out dominate): HBM bound.
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace dflash {
@@ -215,6 +218,261 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
     if (row0 + r < a.Dv) store_row<ST, NPT>(sout + (size_t)(row0 + r) * Dk + NPT * lane, S[r]);
 }
 
+// ---- tape replay as a pure stream (the common case: scalar gate, no mask, fp32 state, Dk = 128, bf16 k) ----------------
+// S = S * g_t + k_t (x) delta_t over the committed steps is element-wise in S: no reductions, so the kernel is a copy of
+// the state with 2 x steps flops per element in between.  One block = 64 rows of one (layer, head): 8 warps x 8 rows, a
+// lane holds 4 key channels of each of its rows (32 floats), every row a 16-byte load per lane.  The step inputs of the
+// head (k as fp32, the 64 tape rows, the gates: 12 KB) are staged once per block.  Arithmetic is the packed fp32 pair
+// form (mul.f32x2 / fma.rn.f32x2: IEEE per element, so the bits equal the record kernel's), which halves the issue
+// slots - with scalar FMAs the arithmetic would take as long as the memory traffic.
+constexpr int kFastRows = 64, kFastWarps = 8, kFastT = 16;
+
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+__global__ void __launch_bounds__(kFastWarps * 32, 4) tape_replay_stream_kernel(const GdnArgs a) {
+  constexpr int Dk = 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
+  const int row_base = blockIdx.x * kFastRows, row0 = row_base + warp * 8;
+  __shared__ float sk[kFastT][Dk];
+  __shared__ float sd[kFastT][kFastRows];
+  __shared__ float sg[kFastT];
+  // the state rows are nobody's output in this stream position: requested before the wait on the previous kernel
+  const float* sin = (const float*)a.state_in + ((size_t)bh * a.Dv) * Dk;
+  float* sout = (float*)a.state_out + ((size_t)bh * a.Dv) * Dk;
+  unsigned long long S[8][2];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row0 + r < a.Dv) v = *(const float4*)(sin + (size_t)(row0 + r) * Dk + 4 * lane);
+    S[r][0] = pack2(v.x, v.y);
+    S[r][1] = pack2(v.z, v.w);
+  }
+  pdl_wait();
+  pdl_trigger();
+  int steps = a.steps;
+  if (a.steps_dev != nullptr) steps = min(max(*a.steps_dev, 0), a.T);
+  const __nv_bfloat16* kg = (const __nv_bfloat16*)a.k;
+  for (int t0 = 0; t0 < steps; t0 += kFastT) {
+    const int nt = min(kFastT, steps - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * Dk / 2; i += kFastWarps * 32) {  // two bf16 per load
+      const int t = i / (Dk / 2), d2 = i % (Dk / 2);
+      const __nv_bfloat162 v = *(const __nv_bfloat162*)(kg + (((size_t)b * a.T + t0 + t) * a.Hk + hk) * Dk + 2 * d2);
+      sk[t][2 * d2] = __bfloat162float(v.x);
+      sk[t][2 * d2 + 1] = __bfloat162float(v.y);
+    }
+    for (int i = threadIdx.x; i < nt * kFastRows; i += kFastWarps * 32) {
+      const int t = i / kFastRows, r = i % kFastRows, row = row_base + r;
+      sd[t][r] = row < a.Dv ? a.tape_in[(((size_t)b * a.T + t0 + t) * a.Hv + hv) * a.Dv + row] : 0.f;
+    }
+    if (threadIdx.x < nt) sg[threadIdx.x] = a.g[((size_t)b * a.T + t0 + threadIdx.x) * a.Hv + hv];
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float g = sg[t];
+      const unsigned long long gg = pack2(g, g);
+      const float4 kv = *(const float4*)&sk[t][4 * lane];
+      const unsigned long long k01 = pack2(kv.x, kv.y), k23 = pack2(kv.z, kv.w);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float d = sd[t][warp * 8 + r];
+        const unsigned long long dd = pack2(d, d);
+        S[r][0] = fma2(k01, dd, mul2(S[r][0], gg));   // S *= g ; S += k * delta (kernels.py:273-288), two roundings
+        S[r][1] = fma2(k23, dd, mul2(S[r][1], gg));
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    if (row0 + r < a.Dv) {
+      float4 v;
+      unpack2(S[r][0], v.x, v.y);
+      unpack2(S[r][1], v.z, v.w);
+      *(float4*)(sout + (size_t)(row0 + r) * Dk + 4 * lane) = v;
+    }
+}
+
+// ---- the same stream, software-pipelined: one persistent block per SM --------------------------------------------------
+// The kernel above has nothing in flight while a block computes, so with 4 blocks per SM only about half of the bytes the
+// memory system needs outstanding are requested at any time.  Here a producer warp runs kPipeStages tiles ahead with bulk
+// copies (cp.async.bulk: a tile's 32 KB of state and its 16 + 16 rows of k and tape land in shared memory and complete
+// on an mbarrier), and two groups of 8 warps each take every other tile: registers <- shared memory, the steps, then the
+// 16-byte stores.  Same arithmetic, same bits.  Every wait is bounded (device error code 41).
+constexpr int kPipeStages = 5, kPipeGroups = 2;
+constexpr int kPipeStateBytes = kFastRows * 128 * 4;   // 32 KB
+constexpr int kPipeKBytes = kFastT * 128 * 2;          // k of the head, bf16
+constexpr int kPipeTapeBytes = kFastT * kFastRows * 4;
+constexpr int kPipeStageBytes = kPipeStateBytes + kPipeKBytes + kPipeTapeBytes + 128;  // + gates
+constexpr int kPipeThreads = (kPipeGroups * kFastWarps + 1) * 32;
+constexpr size_t kPipeSmem = (size_t)kPipeStages * kPipeStageBytes + 16 * kPipeStages;
+
+__device__ __forceinline__ void tma_load_3d_plain(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kPipeThreads, 1) tape_replay_pipe_kernel(const GdnArgs a, int* __restrict__ err,
+                                                                            const __grid_constant__ CUtensorMap tmK,
+                                                                            const __grid_constant__ CUtensorMap tmTape) {
+  constexpr int Dk = 128;
+  extern __shared__ __align__(128) uint8_t smem[];   // used as is: the compiler then knows these are shared-memory loads
+  uint64_t* bars = (uint64_t*)(smem + (size_t)kPipeStages * kPipeStageBytes);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kPipeStages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_blocks = (a.Dv + kFastRows - 1) / kFastRows;
+  const int tiles = a.B * a.Hv * row_blocks;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPipeStages; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, kFastWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == kPipeGroups * kFastWarps) {
+    // ---------------- producer ----------------
+    pdl_wait();   // k, tape and gates come from the kernels before this one
+    int j = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++j) {
+      const int stage = j % kPipeStages;
+      const uint32_t par = ((j / kPipeStages) & 1) ^ 1;   // first use of a stage passes at once
+      if (!mbar_wait_quiet(bar_empty + 8 * stage, par)) { if (lane == 0) atomicCAS(err, 0, 41 | (j << 8)); break; }
+      const int bh = tile / row_blocks, rb = tile % row_blocks;
+      const int b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
+      const int row_base = rb * kFastRows, rows = min(kFastRows, a.Dv - row_base);
+      uint8_t* st = smem + (size_t)stage * kPipeStageBytes;
+      if (lane == 0) {
+        const int T = min(a.T, kFastT);
+        const uint32_t bytes = (uint32_t)rows * Dk * 4 + (uint32_t)T * (Dk * 2 + kFastRows * 4);
+        const uint32_t full = bar_full + 8 * stage;
+        mbar_arrive_expect_tx(full, bytes);
+        bulk_load_1d(smem_u32(st), (const float*)a.state_in + ((size_t)bh * a.Dv + row_base) * Dk, (uint32_t)rows * Dk * 4, full);
+        const __nv_bfloat16* kg = (const __nv_bfloat16*)a.k;
+        // the head's k rows and the tile's tape rows of all T steps: one tiled copy each (32 small bulk copies took 8 us
+        // of a 52 us launch); columns beyond Dv are filled with zeros
+        tma_load_3d_plain(smem_u32(st + kPipeStateBytes), &tmK, 0, hk, b * a.T, full);
+        tma_load_3d_plain(smem_u32(st + kPipeStateBytes + kPipeKBytes), &tmTape, row_base, hv, b * a.T, full);
+      }
+    }
+  } else {
+    // ---------------- consumers: group = warp / 8 takes this block's tiles j with j % 2 == group ----------------
+    const int group = warp / kFastWarps, w = warp % kFastWarps;
+    pdl_wait();   // the output buffer may still be read by the kernel before this one; the step count is its output
+    pdl_trigger();
+    int steps = a.steps;
+    if (a.steps_dev != nullptr) steps = min(max(*a.steps_dev, 0), a.T);
+    steps = min(steps, kFastT);
+    int j = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++j) {
+      if (j % kPipeGroups != group) continue;
+      const int stage = j % kPipeStages;
+      const uint32_t par = (j / kPipeStages) & 1;
+      const int bh = tile / row_blocks, rb = tile % row_blocks;
+      const int row_base = rb * kFastRows, row0 = row_base + w * 8;
+      // lane t fetches the gate of step t (strided scalars: not worth a bulk copy) while the tile is still landing
+      const float g_mine = lane < a.T ? a.g[((size_t)(bh / a.Hv) * a.T + lane) * a.Hv + (bh % a.Hv)] : 1.f;
+      if (!mbar_wait_quiet(bar_full + 8 * stage, par)) { if (lane == 0) atomicCAS(err, 0, 41 | (j << 8)); break; }
+      const uint8_t* st = smem + (size_t)stage * kPipeStageBytes;
+      const float* ss = (const float*)st;
+      const __nv_bfloat16* skb = (const __nv_bfloat16*)(st + kPipeStateBytes);
+      const float* sd = (const float*)(st + kPipeStateBytes + kPipeKBytes);
+      // fp32 pairs run ACROSS two rows of the same key channel: the two deltas of a row pair then sit next to each other
+      // as they come from shared memory, and only the gate and the four k values have to be duplicated per step
+      unsigned long long S[4][4];
+#pragma unroll
+      for (int rp = 0; rp < 4; ++rp) {
+        const float4 va = *(const float4*)(ss + (size_t)(w * 8 + 2 * rp) * Dk + 4 * lane);
+        const float4 vb = *(const float4*)(ss + (size_t)(w * 8 + 2 * rp + 1) * Dk + 4 * lane);
+        S[rp][0] = pack2(va.x, vb.x); S[rp][1] = pack2(va.y, vb.y); S[rp][2] = pack2(va.z, vb.z); S[rp][3] = pack2(va.w, vb.w);
+      }
+#pragma unroll 4
+      for (int t = 0; t < steps; ++t) {
+        const float g = __shfl_sync(0xffffffffu, g_mine, t);
+        const unsigned long long gg = pack2(g, g);
+        const uint2 kb = *(const uint2*)(skb + t * Dk + 4 * lane);   // four bf16
+        const float k0 = __uint_as_float(kb.x << 16), k1 = __uint_as_float(kb.x & 0xFFFF0000u);
+        const float k2 = __uint_as_float(kb.y << 16), k3 = __uint_as_float(kb.y & 0xFFFF0000u);
+        const unsigned long long kk[4] = {pack2(k0, k0), pack2(k1, k1), pack2(k2, k2), pack2(k3, k3)};
+        const float4 d0 = *(const float4*)(sd + t * kFastRows + w * 8), d1 = *(const float4*)(sd + t * kFastRows + w * 8 + 4);
+        const unsigned long long dp[4] = {pack2(d0.x, d0.y), pack2(d0.z, d0.w), pack2(d1.x, d1.y), pack2(d1.z, d1.w)};
+#pragma unroll
+        for (int rp = 0; rp < 4; ++rp)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            S[rp][i] = fma2(kk[i], dp[rp], mul2(S[rp][i], gg));   // S *= g ; S += k * delta (kernels.py:273-288)
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * stage);   // this warp has read all it needs from the stage
+      float* sout = (float*)a.state_out + ((size_t)bh * a.Dv) * Dk;
+#pragma unroll
+      for (int rp = 0; rp < 4; ++rp) {
+        float4 va, vb;
+        unpack2(S[rp][0], va.x, vb.x); unpack2(S[rp][1], va.y, vb.y); unpack2(S[rp][2], va.z, vb.z); unpack2(S[rp][3], va.w, vb.w);
+        if (row0 + 2 * rp < a.Dv) *(float4*)(sout + (size_t)(row0 + 2 * rp) * Dk + 4 * lane) = va;
+        if (row0 + 2 * rp + 1 < a.Dv) *(float4*)(sout + (size_t)(row0 + 2 * rp + 1) * Dk + 4 * lane) = vb;
+      }
+    }
+  }
+}
+
+// Tensor maps of the pipelined replay: k as [B*T][Hk][128] bf16 with a box of one head over all T steps, the tape as
+// [B*T][Hv][Dv] fp32 with a box of 64 rows of one head over all T steps.  Cached per (pointer, shape).
+struct ReplayMapKey {
+  const void* p; int a, b, c, kind;
+  bool operator==(const ReplayMapKey& o) const { return p == o.p && a == o.a && b == o.b && c == o.c && kind == o.kind; }
+};
+struct ReplayMapKeyHash {
+  size_t operator()(const ReplayMapKey& k) const {
+    return std::hash<const void*>()(k.p) ^ ((size_t)k.a * 1000003u) ^ ((size_t)k.b * 7919u) ^ ((size_t)k.c * 104729u) ^ (size_t)k.kind;
+  }
+};
+std::mutex g_replay_mu;
+std::unordered_map<ReplayMapKey, CUtensorMap, ReplayMapKeyHash> g_replay_maps;
+
+bool get_replay_map(const void* ptr, int rows_bt, int heads, int inner, int T, int kind, CUtensorMap* out) {
+  ReplayMapKey key{ptr, rows_bt, heads, inner * 32 + T, kind};
+  {
+    std::lock_guard<std::mutex> lk(g_replay_mu);
+    auto it = g_replay_maps.find(key);
+    if (it != g_replay_maps.end()) { *out = it->second; return true; }
+  }
+  tensormap_encode_fn enc = get_tensormap_encoder();
+  if (!enc) return false;
+  const size_t es = kind == 0 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)heads, (cuuint64_t)rows_bt};
+  cuuint64_t strides[2] = {(cuuint64_t)inner * es, (cuuint64_t)heads * inner * es};
+  cuuint32_t box[3] = {(cuuint32_t)(kind == 0 ? 128 : kFastRows), 1, (cuuint32_t)T};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> lk(g_replay_mu);
+  if (g_replay_maps.size() > 4096) g_replay_maps.clear();
+  g_replay_maps.emplace(key, m);
+  *out = m;
+  return true;
+}
+
 template <typename IT, typename ST, bool RECORD>
 int launch_npt(const GdnArgs& a, cudaStream_t st) {
   dim3 grid((a.Dv + kRowsPerCta - 1) / kRowsPerCta, a.B * a.Hv);
@@ -267,6 +525,11 @@ int check_common(const GdnArgs& a) {
 
 using namespace dflash;
 
+static int g_replay_stream = 1;
+/* Testing knob: 0 = always the general replay kernel, 1 (default) = the pipelined streaming kernel where it applies,
+ * 2 = the plain streaming kernel. */
+extern "C" void dflash_tape_replay_set_stream_kernel(int mode) { g_replay_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode; }
+
 extern "C" int dflash_gdn_forward_tape(const void* q, const void* k, const void* v, const float* g, const float* beta,
                                        const uint8_t* mask, const void* state_in, void* state_out, void* y,
                                        float* tape, int B, int T, int Hk, int Hv, int Dk, int Dv, int g_is_vector,
@@ -287,5 +550,33 @@ extern "C" int dflash_tape_replay(const float* tape, const void* k, const float*
   GdnArgs a{nullptr, k, nullptr, g, nullptr, mask, state_in, state_out, nullptr, nullptr, tape, steps_dev,
             B, T, steps_dev ? T : steps, Hk, Hv, Dk, Dv, g_is_vector};
   if (int rc = check_common(a)) return rc;
+  if (!g_is_vector && mask == nullptr && Dk == 128 && k_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 && g_replay_stream == 1 &&
+      T <= kFastT && Dv % 4 == 0 && ((uintptr_t)tape & 15) == 0 && ((uintptr_t)k & 15) == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    static bool attr_done[64] = {};
+    if (!attr_done[device & 63]) {
+      cudaError_t e0 = cudaFuncSetAttribute(tape_replay_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPipeSmem);
+      if (e0 != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "tape_replay: %s", cudaGetErrorString(e0));
+      attr_done[device & 63] = true;
+    }
+    CUtensorMap tmK, tmTape;
+    if (get_replay_map(k, B * T, Hk, 128, T, 0, &tmK) && get_replay_map(tape, B * T, Hv, Dv, T, 1, &tmTape)) {
+      const int tiles = B * Hv * ((Dv + kFastRows - 1) / kFastRows);
+      const int sms = sm_count(device);
+      cudaError_t e = launch_kernel(tape_replay_pipe_kernel, dim3(tiles < sms ? tiles : sms), dim3(kPipeThreads), kPipeSmem,
+                                    (cudaStream_t)stream, a, device_error_word(device), tmK, tmTape);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "tape_replay launch: %s", cudaGetErrorString(e));
+      return DFLASH_OK;
+    }
+  }
+  if (!g_is_vector && mask == nullptr && Dk == 128 && k_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 && g_replay_stream) {
+    dim3 grid((Dv + kFastRows - 1) / kFastRows, B * Hv);
+    cudaError_t e = launch_kernel(tape_replay_stream_kernel, grid, dim3(kFastWarps * 32), 0, (cudaStream_t)stream, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "tape_replay launch: %s", cudaGetErrorString(e));
+    return DFLASH_OK;
+  }
   return launch_in<false>(a, k_dtype, state_dtype, (cudaStream_t)stream);
 }

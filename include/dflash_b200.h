@@ -164,6 +164,11 @@ DFLASH_API int dflash_tape_replay(const float* tape, const void* k, const float*
                                   const void* state_in, void* state_out, int B, int T, int steps, const int* steps_dev,
                                   int Hk, int Hv, int Dk, int Dv, int g_is_vector, int k_dtype, int state_dtype,
                                   void* stream);
+/* Testing knob: for scalar gates, no mask, fp32 state, Dk = 128 and bf16 k the replay runs a pure-stream kernel (packed
+ * fp32 pair arithmetic, bit-identical results): 1 (default) = persistent blocks fed by bulk copies through a shared-
+ * memory pipeline (T <= 16, Dv % 4 == 0, 16-byte aligned tape and k), 2 = one block per 64 rows, 0 = the general kernel
+ * everywhere. */
+DFLASH_API void dflash_tape_replay_set_stream_kernel(int mode);
 
 /* ---------------------------------------------------------------------------------------------
  * verify_sdpa: exact softmax attention of 16 query rows per head over N keys (split-KV + combine).

@@ -147,3 +147,30 @@ def test_errors(K):
         K.gated_delta_kernel_with_tape(c["q"].to(d), c["k"].to(d), c["v"].to(d), c["g"].to(d)[0], c["beta"].to(d), c["state"].to(d))
     with pytest.raises(ValueError):
         K.tape_replay_kernel(c["v"].float(), c["k"], c["g"], c["state"])    # CPU tensors
+
+
+@pytest.mark.parametrize("Dv,steps", [(128, 16), (128, 5), (96, 16), (64, 0), (40, 9), (256, 3)])
+def test_streaming_replay_kernel_bit_equal_to_the_general_one(K, Dv, steps):
+    """Scalar gate, no mask, fp32 state, Dk = 128: the replay runs a pure-stream kernel with packed fp32 pair arithmetic.
+    Same bits as the general kernel (and therefore as the forward pass), ragged row counts included."""
+    from dflash_mlx_b200 import _lib
+    lib = _lib.lib()
+    c = og.make_gdn_case(seed=31 + Dv, Hk=4, Hv=8, Dk=128, Dv=Dv)
+    d = "cuda"
+    _, _, tape = og.gated_delta_with_tape_ref(c["q"], c["k"], c["v"], c["g"], c["beta"], c["state"])
+    args = (tape.to(d), c["k"].to(d), c["g"].to(d), c["state"].to(d))
+    fast = K.tape_replay_kernel(*args, steps=steps)                      # persistent, pipelined (the default)
+    steps_dev = torch.tensor([steps], dtype=torch.int32, device=d)
+    fast_dev = K.tape_replay_kernel(*args, steps=steps_dev)
+    try:
+        lib.dflash_tape_replay_set_stream_kernel(2)
+        plain = K.tape_replay_kernel(*args, steps=steps)                 # one block per 64 rows
+        lib.dflash_tape_replay_set_stream_kernel(0)
+        general = K.tape_replay_kernel(*args, steps=steps)
+    finally:
+        lib.dflash_tape_replay_set_stream_kernel(1)
+    torch.cuda.synchronize()
+    assert lib.dflash_device_error(0) == 0
+    assert torch.equal(fast, general) and torch.equal(fast_dev, general) and torch.equal(plain, general)
+    ref = og.tape_replay_ref(tape, c["k"], c["g"], c["state"], steps=steps)
+    assert _rel(fast, ref) <= 1e-4
