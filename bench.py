@@ -696,6 +696,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-op lines that ride along on one GPU")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense step with fewer layers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -743,11 +745,15 @@ def main():
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        if sample and args.profiler_range:
+            torch.cuda.profiler.start()
         e0.record()
         for _ in range(steps):
             graph.replay()
         e1.record()
         barrier()
+        if sample and args.profiler_range:
+            torch.cuda.profiler.stop()
         ms = e0.elapsed_time(e1)
         if world > 1:
             t = torch.tensor([ms], device=device)
