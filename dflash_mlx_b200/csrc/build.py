@@ -10,7 +10,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libdflash_b200.so"
-SOURCES = ["runtime.cu", "qmm.cu", "qmm_tc.cu", "gdn.cu", "gdn_layer.cu", "sdpa.cu", "glue.cu", "peer.cu"]
+SOURCES = ["runtime.cu", "qmm.cu", "qmm_tc.cu", "gdn.cu", "gdn_layer.cu", "sdpa.cu", "sdpa_tc.cu", "glue.cu", "peer.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v"]
 

@@ -42,6 +42,13 @@ void set_k_parts(int k_parts);
 void set_stamps(void* dev);
 }  // namespace tc
 
+namespace sdpa_tc {
+size_t workspace_bytes(int B, int Hq, int N, int D);
+int launch(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk, int N, int D, long long khs,
+           long long kss, long long vhs, long long vss, float scale_log2, const int* n_dev, void* ws, size_t ws_bytes,
+           cudaStream_t st);
+}  // namespace sdpa_tc
+
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel_as(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

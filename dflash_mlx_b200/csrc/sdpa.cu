@@ -365,6 +365,11 @@ int launch(SdpaArgs a, void* ws, size_t ws_bytes, int requested_splits, cudaStre
 
 using namespace dflash;
 
+static int g_sdpa_impl = 0;
+/* Kernel choice: 0 (default) = the tcgen05 kernel (csrc/sdpa_tc.cu) where it applies - bf16, no mask array, automatic
+ * split count, at most 8 query heads per KV head - else the mma.sync kernel; 1 = the mma.sync kernel always. */
+extern "C" void dflash_verify_sdpa_set_impl(int impl) { g_sdpa_impl = impl == 1 ? 1 : 0; }
+
 extern "C" size_t dflash_verify_sdpa_workspace_bytes(int B, int Hq, int Hk, int N, int D, int num_splits) {
   if (B < 1 || Hq < 1 || Hk < 1 || N < 1 || Hq % Hk != 0) return 0;
   int device = 0;
@@ -372,7 +377,12 @@ extern "C" size_t dflash_verify_sdpa_workspace_bytes(int B, int Hq, int Hk, int 
   const int gqa = Hq / Hk, nwarps = gqa < 8 ? gqa : 8, zg = (gqa + nwarps - 1) / nwarps;
   int bps;
   const int splits = choose_splits(N, B * Hk * zg, device, num_splits, &bps);
-  return (size_t)B * Hq * 16 * splits * (D + 2) * sizeof(float) + 256;
+  size_t need = (size_t)B * Hq * 16 * splits * (D + 2) * sizeof(float) + 256;
+  if (num_splits == 0) {   // either kernel may run: enough for both
+    const size_t tc = sdpa_tc::workspace_bytes(B, Hq, N, D);
+    if (tc > need) need = tc;
+  }
+  return need;
 }
 
 static int verify_sdpa_impl(const void* q, const void* k, const void* v, const void* mask, void* out, int B, int Hq,
@@ -395,6 +405,11 @@ static int verify_sdpa_impl(const void* q, const void* k, const void* v, const v
   a.scale_log2 = scale * kLog2e;
   a.n_dev = n_dev;
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DFLASH_BF16 && mask == nullptr && num_splits == 0 && g_sdpa_impl == 0) {
+    const int rc = sdpa_tc::launch(q, k, v, out, B, Hq, Hk, N, D, k_head_stride, k_seq_stride, v_head_stride, v_seq_stride,
+                                   a.scale_log2, n_dev, workspace, workspace_bytes, st);
+    if (rc <= 0) return rc;
+  }
   if (dtype == DFLASH_BF16)
     return D == 128 ? launch<__nv_bfloat16, 128>(a, workspace, workspace_bytes, num_splits, st)
                     : launch<__nv_bfloat16, 256>(a, workspace, workspace_bytes, num_splits, st);

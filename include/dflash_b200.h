@@ -188,6 +188,12 @@ DFLASH_API int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
                                   int Hq, int Hk, int N, int D, long long k_head_stride, long long k_seq_stride,
                                   long long v_head_stride, long long v_seq_stride, float scale, int dtype,
                                   int num_splits, void* workspace, size_t workspace_bytes, void* stream);
+/* Kernel choice for verify_sdpa: 0 (default) = the tcgen05 kernel (K/V by TMA, S = Q K^T and O = P V on the tensor
+ * cores with S / P / O in tensor memory, 256 keys per block, bf16 partials) where it applies - bf16, no mask array,
+ * num_splits = 0, at most 8 query heads per KV head - else the mma.sync kernel; 1 = the mma.sync kernel always.  With
+ * the device-side KV length (dflash_verify_sdpa_dev_len) the tcgen05 kernel reads cache rows up to the next multiple of
+ * 64 beyond the length: they must hold finite values (they get weight zero). */
+DFLASH_API void dflash_verify_sdpa_set_impl(int impl);
 
 /* verify_sdpa for callers that cannot allocate device memory.  (No counterpart in the reference.)
  * Some hosts of this library - a serving loop that has handed all device memory to its own pool, code
