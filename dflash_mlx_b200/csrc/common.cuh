@@ -43,6 +43,8 @@ void set_stamps(void* dev);
 }  // namespace tc
 
 namespace sdpa_tc {
+void set_fuse_combine(int on);
+void set_split128(int on);
 size_t workspace_bytes(int B, int Hq, int N, int D);
 int launch(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk, int N, int D, long long khs,
            long long kss, long long vhs, long long vss, float scale_log2, const int* n_dev, void* ws, size_t ws_bytes,

@@ -368,7 +368,11 @@ using namespace dflash;
 static int g_sdpa_impl = 0;
 /* Kernel choice: 0 (default) = the tcgen05 kernel (csrc/sdpa_tc.cu) where it applies - bf16, no mask array, automatic
  * split count, at most 8 query heads per KV head - else the mma.sync kernel; 1 = the mma.sync kernel always. */
-extern "C" void dflash_verify_sdpa_set_impl(int impl) { g_sdpa_impl = impl == 1 ? 1 : 0; }
+extern "C" void dflash_verify_sdpa_set_impl(int impl) {
+  g_sdpa_impl = impl == 1 ? 1 : 0;
+  sdpa_tc::set_fuse_combine(impl == 2 ? 1 : 0);   // 2 = the tcgen05 kernel with the combine pass inside the same launch
+  sdpa_tc::set_split128(impl == 3 ? 1 : 0);       // 3 = the tcgen05 kernel with 128 keys per block while the grid fits the SMs
+}
 
 extern "C" size_t dflash_verify_sdpa_workspace_bytes(int B, int Hq, int Hk, int N, int D, int num_splits) {
   if (B < 1 || Hq < 1 || Hk < 1 || N < 1 || Hq % Hk != 0) return 0;

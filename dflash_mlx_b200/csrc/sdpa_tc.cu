@@ -16,6 +16,7 @@
 // The four K blocks land in four 32 KB buffers (D = 256); as soon as the MMAs of block b are done its buffer takes
 // V block b, which therefore streams in while the softmax runs.  Partials: bf16 O + fp32 max / sum; the combine pass is
 // the second launch.  Every wait is bounded (device error code 51); no mask array, bf16 only, <= 8 heads per KV head.
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -27,13 +28,15 @@ namespace sdpa_tc {
 constexpr int kKeys = 256, kBlk = 64, kBufs = 4, kRows = 128;
 constexpr int kSoftWarps = 4, kProducerWarp = 4, kMmaWarp0 = 5, kThreads = 9 * 32;
 constexpr uint32_t kTmemCols = 512, kOCol0 = 256;
+constexpr int kFuseMaxSplits = 128;   // most key ranges per head the one-launch combine handles
 
 struct Args {
   const float* scale_dummy;
   void* out; __nv_bfloat16* part_o; float* part_m; float* part_l;
-  int B, Hq, Hk, N, gqa, splits;
+  int B, Hq, Hk, N, gqa, splits, keys_per_split;
   float scale_log2;
   const int* n_dev;
+  unsigned* counters;   // non-NULL: the blocks of a KV head meet after pass 1 and share pass 2 between them (one launch)
 };
 
 // Bounded wait (hardware-suspended polls): gives up after ~2^16 polls of a few microseconds each (a fraction of a second).
@@ -168,8 +171,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   pdl_wait();      // q and the newest cache rows are the previous kernels' output
   pdl_trigger();
   const int N = a.n_dev ? max(16, min(*a.n_dev, a.N)) : a.N;
-  const int k0 = split * kKeys;
-  const int nkeys = max(0, min(kKeys, N - k0));
+  const int k0 = split * a.keys_per_split;
+  const int nkeys = max(0, min(a.keys_per_split, N - k0));
   const int nblk = (nkeys + kBlk - 1) / kBlk;
 
   if (warp == kProducerWarp) {
@@ -299,10 +302,94 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       a.part_m[grow * a.splits + split] = (m == -INFINITY) ? -INFINITY : m * a.scale_log2;
       a.part_l[grow * a.splits + split] = l;
     }
+    __threadfence();   // the partials are read by other blocks when pass 2 runs inside this launch
   }
   fence_before();
   __syncthreads();
   if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+  if (a.counters == nullptr || a.splits == 1) return;
+  // ---------------- pass 2 inside the same launch ----------------
+  // Every block of this KV head has been launched (the host takes this path only when the whole grid is resident: at most
+  // one block per SM), so the blocks can wait for each other: arrive on the head's counter, wait (bounded) until all
+  // `splits` blocks have, then each block combines its share of the head group's rows (kernels.py:595-637).
+  __shared__ float c_w[kThreads / 32][kFuseMaxSplits];   // per warp: the weights of the row it is combining
+  __shared__ int c_ok;
+  unsigned* arrived = a.counters + 2 * bhk;
+  unsigned* done = arrived + 1;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(arrived, 1u);
+    int ok = 0;
+    for (unsigned spins = 0; spins < (1u << 22); ++spins) {
+      unsigned c;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(arrived) : "memory");
+      if (c >= (unsigned)a.splits) { ok = 1; break; }
+      __nanosleep(64);
+    }
+    if (!ok) atomicCAS(err, 0, 51 | (7 << 8));
+    c_ok = ok;
+  }
+  __syncthreads();
+  if (c_ok) {
+    // a warp combines one row at a time (no block-wide barrier): lane = 8 channels, 16-byte loads of the bf16 partials
+    const int rows_head = a.gqa * 16;
+    constexpr int kLanes = D / 8;
+    float* w_row = c_w[warp];
+    for (int rr = split + warp * a.splits; rr < rows_head; rr += a.splits * (kThreads / 32)) {
+      const size_t row = ((size_t)b * a.Hq + hk * a.gqa) * 16 + rr;
+      const float* pm = a.part_m + row * a.splits;
+      const float* pl = a.part_l + row * a.splits;
+      float mx = -INFINITY;
+      for (int sidx = lane; sidx < a.splits; sidx += 32) mx = fmaxf(mx, __ldcg(pm + sidx));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float ref = (mx == -INFINITY) ? 0.f : mx;
+      float den = 0.f;
+      __syncwarp();
+      for (int sidx = lane; sidx < a.splits; sidx += 32) {
+        const float w = exp2f(__ldcg(pm + sidx) - ref);
+        w_row[sidx] = w;
+        den += w * __ldcg(pl + sidx);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+      __syncwarp();
+      if (lane < kLanes) {
+        const uint4* po = (const uint4*)(a.part_o + row * a.splits * D) + lane;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int sidx = 0; sidx < a.splits; ++sidx) {   // split order: the same sum as the combine kernel's per channel
+          const uint4 v = __ldcg(po + (size_t)sidx * (D / 8));
+          const float w = w_row[sidx];
+          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] = fmaf(w, __uint_as_float(u[e] << 16), acc[2 * e]);
+            acc[2 * e + 1] = fmaf(w, __uint_as_float(u[e] & 0xFFFF0000u), acc[2 * e + 1]);
+          }
+        }
+        const float inv = den == 0.f ? 1.f : 1.f / den;
+        uint4 o4;
+        uint32_t* op = (uint32_t*)&o4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+          op[e] = *(uint32_t*)&h;
+        }
+        *((uint4*)((__nv_bfloat16*)a.out + row * D) + lane) = o4;
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned d = atomicAdd(done, 1u);
+    if (d == (unsigned)a.splits - 1) {   // the last block to finish: nobody reads the counters any more
+      *arrived = 0;
+      *done = 0;
+    }
+  }
 }
 
 // pass 2 with bf16 partial outputs: out = sum_s w_s O_s / sum_s w_s l_s, w_s = exp2(m_s - max_s m_s) (kernels.py:595-637)
@@ -406,10 +493,30 @@ bool get_map(const void* ptr, int kind, long long rows_or_n, int D, long long he
   return true;
 }
 
-int splits_for(int N) { return (N + kKeys - 1) / kKeys; }
+extern int g_split128;
+// Keys per block: 256 (the accumulator width); optionally 128 while that still leaves the grid within one block per SM (more
+// SMs stream the cache, at the price of twice the partials: measured no faster, so off by default).
+int keys_per_split(int N, int heads, int device) {
+  const int s128 = (N + 127) / 128;
+  return (g_split128 && (long long)s128 * heads <= sm_count(device)) ? 128 : kKeys;
+}
+int splits_for(int N, int heads, int device) {
+  const int kp = keys_per_split(N, heads, device);
+  return (N + kp - 1) / kp;
+}
+
+// Arrival / completion counters of the one-launch path: kSlots sets of 2 words per KV head, zero when idle (the last
+// block of a head resets its pair).  Launches take the sets round robin, so launches in flight on different streams
+// do not share one unless more than kSlots are in flight.
+constexpr int kSlots = 64, kSlotHeads = 1024;
+__device__ unsigned g_counters[kSlots * kSlotHeads * 2];
+unsigned* g_counters_ptr[64] = {};
+std::atomic<unsigned> g_slot{0};
+int g_fuse_combine = 0;
+int g_split128 = 0;
 
 size_t workspace_bytes(int B, int Hq, int N, int D) {
-  const size_t rows = (size_t)B * Hq * 16, s = (size_t)splits_for(N);
+  const size_t rows = (size_t)B * Hq * 16, s = (size_t)((N + 127) / 128);   // the finer of the two splittings
   return s > 1 ? rows * s * ((size_t)D * 2 + 8) + 256 : 0;
 }
 
@@ -423,11 +530,13 @@ int launch_d(const void* q, const void* k, const void* v, void* out, int B, int 
       !get_map(v, 1, N, D, (long long)B * Hk, vss, vhs, &tv))
     return 1;
   Args a{};
-  a.out = out; a.B = B; a.Hq = Hq; a.Hk = Hk; a.N = N; a.gqa = Hq / Hk; a.splits = splits_for(N);
+  a.out = out; a.B = B; a.Hq = Hq; a.Hk = Hk; a.N = N; a.gqa = Hq / Hk;
+  a.keys_per_split = keys_per_split(N, B * Hk, device);
+  a.splits = splits_for(N, B * Hk, device);
   a.scale_log2 = scale_log2; a.n_dev = n_dev;
   const size_t rows = (size_t)B * Hq * 16;
   if (a.splits > 1) {
-    const size_t need = workspace_bytes(B, Hq, N, D);
+    const size_t need = rows * a.splits * ((size_t)D * 2 + 8);
     if (!ws || ws_bytes < need) return fail(DFLASH_ERR_WORKSPACE, "verify_sdpa needs %zu workspace bytes, got %zu", need, ws_bytes);
     if ((uintptr_t)ws & 15) return fail(DFLASH_ERR_MISALIGNED, "verify_sdpa workspace must be 16-byte aligned");
     a.part_o = (__nv_bfloat16*)ws;
@@ -442,10 +551,22 @@ int launch_d(const void* q, const void* k, const void* v, void* out, int B, int 
     if (e0 != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e0));
     attr_done[device & 63] = true;
   }
+  // pass 2 inside the same launch when every block is resident at once (one block per SM) and the heads fit a counter set
+  const bool fuse = g_fuse_combine && a.splits > 1 && a.splits <= kFuseMaxSplits && a.splits * B * Hk <= sm_count(device) && B * Hk <= kSlotHeads &&
+                    device >= 0 && device < 64;
+  if (fuse) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_counters_ptr[device] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_counters) != cudaSuccess || p == nullptr) return fail(DFLASH_ERR_LAUNCH, "sdpa: counter symbol");
+      g_counters_ptr[device] = (unsigned*)p;
+    }
+    a.counters = g_counters_ptr[device] + (size_t)(g_slot.fetch_add(1) % kSlots) * kSlotHeads * 2;
+  }
   cudaError_t e = launch_kernel(kern, dim3(a.splits, B * Hk), dim3(kThreads), smem, st, tq, tk, tv, a, device_error_word(device));
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa (tcgen05) launch: %s", cudaGetErrorString(e));
-  if (a.splits > 1) {
+  if (a.splits > 1 && !fuse) {
     e = launch_kernel(combine_kernel<D>, dim3((unsigned)rows), dim3(D), 0, st, a);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "sdpa combine launch: %s", cudaGetErrorString(e));
@@ -453,11 +574,14 @@ int launch_d(const void* q, const void* k, const void* v, void* out, int B, int 
   return DFLASH_OK;
 }
 
+void set_fuse_combine(int on) { g_fuse_combine = on ? 1 : 0; }
+void set_split128(int on) { g_split128 = on ? 1 : 0; }
+
 // Returns DFLASH_OK, a negative status, or +1 when the shape is not handled here (the caller then runs csrc/sdpa.cu).
 int launch(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk, int N, int D, long long khs,
            long long kss, long long vhs, long long vss, float scale_log2, const int* n_dev, void* ws, size_t ws_bytes,
            cudaStream_t st) {
-  if (Hq % Hk != 0 || (Hq / Hk) * 16 > kRows || (long long)B * Hk > 65535 || splits_for(N) > 1024) return 1;
+  if (Hq % Hk != 0 || (Hq / Hk) * 16 > kRows || (long long)B * Hk > 65535 || (N + 127) / 128 > 1024) return 1;
   if (D == 256) return launch_d<256>(q, k, v, out, B, Hq, Hk, N, khs, kss, vhs, vss, scale_log2, n_dev, ws, ws_bytes, st);
   if (D == 128) return launch_d<128>(q, k, v, out, B, Hq, Hk, N, khs, kss, vhs, vss, scale_log2, n_dev, ws, ws_bytes, st);
   return 1;

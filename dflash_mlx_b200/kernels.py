@@ -130,6 +130,11 @@ def _ensure_sdpa_declared():
     _lib.declare("dflash_verify_sdpa_workspace_bytes", _c.c_size_t, [_i32] * 6)
     _lib.declare("dflash_verify_sdpa", _i32,
                  [_vp] * 5 + [_i32] * 5 + [ll] * 4 + [_f32, _i32, _i32, _vp, _c.c_size_t, _vp])
+    _lib.declare("dflash_verify_sdpa_set_impl", None, [_i32])
+    import os
+    impl = {"tcgen05": 0, "mma.sync": 1, "tcgen05_1launch": 2, "tcgen05_128": 3}.get(os.environ.get("DFLASH_VERIFY_SDPA_VARIANT", ""), None)
+    if impl is not None:        # kernel choice of the verify attention (default: tcgen05)
+        _lib.lib().dflash_verify_sdpa_set_impl(impl)
     _sdpa_declared = True
 
 

@@ -190,7 +190,10 @@ DFLASH_API int dflash_verify_sdpa(const void* q, const void* k, const void* v, c
                                   int num_splits, void* workspace, size_t workspace_bytes, void* stream);
 /* Kernel choice for verify_sdpa: 0 (default) = the tcgen05 kernel (K/V by TMA, S = Q K^T and O = P V on the tensor
  * cores with S / P / O in tensor memory, 256 keys per block, bf16 partials) where it applies - bf16, no mask array,
- * num_splits = 0, at most 8 query heads per KV head - else the mma.sync kernel; 1 = the mma.sync kernel always.  With
+ * num_splits = 0, at most 8 query heads per KV head - else the mma.sync kernel; 1 = the mma.sync kernel always; 2 = as 0
+ * but with the combine pass inside the same launch (the blocks of a KV head meet on a counter and share it) whenever the
+ * whole grid is resident, i.e. has at most one block per SM - measured slower than the second launch, so not the
+ * default; 3 = as 0 with 128 keys per block while that keeps the grid within one block per SM (no faster either).  With
  * the device-side KV length (dflash_verify_sdpa_dev_len) the tcgen05 kernel reads cache rows up to the next multiple of
  * 64 beyond the length: they must hold finite values (they get weight zero). */
 DFLASH_API void dflash_verify_sdpa_set_impl(int impl);
