@@ -276,6 +276,7 @@ class HybridVerifyModel:
         matmul to its accumulators), the residual add is the producer's epilogue and SwiGLU the gate|up epilogue."""
         import os
         cfg, T = self.cfg, self.cfg.block
+        explicit_off = fused is False
         ok = self.moe is None and self.all_reduce is None and self.peer is None and getattr(cfg, "tp_world", 1) == 1
         if ok:
             mats = [self.w["lm_head"]]
@@ -288,6 +289,15 @@ class HybridVerifyModel:
         elif fused and not ok:
             raise ValueError("the fused step needs a dense, unsharded model whose matmuls are bf16 / group 64 / K % 512 == 0")
         self.fused = bool(fused)
+        # SwiGLU inside the gate|up epilogue also works for a tensor-parallel shard (nothing is summed over the ranks
+        # between gate|up and SwiGLU): one launch less per layer
+        self.fused_swiglu = False
+        if (not self.fused and self.moe is None and not explicit_off and os.environ.get("DFLASH_STEP_FUSED", "1") != "0"):
+            self.fused_swiglu = all(
+                self.lib.dflash_verify_qmm_fused_supported(T, L["gate_up"]["w"].shape[1] * 8, L["gate_up"]["w"].shape[0],
+                                                           cfg.group_size, _lib.BF16) == 1 for L in self.w["layers"])
+        if self.fused_swiglu:
+            self.gate_up_il = [self._interleave_gate_up(L["gate_up"]) for L in self.w["layers"]]
         if not self.fused:
             return
         H = cfg.hidden
@@ -297,12 +307,16 @@ class HybridVerifyModel:
         self.ssq_parts = parts
         self.gate_up_il = []
         for L in self.w["layers"]:
-            W = L["gate_up"]
-            n = W["w"].shape[0]
-            order = torch.arange(n, device=W["w"].device).view(2, n // 2).t().reshape(-1)   # gate_0, up_0, gate_1, ...
-            self.gate_up_il.append({k: W[k].index_select(0, order).contiguous() for k in ("w", "s", "b")})
+            self.gate_up_il.append(self._interleave_gate_up(L["gate_up"]))
             if release_unfused:
                 L["gate_up"] = None
+
+    @staticmethod
+    def _interleave_gate_up(W):
+        """[gate rows | up rows] -> gate_0, up_0, gate_1, up_1, ... (the row order the SwiGLU epilogue pairs up)."""
+        n = W["w"].shape[0]
+        order = torch.arange(n, device=W["w"].device).view(2, n // 2).t().reshape(-1)
+        return {k: W[k].index_select(0, order).contiguous() for k in ("w", "s", "b")}
 
     def _qmm_fused(self, x, W, out, ep: QmmEpilogue):
         n, k = W["w"].shape[0], W["w"].shape[1] * 8
@@ -532,9 +546,12 @@ class HybridVerifyModel:
                 if self._moe_counts is not None:
                     self._moe_counts.append(self.moe.n_active.clone())
             else:
-                self._qmm(self.x, L["gate_up"], self.gu)
-                self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2, BF, st),
-                          "dflash_swiglu")
+                if self.fused_swiglu:
+                    self._qmm_fused(self.x, self.gate_up_il[i], self.act, QmmEpilogue(mode=2))
+                else:
+                    self._qmm(self.x, L["gate_up"], self.gu)
+                    self._chk(lib.dflash_swiglu(self.gu.data_ptr(), self.act.data_ptr(), T, L["gate_up"]["w"].shape[0] // 2,
+                                                BF, st), "dflash_swiglu")
                 self._qmm(self.act, L["down"], self.delta)
             delta = self.delta
         if not fused:
@@ -617,7 +634,10 @@ class HybridVerifyModel:
             if self.moe is not None:
                 out.append((self.x, L["router"], self.router_logits[i], None))   # the expert matmuls are not in this list
             else:
-                out.append((self.x, L["gate_up"], self.gu, None))
+                if getattr(self, "fused_swiglu", False):
+                    out.append((self.x, self.gate_up_il[i], self.act, QmmEpilogue(mode=2)))
+                else:
+                    out.append((self.x, L["gate_up"], self.gu, None))
                 out.append((self.act, L["down"], self.delta, None))
         out.append((self.hw if fused else self.x, self.w["lm_head"], self.logits, self._ep_in(0, in_parts) if fused else None))
         return out
