@@ -262,6 +262,10 @@ class DenseStepWorkload:
                        "algorithmic_bytes_per_step_per_rank": self.bytes,
                        "l2": "inputs larger than L2: one step streams %.1f GB of weights" % (self.bytes["qmm"] / 1e9),
                        "parallelism": f"tp{world}", "row_parallel_reduce": self.reduce_mode}
+        if self.MOE and world > 1:
+            # "none": every rank holds all tokens, partial expert outputs are summed like any row-parallel output;
+            # "a2a": dispatch + combine all-to-all collectives (DFLASH_MOE_EXCHANGE=a2a)
+            self.config["expert_exchange"] = self.model.moe_exchange
 
     def step(self):
         self.model.verify(self.ids)
@@ -293,6 +297,11 @@ class DenseStepWorkload:
         other.prefill_synthetic(self.CONTEXT, 0xDF1D)
         la = self.model.verify(self.ids).float()
         ta = self.model.tokens.clone()
+        if self.MOE:
+            # both passes route by the first one's router logits: with the random-init router the top-k weights are
+            # nearly equal, so rounding noise that flips the k-th expert changes a row by ~1/k of its expert output
+            other.routing_from = self.model.router_logits
+            what += " (same routing)"
         lb = other.verify(self.ids).float()
         tb = other.tokens.clone()
         torch.cuda.synchronize()

@@ -185,7 +185,7 @@ class HybridVerifyModel:
     intermediate dimension and the vocabulary are split; ``all_reduce`` sums the row-parallel outputs)."""
 
     def __init__(self, cfg: HybridConfig, weights: Dict, device, *, all_reduce=None, all_gather=None, peer=None,
-                 fused: Optional[bool] = None, release_unfused: bool = False):
+                 fused: Optional[bool] = None, release_unfused: bool = False, moe_exchange: Optional[str] = None):
         """``fused`` (default: wherever it applies, environment ``DFLASH_STEP_FUSED=0`` turns it off): RMSNorms, residual
         adds and SwiGLU run inside the matmuls' epilogues.  The gate|up rows are then kept interleaved in a copy;
         ``release_unfused`` drops the caller's original from ``weights`` to give the memory back."""
@@ -262,6 +262,23 @@ class HybridVerifyModel:
             self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
         self.launches_per_step = 0
         import os
+        self._delta_is_full = False
+        # router logits [layers, block, experts + 1] of another pass to route by instead of this pass's own (comparing two
+        # formulations of one step: a near-tie in the top-k is a discontinuity, not an arithmetic difference)
+        self.routing_from = None
+        self._world = getattr(cfg, "tp_world", 1)
+        # expert-parallel exchange: "none" = every rank holds all tokens, partial outputs are summed like any row-parallel
+        # output; "a2a" = token dispatch + combine as all-to-all collectives (DFLASH_MOE_EXCHANGE)
+        if moe_exchange is None:
+            moe_exchange = os.environ.get("DFLASH_MOE_EXCHANGE", "none")
+        if moe_exchange not in ("none", "a2a"):
+            raise ValueError("moe_exchange must be 'none' or 'a2a'")
+        self.moe_exchange = moe_exchange if (self.moe is not None and self._world > 1) else "none"
+        if self.moe_exchange == "a2a":
+            if T % self._world != 0:
+                raise ValueError("the all-to-all expert exchange needs the block to split evenly over the ranks")
+            self._a2a_send = z(T, H)
+            self._a2a_recv = z(T, H)
         # DFLASH_GDN_FUSED=1: one launch per GatedDeltaNet layer between its projections instead of three (fewer launches,
         # but measured slower inside a step: its long blocks delay the next matmul's start)
         self.gdn_fused = (os.environ.get("DFLASH_GDN_FUSED", "0") == "1" and bool(self.gdn_layers) and
@@ -375,6 +392,10 @@ class HybridVerifyModel:
 
     def _reduce_add_rmsnorm(self, delta, w):
         """h += sum over ranks of a row-parallel output; x = rmsnorm(h) * w."""
+        if delta is not None and self._delta_is_full:       # already summed over the ranks (expert all-to-all combine)
+            self._delta_is_full = False
+            self._add_rmsnorm(delta, w)
+            return
         if delta is not None and self.peer is not None:
             self.launches_per_step += 1
             self.peer.reduce_add_rmsnorm(delta, self.h, w, self.x, self.cfg.eps, _lib.BF16)
@@ -382,6 +403,32 @@ class HybridVerifyModel:
         if delta is not None:
             self._reduce(delta)
         self._add_rmsnorm(delta, w)
+
+    def _moe_all_to_all(self, i, L):
+        """The expert block with token dispatch and combine as all-to-all exchanges (the classic expert-parallel
+        pattern): every rank OWNS block / world tokens; it sends their activations to the ranks that hold experts
+        (dispatch), every rank applies its experts to the rows it received, sends each partial output row back to the
+        token's owner (combine), the owner sums the world partial rows in rank order, and an all-gather hands every rank
+        the full block again (the next layer's attention / GatedDeltaNet is tensor-parallel over replicated tokens).
+        With 16 tokens choosing 8 of 256 experts nearly every token reaches every rank, so the exchanges are dense
+        fixed-size ones ([block / world, hidden] per rank pair): three collectives per layer where the variant without
+        dispatch (every rank already holds all tokens; partial outputs summed by the peer-memory reduce) needs one."""
+        import torch.distributed as dist
+        T, H, world = self._T, self.cfg.hidden, self._world
+        To = T // world
+        rank = dist.get_rank()
+        own = self.x[rank * To:(rank + 1) * To]
+        self._a2a_send[: world * To].view(world, To, H).copy_(own.unsqueeze(0).expand(world, To, H))
+        dist.all_to_all_single(self._a2a_recv[: world * To], self._a2a_send[: world * To])      # dispatch
+        self.lib.dflash_pdl_plain_next(1)
+        x_all = self._a2a_recv[: world * To]                        # rows in rank order = token order
+        self.moe(x_all, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
+        dist.all_to_all_single(self._a2a_recv[: world * To], self.delta[: world * To])          # combine
+        summed = self._a2a_recv[: world * To].view(world, To, H).float().sum(dim=0).to(torch.bfloat16)
+        dist.all_gather_into_tensor(self.delta[: world * To], summed)
+        self.lib.dflash_pdl_plain_next(1)
+        self._delta_is_full = True
+        self.launches_per_step += 3
 
     def _add_rmsnorm(self, delta, w):
         st = self.lib.dflash_add_rmsnorm(self.h.data_ptr(), _lib.ptr(delta), w.data_ptr(), self.h.data_ptr(),
@@ -540,8 +587,14 @@ class HybridVerifyModel:
             self._reduce_add_rmsnorm(self.delta, L["post_norm"])
             if self.moe is not None:
                 # router -> top-k -> gate|up of the active experts -> weighted SwiGLU -> down summed over the experts
-                self._qmm(self.x, L["router"], self.router_logits[i])
-                self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
+                if self.routing_from is not None:
+                    self.router_logits[i].copy_(self.routing_from[i])
+                else:
+                    self._qmm(self.x, L["router"], self.router_logits[i])
+                if self.moe_exchange == "a2a" and T % self._world == 0:     # (a short block that does not split: no dispatch)
+                    self._moe_all_to_all(i, L)
+                else:
+                    self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
                 self.launches_per_step += self.moe.launches
                 if self._moe_counts is not None:
                     self._moe_counts.append(self.moe.n_active.clone())

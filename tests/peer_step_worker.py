@@ -1,5 +1,8 @@
-"""Worker of tests/test_peer_reduce_gpu.py::test_two_gpus_fused_step_matches_nccl_step (one process per GPU, launched
-with torchrun): a small tensor-parallel verify step with the fused peer reduction against the same step with NCCL."""
+"""Worker of tests/test_peer_reduce_gpu.py (one process per GPU, launched with torchrun).
+
+No argument: a small tensor-parallel verify step with the fused peer reduction against the same step with NCCL.
+Argument ``moe``: a small expert-parallel step with the dispatch + combine all-to-all exchange against the same step
+without dispatch (partial expert outputs summed by an all-reduce)."""
 import os
 import sys
 
@@ -8,6 +11,51 @@ import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+
+
+def moe_main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    from dflash_mlx_b200 import _lib, parallel
+    from dflash_mlx_b200.verify_step import HybridConfig, HybridVerifyModel, init_weights, weights_to
+    full = HybridConfig(layers=4, hidden=1024, intermediate=512, q_heads=4, kv_heads=2, head_dim=128, rope_dims=64,
+                        gdn_k_heads=4, gdn_v_heads=8, vocab=4096, max_context=256, moe_experts=16, moe_top_k=2,
+                        moe_inter=512)
+    W = weights_to(init_weights(full, 0, "cpu"), "cpu")
+    cfg, Wl = parallel.shard_weights(full, W, rank, world)
+    Wr = weights_to(Wl, "cuda")
+    ar, ag = parallel.make_collectives(world)
+    ids = torch.arange(16, dtype=torch.int32, device="cuda") * 11 % full.vocab
+    out = {}
+    for mode in ("none", "a2a"):
+        m = HybridVerifyModel(cfg, Wr, "cuda", all_reduce=ar, all_gather=ag, moe_exchange=mode)
+        assert m.moe_exchange == mode
+        m.prefill_synthetic(64, seed=3)
+        m.arm_rollback()
+        m.verify(ids)
+        torch.cuda.synchronize()
+        eager_tokens, launches = m.tokens.clone(), m.launches_per_step
+        m._armed = True
+        m.capture()
+        m.verify_captured(ids)
+        torch.cuda.synchronize()
+        assert torch.equal(m.tokens, eager_tokens), mode
+        out[mode] = (m.tokens.clone(), m.h.clone().float(), launches)
+        dist.barrier()
+    rel = float((out["none"][1] - out["a2a"][1]).abs().max() / out["none"][1].abs().max())
+    same = float((out["none"][0] == out["a2a"][0]).float().mean())
+    err = _lib.lib().dflash_device_error(torch.cuda.current_device())
+    # the two differ in where the partial expert outputs are rounded to bf16 (NCCL sums bf16; the combine sums fp32)
+    ok = rel <= 3e-2 and same >= 0.8 and err == 0 and out["a2a"][2] > out["none"][2]
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"rel={rel:.4g} same_tokens={same:.3f} device_error={err} launches={out['none'][2]}/{out['a2a'][2]}")
+        print("MOE_EXCHANGE_OK" if int(flag) == 1 else "MOE_EXCHANGE_FAILED")
+    sys.stdout.flush()
+    dist.barrier()
+    os._exit(0 if int(flag) == 1 else 1)
 
 
 def main():
@@ -57,4 +105,4 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    moe_main() if sys.argv[1:] == ["moe"] else main()

@@ -133,3 +133,13 @@ def test_two_gpus_fused_step_matches_nccl_step():
     res = subprocess.run(cmd, cwd=ROOT, env=env2, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "PEER_STEP_OK" in res.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_expert_all_to_all_matches_step_without_dispatch():
+    env2 = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29617", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29617", os.path.join(ROOT, "tests", "peer_step_worker.py"), "moe"]
+    res = subprocess.run(cmd, cwd=ROOT, env=env2, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "MOE_EXCHANGE_OK" in res.stdout
