@@ -71,6 +71,7 @@ struct GdnArgs {
   const void* state_in; void* state_out; void* y; float* tape; const float* tape_in;
   const int* steps_dev;
   int B, T, steps, Hk, Hv, Dk, Dv, g_is_vector;
+  int vec_ok;  // q and k start on 16-byte boundaries: their rows are staged with 16-byte loads
 };
 
 // RECORD = true : forward with tape.  RECORD = false : replay of `steps` tape entries.
@@ -78,6 +79,10 @@ template <typename IT, typename ST, int NPT, bool RECORD>
 __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
   constexpr int Dk = NPT * 32;
   constexpr int kStepChunk = (NPT == 8) ? 8 : 16;  // keeps the static shared memory under 48 KB
+  constexpr int kThreads = kWarps * 32;
+  constexpr int kElemPerVec = 16 / (int)sizeof(IT), kVecPerRow = Dk / kElemPerVec;   // 16-byte vectors of a q / k row
+  constexpr int kVecPerThread = (kStepChunk * kVecPerRow + kThreads - 1) / kThreads;
+  constexpr int kValPerThread = (kStepChunk * kRowsPerCta + kThreads - 1) / kThreads;
   pdl_wait();
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,26 +117,79 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
   for (int t0 = 0; t0 < steps; t0 += kStepChunk) {
     const int nt = min(kStepChunk, steps - t0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * Dk; i += kWarps * 32) {
-      const int t = i / Dk, d = i % Dk;
-      const size_t kq = (((size_t)b * a.T + t0 + t) * a.Hk + hk) * Dk + d;
-      sk[t][d] = ldf<IT>(kg + kq);
-      if (RECORD) sq[t][d] = ldf<IT>(qg + kq);
-      if (a.g_is_vector) sgv[t][d] = a.g[(((size_t)b * a.T + t0 + t) * a.Hv + hv) * Dk + d];
+    // Every global load of the chunk is issued before the first loaded value is used, so the chunk costs one memory
+    // latency (a load-convert-store loop pays one per iteration: a warp issues in order and stalls at the convert).
+    uint4 kvec[kVecPerThread], qvec[kVecPerThread];
+    float vreg[kValPerThread];
+    float g_r = 1.f, b_r = 0.f;
+    int m_r = 1;
+    if (a.vec_ok) {
+#pragma unroll
+      for (int u = 0; u < kVecPerThread; ++u) {
+        const int i = u * kThreads + (int)threadIdx.x;
+        if (i < nt * kVecPerRow) {
+          const int t = i / kVecPerRow, c = i % kVecPerRow;
+          const size_t kq = (((size_t)b * a.T + t0 + t) * a.Hk + hk) * Dk + (size_t)c * kElemPerVec;
+          kvec[u] = *(const uint4*)(kg + kq);
+          if (RECORD) qvec[u] = *(const uint4*)(qg + kq);
+        }
+      }
     }
-    for (int i = threadIdx.x; i < nt * kRowsPerCta; i += kWarps * 32) {
+#pragma unroll
+    for (int u = 0; u < kValPerThread; ++u) {
+      const int i = u * kThreads + (int)threadIdx.x;
       const int t = i / kRowsPerCta, r = i % kRowsPerCta;
       const int row = blockIdx.x * kRowsPerCta + r;
-      const size_t idx = (((size_t)b * a.T + t0 + t) * a.Hv + hv) * a.Dv + row;
-      float val = 0.f;
-      if (row < a.Dv) val = RECORD ? ldf<IT>(vg + idx) : a.tape_in[idx];
-      sv[t][r] = val;
+      vreg[u] = 0.f;
+      if (t < nt && row < a.Dv) {
+        const size_t idx = (((size_t)b * a.T + t0 + t) * a.Hv + hv) * a.Dv + row;
+        vreg[u] = RECORD ? ldf<IT>(vg + idx) : a.tape_in[idx];
+      }
     }
     if (threadIdx.x < nt) {
       const size_t idx = ((size_t)b * a.T + t0 + threadIdx.x) * a.Hv + hv;
-      sg[threadIdx.x] = a.g_is_vector ? 1.f : a.g[idx];
-      sb[threadIdx.x] = RECORD ? a.beta[idx] : 0.f;
-      sm[threadIdx.x] = a.mask ? (int)a.mask[(size_t)b * a.T + t0 + threadIdx.x] : 1;
+      if (!a.g_is_vector) g_r = a.g[idx];
+      if (RECORD) b_r = a.beta[idx];
+      if (a.mask) m_r = (int)a.mask[(size_t)b * a.T + t0 + threadIdx.x];
+    }
+    if (a.vec_ok) {
+#pragma unroll
+      for (int u = 0; u < kVecPerThread; ++u) {
+        const int i = u * kThreads + (int)threadIdx.x;
+        if (i < nt * kVecPerRow) {
+          const int t = i / kVecPerRow, c = i % kVecPerRow;
+          const IT* ke = (const IT*)&kvec[u];
+          const IT* qe = (const IT*)&qvec[u];
+#pragma unroll
+          for (int j = 0; j < kElemPerVec; ++j) {
+            sk[t][c * kElemPerVec + j] = ldf<IT>(ke + j);
+            if (RECORD) sq[t][c * kElemPerVec + j] = ldf<IT>(qe + j);
+          }
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * Dk; i += kThreads) {
+        const int t = i / Dk, d = i % Dk;
+        const size_t kq = (((size_t)b * a.T + t0 + t) * a.Hk + hk) * Dk + d;
+        sk[t][d] = ldf<IT>(kg + kq);
+        if (RECORD) sq[t][d] = ldf<IT>(qg + kq);
+      }
+    }
+    if (a.g_is_vector) {
+      for (int i = threadIdx.x; i < nt * Dk; i += kThreads) {
+        const int t = i / Dk, d = i % Dk;
+        sgv[t][d] = a.g[(((size_t)b * a.T + t0 + t) * a.Hv + hv) * Dk + d];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kValPerThread; ++u) {
+      const int i = u * kThreads + (int)threadIdx.x;
+      if (i / kRowsPerCta < nt) sv[i / kRowsPerCta][i % kRowsPerCta] = vreg[u];
+    }
+    if (threadIdx.x < nt) {
+      sg[threadIdx.x] = g_r;
+      sb[threadIdx.x] = b_r;
+      sm[threadIdx.x] = m_r;
     }
     __syncthreads();
 
@@ -473,6 +531,143 @@ bool get_replay_map(const void* ptr, int rows_bt, int heads, int inner, int T, i
   return true;
 }
 
+// ---- tape record, the common case (scalar gate, no mask, fp32 state, Dk = 128, bf16 inputs, T <= 16) -------------------
+// The recurrence is a chain of 16 dependent token steps, so the kernel is bound by the latency and the instruction count
+// of one step, not by memory.  Against the general kernel above: (1) a state row is spread over 8 lanes (16 elements
+// each) instead of 32, so a row reduction is 3 shuffle levels instead of 5 and a warp advances 4 rows with one
+// instruction stream; (2) y_t = S_t q_t is computed as S' q_t + delta_t (k_t . q_t) with S' the decayed state BEFORE the
+// update, so both row reductions of a step (S' k_t and S' q_t) run as one interleaved shuffle chain instead of two in
+// sequence (k_t . q_t is one scalar per token, computed while the step inputs are staged); (3) packed fp32 pair
+// arithmetic.  The state itself goes through the same two roundings per step as everywhere else (S *= g ; S += k delta),
+// so a replay of the tape still reproduces it bit for bit.  Lane l = 8 * (row within the warp) + c holds the 16-byte
+// chunks c, c + 8, c + 16, c + 24 of its row: global and shared accesses of 8 neighbouring lanes are contiguous.
+constexpr int kRecT = 16, kRecRows = 16;
+__global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ __align__(16) float sk[kRecT][128];
+  __shared__ __align__(16) float sq[kRecT][128];
+  __shared__ float sv[kRecT][kRecRows];
+  __shared__ float sg[kRecT], sb[kRecT], skq[kRecT];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rsub = lane >> 3, cg = lane & 7;
+  const int bh = blockIdx.y, b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
+  const int row = blockIdx.x * kRecRows + warp * 4 + rsub;
+  const bool row_ok = row < a.Dv;
+  const int T = a.T;
+  const __nv_bfloat16* qg = (const __nv_bfloat16*)a.q;
+  const __nv_bfloat16* kg = (const __nv_bfloat16*)a.k;
+  const __nv_bfloat16* vg = (const __nv_bfloat16*)a.v;
+
+  // every global load is issued before the first use
+  float4 s4[4];
+  const float* sin = (const float*)a.state_in + ((size_t)bh * a.Dv + (row_ok ? row : 0)) * 128;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s4[i] = row_ok ? *(const float4*)(sin + 4 * (cg + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  uint4 kvec[2], qvec[2];
+  float vreg[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int i = u * 128 + tid, t = i >> 4, c = i & 15;        // 16 vectors of 8 elements per token row
+    kvec[u] = make_uint4(0u, 0u, 0u, 0u);
+    qvec[u] = make_uint4(0u, 0u, 0u, 0u);
+    vreg[u] = 0.f;
+    if (t < T) {
+      const size_t kq = (((size_t)b * T + t) * a.Hk + hk) * 128 + (size_t)c * 8;
+      kvec[u] = *(const uint4*)(kg + kq);
+      qvec[u] = *(const uint4*)(qg + kq);
+      const int vrow = blockIdx.x * kRecRows + c;                // c doubles as the row of the block for the v tile
+      if (vrow < a.Dv) vreg[u] = __bfloat162float(vg[(((size_t)b * T + t) * a.Hv + hv) * a.Dv + vrow]);
+    }
+  }
+  float g_r = 1.f, b_r = 0.f;
+  if (tid < T) {
+    const size_t idx = ((size_t)b * T + tid) * a.Hv + hv;
+    g_r = a.g[idx];
+    b_r = a.beta[idx];
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int i = u * 128 + tid, t = i >> 4, c = i & 15;
+    const __nv_bfloat16* ke = (const __nv_bfloat16*)&kvec[u];
+    const __nv_bfloat16* qe = (const __nv_bfloat16*)&qvec[u];
+    float kf[8], qf[8], dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      kf[j] = __bfloat162float(ke[j]);
+      qf[j] = __bfloat162float(qe[j]);
+      dot = fmaf(kf[j], qf[j], dot);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);   // the 16 lanes of one token row
+    if (t < T) {
+      *(float4*)&sk[t][c * 8] = make_float4(kf[0], kf[1], kf[2], kf[3]);
+      *(float4*)&sk[t][c * 8 + 4] = make_float4(kf[4], kf[5], kf[6], kf[7]);
+      *(float4*)&sq[t][c * 8] = make_float4(qf[0], qf[1], qf[2], qf[3]);
+      *(float4*)&sq[t][c * 8 + 4] = make_float4(qf[4], qf[5], qf[6], qf[7]);
+      sv[t][c] = vreg[u];
+      if (c == 0) skq[t] = dot;
+    }
+  }
+  if (tid < T) { sg[tid] = g_r; sb[tid] = b_r; }
+  __syncthreads();
+
+  unsigned long long S2[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { S2[2 * i] = pack2(s4[i].x, s4[i].y); S2[2 * i + 1] = pack2(s4[i].z, s4[i].w); }
+  __nv_bfloat16* yg = (__nv_bfloat16*)a.y;
+  for (int t = 0; t < T; ++t) {
+    unsigned long long k2[8], q2[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 kk = *(const float4*)&sk[t][4 * (cg + 8 * i)];
+      const float4 qq = *(const float4*)&sq[t][4 * (cg + 8 * i)];
+      k2[2 * i] = pack2(kk.x, kk.y); k2[2 * i + 1] = pack2(kk.z, kk.w);
+      q2[2 * i] = pack2(qq.x, qq.y); q2[2 * i + 1] = pack2(qq.z, qq.w);
+    }
+    const float g = sg[t], beta = sb[t], vv = sv[t][warp * 4 + rsub], kq = skq[t];
+    const unsigned long long g2 = pack2(g, g);
+    unsigned long long ak0 = 0ull, ak1 = 0ull, aq0 = 0ull, aq1 = 0ull;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      S2[2 * i] = mul2(S2[2 * i], g2);
+      S2[2 * i + 1] = mul2(S2[2 * i + 1], g2);
+      ak0 = fma2(S2[2 * i], k2[2 * i], ak0);
+      ak1 = fma2(S2[2 * i + 1], k2[2 * i + 1], ak1);
+      aq0 = fma2(S2[2 * i], q2[2 * i], aq0);
+      aq1 = fma2(S2[2 * i + 1], q2[2 * i + 1], aq1);
+    }
+    float a0, a1, a2, a3;
+    unpack2(ak0, a0, a1); unpack2(ak1, a2, a3);
+    float pk = (a0 + a1) + (a2 + a3);
+    unpack2(aq0, a0, a1); unpack2(aq1, a2, a3);
+    float pq = (a0 + a1) + (a2 + a3);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      pk += __shfl_xor_sync(0xffffffffu, pk, o);
+      pq += __shfl_xor_sync(0xffffffffu, pq, o);
+    }
+    const float dl = (vv - pk) * beta;
+    const unsigned long long d2 = pack2(dl, dl);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) S2[i] = fma2(k2[i], d2, S2[i]);
+    if (cg == 0 && row_ok) {
+      const size_t idx = (((size_t)b * T + t) * a.Hv + hv) * a.Dv + row;
+      yg[idx] = __float2bfloat16_rn(fmaf(dl, kq, pq));
+      a.tape[idx] = dl;
+    }
+  }
+  if (row_ok) {
+    float* sout = (float*)a.state_out + ((size_t)bh * a.Dv + row) * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 o;
+      unpack2(S2[2 * i], o.x, o.y);
+      unpack2(S2[2 * i + 1], o.z, o.w);
+      *(float4*)(sout + 4 * (cg + 8 * i)) = o;
+    }
+  }
+}
+
 template <typename IT, typename ST, bool RECORD>
 int launch_npt(const GdnArgs& a, cudaStream_t st) {
   dim3 grid((a.Dv + kRowsPerCta - 1) / kRowsPerCta, a.B * a.Hv);
@@ -530,14 +725,28 @@ static int g_replay_stream = 1;
  * 2 = the plain streaming kernel. */
 extern "C" void dflash_tape_replay_set_stream_kernel(int mode) { g_replay_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode; }
 
+static int g_record_fast = 1;
+/* Testing knob: 0 = always the general record kernel, 1 (default) = the low-latency kernel where it applies (scalar
+ * gate, no mask, Dk = 128, bf16 inputs, fp32 state, at most 16 tokens). */
+extern "C" void dflash_gdn_forward_set_kernel(int mode) { g_record_fast = mode != 0; }
+
 extern "C" int dflash_gdn_forward_tape(const void* q, const void* k, const void* v, const float* g, const float* beta,
                                        const uint8_t* mask, const void* state_in, void* state_out, void* y,
                                        float* tape, int B, int T, int Hk, int Hv, int Dk, int Dv, int g_is_vector,
                                        int in_dtype, int state_dtype, void* stream) {
   if (!q || !k || !v || !g || !beta || !state_in || !state_out || !y || !tape)
     return fail(DFLASH_ERR_BAD_ARG, "gdn_forward_tape: null operand");
-  GdnArgs a{q, k, v, g, beta, mask, state_in, state_out, y, tape, nullptr, nullptr, B, T, T, Hk, Hv, Dk, Dv, g_is_vector};
+  GdnArgs a{q, k, v, g, beta, mask, state_in, state_out, y, tape, nullptr, nullptr, B, T, T, Hk, Hv, Dk, Dv, g_is_vector,
+            (((uintptr_t)q | (uintptr_t)k) & 15) == 0};
   if (int rc = check_common(a)) return rc;
+  if (g_record_fast && !g_is_vector && mask == nullptr && Dk == 128 && in_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 &&
+      T >= 1 && T <= kRecT && a.vec_ok && ((uintptr_t)v & 1) == 0) {
+    cudaError_t e = launch_kernel(gdn_record_fast_kernel, dim3((Dv + kRecRows - 1) / kRecRows, B * Hv), dim3(128), 0,
+                                  (cudaStream_t)stream, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "gdn_forward_tape launch: %s", cudaGetErrorString(e));
+    return DFLASH_OK;
+  }
   return launch_in<true>(a, in_dtype, state_dtype, (cudaStream_t)stream);
 }
 
@@ -548,7 +757,7 @@ extern "C" int dflash_tape_replay(const float* tape, const void* k, const float*
   if (!tape || !k || !g || !state_in || !state_out) return fail(DFLASH_ERR_BAD_ARG, "tape_replay: null operand");
   if (steps < 0 || steps > T) return fail(DFLASH_ERR_BAD_SHAPE, "tape_replay: steps=%d outside 0..T=%d", steps, T);
   GdnArgs a{nullptr, k, nullptr, g, nullptr, mask, state_in, state_out, nullptr, nullptr, tape, steps_dev,
-            B, T, steps_dev ? T : steps, Hk, Hv, Dk, Dv, g_is_vector};
+            B, T, steps_dev ? T : steps, Hk, Hv, Dk, Dv, g_is_vector, ((uintptr_t)k & 15) == 0};
   if (int rc = check_common(a)) return rc;
   if (!g_is_vector && mask == nullptr && Dk == 128 && k_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 && g_replay_stream == 1 &&
       T <= kFastT && Dv % 4 == 0 && ((uintptr_t)tape & 15) == 0 && ((uintptr_t)k & 15) == 0) {

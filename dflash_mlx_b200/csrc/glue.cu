@@ -294,18 +294,52 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
   const T* proj = (const T*)a.proj;
   const T* cs = (const T*)a.conv_state;
   const int keep = a.Kc - 1;
+  // All global loads are issued before the first loaded value is used (a warp issues in order, so a load placed after
+  // a dependent instruction or a store waits for the earlier round trip): the block pays one memory latency.
+  constexpr int kMaxTaps = 8;
+  T in[kMaxTaps], wv[kMaxTaps];
+  T cb = fromf<T>(0.f), carry = fromf<T>(0.f);
+  const bool has_carry = live && t < keep;       // this block also writes row t of the new conv window
+  float gate_a = 0.f, gate_b = 0.f, dtb = 0.f, alog = 0.f;
+  const bool gates = is_v && d == 0;             // one thread per value head also produces the head's gate and beta
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) {
+      if (j < a.Kc) {
+        const int r = t + j;  // row of [conv_state ; qkv]
+        in[j] = r < keep ? cs[(size_t)r * conv_dim + c] : proj[(size_t)(r - keep) * a.ld + c];
+        wv[j] = ((const T*)a.conv_w)[(size_t)c * a.Kc + j];
+      }
+    }
+    if (a.conv_b) cb = ((const T*)a.conv_b)[c];
+    if (has_carry) {
+      const int src = a.T + t;
+      carry = src < keep ? cs[(size_t)src * conv_dim + c] : proj[(size_t)(src - keep) * a.ld + c];
+    }
+  }
+  if (gates) {
+    const int hv = hb - 2 * a.Hk;
+    gate_a = tof<T>(proj[(size_t)t * a.ld + a.a_off + hv]);
+    gate_b = tof<T>(proj[(size_t)t * a.ld + a.b_off + hv]);
+    dtb = a.dt_bias[hv];
+    alog = a.A_log[hv];
+  }
   float val = 0.f;
   if (live) {
-    float acc = a.conv_b ? tof<T>(((const T*)a.conv_b)[c]) : 0.f;
-    for (int j = 0; j < a.Kc; ++j) {
-      const int r = t + j;  // row of [conv_state ; qkv]
-      const float in = r < keep ? tof<T>(cs[(size_t)r * conv_dim + c]) : tof<T>(proj[(size_t)(r - keep) * a.ld + c]);
-      acc = fmaf(tof<T>(((const T*)a.conv_w)[(size_t)c * a.Kc + j]), in, acc);
+    float acc = tof<T>(cb);
+    T last = in[0];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) {
+      if (j < a.Kc) {
+        acc = fmaf(tof<T>(wv[j]), tof<T>(in[j]), acc);
+        last = in[j];
+      }
     }
     val = tof<T>(fromf<T>(acc));
     val = tof<T>(fromf<T>(silu(val)));
-    ((T*)a.qkv_tape)[(size_t)t * conv_dim + c] = proj[(size_t)t * a.ld + c];
-    for (int r = t; r < keep; r += a.T) {  // new conv window = rows T .. T+keep-1 of the concatenation
+    ((T*)a.qkv_tape)[(size_t)t * conv_dim + c] = last;      // the last tap is this token's own qkv value
+    if (has_carry) ((T*)a.new_conv_state)[(size_t)t * conv_dim + c] = carry;
+    for (int r = t + a.T; r < keep; r += a.T) {  // (a window longer than the block: rows T .. T+keep-1 of the concatenation)
       const int src = a.T + r;
       ((T*)a.new_conv_state)[(size_t)r * conv_dim + c] =
           src < keep ? cs[(size_t)src * conv_dim + c] : proj[(size_t)(src - keep) * a.ld + c];
@@ -313,14 +347,12 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
   }
   if (is_v) {
     if (live) ((T*)a.v)[((size_t)t * a.Hv + (hb - 2 * a.Hk)) * a.Dv + d] = fromf<T>(val);
-    // one v-head block per head also produces that head's gate and beta
-    if (d == 0) {
+    if (gates) {
       const int hv = hb - 2 * a.Hk;
-      const float av = tof<T>(proj[(size_t)t * a.ld + a.a_off + hv]), bv = tof<T>(proj[(size_t)t * a.ld + a.b_off + hv]);
-      const float xs = tof<T>(fromf<T>(av + a.dt_bias[hv]));
+      const float xs = tof<T>(fromf<T>(gate_a + dtb));
       const float sp = xs > 20.f ? xs : log1pf(expf(xs));
-      a.g[(size_t)t * a.Hv + hv] = expf(-expf(a.A_log[hv]) * sp);
-      a.beta[(size_t)t * a.Hv + hv] = tof<T>(fromf<T>(sigmoidf(bv)));
+      a.g[(size_t)t * a.Hv + hv] = expf(-expf(alog) * sp);
+      a.beta[(size_t)t * a.Hv + hv] = tof<T>(fromf<T>(sigmoidf(gate_b)));
     }
     return;
   }
@@ -344,14 +376,39 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const T* __restrict_
   if (rh >= rows_heads) return;
   const int t = rh / Hv, hv = rh % Hv;
   const T* yr = y + (size_t)rh * Dv;
+  const T* zr = proj + (size_t)t * ld + z_off + hv * Dv;
+  T* orow = out + (size_t)t * Hv * Dv + hv * Dv;
+  if (Dv <= 256) {
+    // every load is issued before the first use: one memory latency per row instead of one per 32 channels
+    T yv[8], zv[8], wv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < Dv) { yv[j] = yr[d]; zv[j] = zr[d]; wv[j] = w[d]; }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (lane + 32 * j < Dv) { const float v = tof<T>(yv[j]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)Dv + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < Dv) {
+        const float n = tof<T>(fromf<T>(tof<T>(yv[j]) * inv * tof<T>(wv[j])));
+        orow[d] = fromf<T>(n * silu(tof<T>(zv[j])));
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int d = lane; d < Dv; d += 32) { const float v = tof<T>(yr[d]); ss += v * v; }
   ss = warp_sum(ss);
   const float inv = rsqrtf(ss / (float)Dv + eps);
   for (int d = lane; d < Dv; d += 32) {
     const float n = tof<T>(fromf<T>(tof<T>(yr[d]) * inv * tof<T>(w[d])));
-    const float z = tof<T>(proj[(size_t)t * ld + z_off + hv * Dv + d]);
-    out[(size_t)t * Hv * Dv + hv * Dv + d] = fromf<T>(n * silu(z));
+    orow[d] = fromf<T>(n * silu(tof<T>(zr[d])));
   }
 }
 
@@ -387,6 +444,16 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
     if (!in_cache) return;
     const int hk = h - a.Hq - a.Hk;
     T* dst = (T*)a.vcache + (size_t)hk * a.cache_head_stride + (size_t)pos * a.D;
+    if (a.D <= 256) {   // loads first, then stores: one memory latency for the row
+      T vv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j < a.D) vv[j] = row[a.v_off + hk * a.D + lane + 32 * j];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j < a.D) dst[lane + 32 * j] = vv[j];
+      return;
+    }
     for (int d = lane; d < a.D; d += 32) dst[d] = row[a.v_off + hk * a.D + d];
     return;
   }
@@ -395,11 +462,64 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
   const T* w = (const T*)(is_q ? a.q_norm_w : a.k_norm_w);
   T* dst = is_q ? (T*)a.q + ((size_t)h * a.T + t) * a.D
                 : (T*)a.kcache + (size_t)(h - a.Hq) * a.cache_head_stride + (size_t)pos * a.D;
+  const int half = a.rope_dims / 2;
+  if (a.D <= 256) {
+    // Every load (the row, the norm weights, the rotation partners) is issued before the first use, and the rotation
+    // angles - double-precision pow / sincos, independent of the data - are computed while the loads are in flight.
+    T xv[8], wv[8], xpv[8], wpv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < a.D) {
+        xv[j] = src[d];
+        wv[j] = w[d];
+        if (d < a.rope_dims) {
+          const int pd = d < half ? d + half : d - half;
+          xpv[j] = src[pd];
+          wpv[j] = w[pd];
+        }
+      }
+    }
+    float cs_[8], sn_[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      cs_[j] = 1.f;
+      sn_[j] = 0.f;
+      if (d < a.D && d < a.rope_dims) {
+        const int i = d < half ? d : d - half;
+        const double theta = (double)pos * pow((double)a.rope_base, -2.0 * (double)i / (double)a.rope_dims);
+        double sn, cs;
+        sincos(theta, &sn, &cs);
+        cs_[j] = (float)cs;
+        sn_[j] = (float)sn;
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (lane + 32 * j < a.D) { const float v = tof<T>(xv[j]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)a.D + a.eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < a.D) {
+        const float x = tof<T>(fromf<T>(tof<T>(xv[j]) * inv * tof<T>(wv[j])));
+        float o = x;
+        if (d < a.rope_dims) {
+          const float xp = tof<T>(fromf<T>(tof<T>(xpv[j]) * inv * tof<T>(wpv[j])));
+          o = d < half ? x * cs_[j] - xp * sn_[j] : xp * sn_[j] + x * cs_[j];
+        }
+        if (is_q || in_cache) dst[d] = fromf<T>(o);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int d = lane; d < a.D; d += 32) { const float v = tof<T>(src[d]); ss += v * v; }
   ss = warp_sum(ss);
   const float inv = rsqrtf(ss / (float)a.D + a.eps);
-  const int half = a.rope_dims / 2;
   for (int d = lane; d < a.D; d += 32) {
     const float x = tof<T>(fromf<T>(tof<T>(src[d]) * inv * tof<T>(w[d])));
     float o = x;

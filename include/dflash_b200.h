@@ -169,6 +169,12 @@ DFLASH_API int dflash_tape_replay(const float* tape, const void* k, const float*
  * memory pipeline (T <= 16, Dv % 4 == 0, 16-byte aligned tape and k), 2 = one block per 64 rows, 0 = the general kernel
  * everywhere. */
 DFLASH_API void dflash_tape_replay_set_stream_kernel(int mode);
+/* Testing knob for dflash_gdn_forward_tape: 1 (default) = the low-latency record kernel where it applies (scalar gate, no
+ * mask, Dk = 128, bf16 inputs, fp32 state, T <= 16, 16-byte aligned q and k: a state row over 8 lanes, both row
+ * reductions of a step in one shuffle chain, y_t = S' q_t + delta_t (k_t . q_t)); 0 = the general kernel everywhere.
+ * The two agree to fp32 rounding (another summation order), not bit for bit; either one's tape replays to its own
+ * state bit for bit. */
+DFLASH_API void dflash_gdn_forward_set_kernel(int mode);
 
 /* ---------------------------------------------------------------------------------------------
  * verify_sdpa: exact softmax attention of 16 query rows per head over N keys (split-KV + combine).

@@ -174,3 +174,30 @@ def test_streaming_replay_kernel_bit_equal_to_the_general_one(K, Dv, steps):
     assert torch.equal(fast, general) and torch.equal(fast_dev, general) and torch.equal(plain, general)
     ref = og.tape_replay_ref(tape, c["k"], c["g"], c["state"], steps=steps)
     assert _rel(fast, ref) <= 1e-4
+
+
+@pytest.mark.parametrize("T,Hk,Hv,Dv", [(16, 16, 32, 128), (16, 4, 8, 96), (7, 2, 4, 40), (1, 1, 2, 16), (12, 2, 2, 256)])
+def test_low_latency_record_kernel_against_the_general_one(K, T, Hk, Hv, Dv):
+    """Scalar gate, no mask, Dk = 128, bf16 inputs, fp32 state, <= 16 tokens: the record pass runs a kernel with a state
+    row over 8 lanes and y_t = S' q_t + delta_t (k_t . q_t).  Another summation order than the general kernel: equal to
+    fp32 rounding (1e-5 of the largest value; y, bf16, within one rounding step), the oracle within the usual 1e-4,
+    and a replay of its own tape reproduces its own state bit for bit.  Ragged row counts included."""
+    from dflash_mlx_b200 import _lib
+    lib = _lib.lib()
+    _lib.declare("dflash_gdn_forward_set_kernel", None, [__import__("ctypes").c_int])
+    c = og.make_gdn_case(seed=77 + T + Dv, T=T, Hk=Hk, Hv=Hv, Dk=128, Dv=Dv)
+    d = "cuda"
+    args = [c[n].to(d) for n in ("q", "k", "v", "g", "beta", "state")]
+    y, s, tape = K.gated_delta_kernel_with_tape(*args)
+    try:
+        lib.dflash_gdn_forward_set_kernel(0)
+        yg, sg, tg = K.gated_delta_kernel_with_tape(*args)
+    finally:
+        lib.dflash_gdn_forward_set_kernel(1)
+    torch.cuda.synchronize()
+    assert lib.dflash_device_error(0) == 0
+    assert _rel(tape, tg) <= 1e-5 and _rel(s, sg) <= 1e-5 and _rel(y, yg) <= 8e-3
+    y_ref, s_ref, tape_ref = og.gated_delta_with_tape_ref(c["q"], c["k"], c["v"], c["g"], c["beta"], c["state"])
+    assert _rel(tape, tape_ref) <= 1e-4 and _rel(s, s_ref) <= 1e-4 and _rel(y, y_ref) <= 1e-2
+    full = K.tape_replay_kernel(tape, c["k"].to(d), c["g"].to(d), c["state"].to(d))
+    assert torch.equal(full, s)

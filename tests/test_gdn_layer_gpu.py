@@ -101,9 +101,14 @@ def _run(c, fused):
                                  o["k"].data_ptr(), v.data_ptr(), o["g"].data_ptr(), beta.data_ptr(), o["new_conv"].data_ptr(),
                                  o["qkv"].data_ptr(), T, Hk, Hv, Dk, Dv, Kc, 1e-6, _lib.BF16, st)
         assert rc == 0, lib.dflash_last_error_string()
-        rc = lib.dflash_gdn_forward_tape(q.data_ptr(), o["k"].data_ptr(), v.data_ptr(), o["g"].data_ptr(), beta.data_ptr(), None,
-                                         dev["state"].data_ptr(), o["state"].data_ptr(), y.data_ptr(), o["tape"].data_ptr(), 1, T,
-                                         Hk, Hv, Dk, Dv, 0, _lib.BF16, _lib.F32, st)
+        _lib.declare("dflash_gdn_forward_set_kernel", None, [__import__("ctypes").c_int])
+        lib.dflash_gdn_forward_set_kernel(0)     # the general record kernel: the one-launch layer sums in its order
+        try:
+            rc = lib.dflash_gdn_forward_tape(q.data_ptr(), o["k"].data_ptr(), v.data_ptr(), o["g"].data_ptr(), beta.data_ptr(),
+                                             None, dev["state"].data_ptr(), o["state"].data_ptr(), y.data_ptr(),
+                                             o["tape"].data_ptr(), 1, T, Hk, Hv, Dk, Dv, 0, _lib.BF16, _lib.F32, st)
+        finally:
+            lib.dflash_gdn_forward_set_kernel(1)
         assert rc == 0, lib.dflash_last_error_string()
         rc = lib.dflash_gated_rmsnorm(y.data_ptr(), dev["proj"].data_ptr(), ld, z_off, dev["g_norm"].data_ptr(),
                                       o["out"].data_ptr(), T, Hv, Dv, 1e-6, _lib.BF16, st)
