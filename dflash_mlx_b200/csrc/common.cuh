@@ -40,6 +40,8 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
 void set_roles(int dequant_warps, int issuing_threads);
 void set_k_parts(int k_parts);
 void set_stamps(void* dev);
+void set_next(const void* wq, const void* sc, const void* bi, int K, int N);
+void set_prefetch_next(int on);
 }  // namespace tc
 
 namespace sdpa_tc {
@@ -183,6 +185,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
       : "memory");
+}
+// 2-D tiled TMA prefetch into L2 (no shared-memory destination, no completion): the box of the tensor map at {x, y}.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 // 3-D tiled TMA load (x innermost), completion counted on an mbarrier, with an L2 cache-policy hint.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,

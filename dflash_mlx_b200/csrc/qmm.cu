@@ -906,13 +906,27 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
 extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }
 extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
 extern "C" void dflash_verify_qmm_set_stamps(void* dev_buffer) { tc::set_stamps(dev_buffer); }
+
+extern "C" void dflash_verify_qmm_prefetch_next(const void* w_q, const void* scales, const void* biases, int K, int N) {
+  tc::set_next(w_q, scales, biases, K, N);
+}
+extern "C" void dflash_verify_qmm_set_prefetch_next(int on) { tc::set_prefetch_next(on); }
 extern "C" void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads) {
   tc::set_roles(dequant_warps, issuing_threads);
 }
 
+namespace {
+// An announcement (dflash_verify_qmm_prefetch_next) is good for exactly one call, whichever kernel that call ends up in:
+// a hint left pending could outlive the weights it names.
+struct NextHintScope {
+  ~NextHintScope() { dflash::tc::set_next(nullptr, nullptr, nullptr, 0, 0); }
+};
+}  // namespace
+
 extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,
                                  const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
                                  void* workspace, size_t workspace_bytes, void* stream) {
+  NextHintScope hint_scope;
   if (!x || !w_q || !scales || !biases || !y) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm: null operand");
   if (M < 1 || M > 16) return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm: M=%d outside 1..16", M);
   if (group_size != 32 && group_size != 64 && group_size != 128)
@@ -935,6 +949,7 @@ extern "C" int dflash_verify_qmm_fused(const void* x, const void* w_q, const voi
                                        const void* bias, void* y, int M, int K, int N, int group_size, int dtype,
                                        const dflash_qmm_epilogue* ep, void* workspace, size_t workspace_bytes,
                                        void* stream) {
+  NextHintScope hint_scope;
   if (!x || !w_q || !scales || !biases || !y || !ep) return fail(DFLASH_ERR_BAD_ARG, "verify_qmm_fused: null operand");
   if (!dflash_verify_qmm_fused_supported(M, K, N, group_size, dtype))
     return fail(DFLASH_ERR_BAD_SHAPE, "verify_qmm_fused: needs bf16, group size 64, K %% 512 == 0, M in 1..16 (M=%d K=%d N=%d G=%d)",

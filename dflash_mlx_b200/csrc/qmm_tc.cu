@@ -90,6 +90,12 @@ constexpr float kPow2Out = 0x1p32f;
 struct Plan {
   int M, K, N, NT, C, ctas, maxp;
 };
+// The matmul that follows this one in the stream (dflash_verify_qmm_prefetch_next): its first units per block are pulled
+// into L2 while this kernel drains, so the next kernel's pipeline fills at L2 latency instead of a cold HBM ramp.
+struct NextPlan {
+  int valid, C, NT, ctas;
+};
+constexpr int kPrefetchUnits = 4;  // units per block of the next matmul (one ring's worth)
 
 __device__ __forceinline__ int cta_of(unsigned u, unsigned units, unsigned ctas) {
   return (int)(((u + 1u) * ctas - 1u) / units);
@@ -383,7 +389,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmX,
               const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* y, float4* __restrict__ pieces,
               unsigned* __restrict__ counters, const __grid_constant__ Plan plan,
-              const __grid_constant__ Epi epi, int* __restrict__ err, unsigned long long* __restrict__ stamps) {
+              const __grid_constant__ Epi epi, int* __restrict__ err, unsigned long long* __restrict__ stamps,
+              const __grid_constant__ CUtensorMap nxW, const __grid_constant__ CUtensorMap nxS,
+              const __grid_constant__ CUtensorMap nxB, const __grid_constant__ NextPlan nxt) {
   using R = Roles<NDQ>;
   // Optional time stamps (dflash_verify_qmm_set_stamps): 16 words per CTA, [0] / [1] = %globaltimer at entry / exit,
   // [2..10] = this SM's clock at entry, set-up done, first activation tile landed, first stage complete, first operand
@@ -486,6 +494,21 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (!mbar_wait_quiet(bar_empty + 8 * p_stage, p_par)) { TC_TRACE(11, p_u - u_begin); atomicCAS(err, 0, 11 | ((int)(p_u - u_begin) << 8)); break; }
         request_weights();
         request_x(p_u);
+      }
+      // Everything this block needs is requested; until it exits (the buffered units, the tail) its share of the memory
+      // system is idle: pull the next matmul's first units into L2 (a hint: nothing waits for it).
+      if (nxt.valid) {
+        const unsigned nunits = (unsigned)nxt.NT * (unsigned)nxt.C;
+        for (int nb = bl; nb < nxt.ctas; nb += (int)gridDim.x) {
+          const unsigned b0 = (unsigned)nb * nunits / (unsigned)nxt.ctas, b1 = (unsigned)(nb + 1) * nunits / (unsigned)nxt.ctas;
+          for (unsigned u = b0; u < b1 && u < b0 + (unsigned)kPrefetchUnits; ++u) {
+            const int nt = (int)(u / (unsigned)nxt.C), kc = (int)(u % (unsigned)nxt.C);
+            tma_prefetch_2d(&nxW, kc * (kBK / 2), nt * kRows);
+            tma_prefetch_2d(&nxW, kc * (kBK / 2) + 128, nt * kRows);
+            tma_prefetch_2d(&nxS, kc * 8, nt * kRows);
+            tma_prefetch_2d(&nxB, kc * 8, nt * kRows);
+          }
+        }
       }
     }
   } else if (warp >= R::kMmaWarp) {
@@ -715,6 +738,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 namespace {
 
 unsigned long long* g_stamps = nullptr;  // dflash_verify_qmm_set_stamps
+struct NextHint {
+  const void* wq; const void* sc; const void* bi; int K, N; bool valid;
+};
+thread_local NextHint t_next = {};   // dflash_verify_qmm_prefetch_next: consumed by this thread's next launch
+bool g_prefetch_next = true;
 int g_ndq = 12;  // dequant warps of the launched instantiation (dflash_verify_qmm_set_tc_roles)
 
 bool make_plan(int M, int K, int N, int device, int max_blocks, Plan* p) {
@@ -800,7 +828,8 @@ bool get_map(const void* ptr, int a, int b, int kind, CUtensorMap* out) {
 template <int NDQ>
 cudaError_t launch_variant(int grid, cudaStream_t st, int device, const CUtensorMap& tw, const CUtensorMap& ts,
                            const CUtensorMap& tb, const CUtensorMap& tx, const void* bias, void* y, float4* pieces,
-                           unsigned* counters, const Plan& plan, const Epi& epi) {
+                           unsigned* counters, const Plan& plan, const Epi& epi, const CUtensorMap& nw,
+                           const CUtensorMap& ns, const CUtensorMap& nb, const NextPlan& nxt) {
   auto kern = qmm_tc_kernel<NDQ>;
   static bool attr_done[64] = {};
   if (!attr_done[device & 63]) {
@@ -815,12 +844,17 @@ cudaError_t launch_variant(int grid, cudaStream_t st, int device, const CUtensor
   }
   return launch_kernel(kern, dim3(grid), dim3(Roles<NDQ>::kThreads), kSmemBytes, st, tw, ts, tb, tx,
                        (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, pieces, counters, plan, epi,
-                       device_error_word(device), g_stamps);
+                       device_error_word(device), g_stamps, nw, ns, nb, nxt);
 }
 
 }  // namespace
 
 void set_k_parts(int) {}  // this kernel cuts K only where a CTA's span ends
+void set_next(const void* wq, const void* sc, const void* bi, int K, int N) {
+  t_next.wq = wq; t_next.sc = sc; t_next.bi = bi; t_next.K = K; t_next.N = N;
+  t_next.valid = wq != nullptr && sc != nullptr && bi != nullptr;
+}
+void set_prefetch_next(int on) { g_prefetch_next = on != 0; }
 void set_stamps(void* dev) { g_stamps = (unsigned long long*)dev; }
 #ifdef DFLASH_TC_TRACE
 }  // namespace tc
@@ -878,8 +912,20 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
   const int grid = plan.ctas;
   cudaError_t e;
-  if (g_ndq == 12) e = launch_variant<12>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi);
-  else e = launch_variant<8>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi);
+  // the matmul announced to follow this one: its tensor maps and block -> unit mapping ride along as a prefetch hint
+  NextPlan nxt = {};
+  CUtensorMap nw = tw, ns = ts, nb = tb;
+  if (t_next.valid) {
+    t_next.valid = false;
+    Plan np;
+    if (g_prefetch_next && t_next.K % kBK == 0 && make_plan(M, t_next.K, t_next.N, device, max_blocks, &np) &&
+        get_map(t_next.wq, t_next.N, t_next.K / 2, 0, &nw) && get_map(t_next.sc, t_next.N, t_next.K / kG, 1, &ns) &&
+        get_map(t_next.bi, t_next.N, t_next.K / kG, 1, &nb)) {
+      nxt.valid = 1; nxt.C = np.C; nxt.NT = np.NT; nxt.ctas = np.ctas;
+    }
+  }
+  if (g_ndq == 12) e = launch_variant<12>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi, nw, ns, nb, nxt);
+  else e = launch_variant<8>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi, nw, ns, nb, nxt);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "qmm_tc launch: %s", cudaGetErrorString(e));
   return DFLASH_OK;

@@ -54,6 +54,9 @@ def _declare():
     d("dflash_verify_sdpa_dev_len", _i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _ll, _ll, _ll, _ll, _f32,
                                            _i32, _i32, _vp, ctypes.c_size_t, _vp])
     d("dflash_verify_qmm_fused_supported", _i32, [_i32] * 5)
+    d("dflash_verify_qmm_prefetch_next", None, [_vp, _vp, _vp, _i32, _i32])
+    d("dflash_verify_qmm_set_prefetch_next", None, [_i32])
+    d("dflash_gdn_forward_set_kernel", None, [_i32])
     d("dflash_verify_qmm_fused", _i32, [_vp] * 6 + [_i32] * 5 + [_c.POINTER(QmmEpilogue), _vp, _c.c_size_t, _vp])
     d("dflash_gdn_layer_supported", _i32, [_i32] * 8)
     d("dflash_gdn_layer", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 14 + [_ll] + [_i32] * 6 + [_f32, _i32, _i32, _vp])
@@ -262,6 +265,9 @@ class HybridVerifyModel:
             self.sdpa_ws = torch.empty(sdpa_need, dtype=torch.uint8, device=dev)
         self.launches_per_step = 0
         import os
+        # DFLASH_QMM_PREFETCH_NEXT=0: no announcement of the following matmul (see _announce_next)
+        self.prefetch_next = os.environ.get("DFLASH_QMM_PREFETCH_NEXT", "1") != "0"
+        self._next_of, self._qmm_seq = {}, []
         self._delta_is_full = False
         # router logits [layers, block, experts + 1] of another pass to route by instead of this pass's own (comparing two
         # formulations of one step: a near-tie in the top-k is a discontinuity, not an arithmetic difference)
@@ -335,8 +341,28 @@ class HybridVerifyModel:
         order = torch.arange(n, device=W["w"].device).view(2, n // 2).t().reshape(-1)
         return {k: W[k].index_select(0, order).contiguous() for k in ("w", "s", "b")}
 
+    def _announce_next(self, W):
+        """Tells the library which matmul follows the one about to be launched (its kernel then pulls the first units of
+        those weights into L2 while it drains).  The order is recorded on the first pass: a step runs the same matmuls
+        in the same order every time, and the last one is followed by the first one of the next step."""
+        if not self.prefetch_next:
+            return
+        nxt = self._next_of.get(id(W["w"]))
+        if nxt is not None:
+            self.lib.dflash_verify_qmm_prefetch_next(nxt["w"].data_ptr(), nxt["s"].data_ptr(), nxt["b"].data_ptr(),
+                                                     nxt["w"].shape[1] * 8, nxt["w"].shape[0])
+        elif self._qmm_seq is not None:
+            self._qmm_seq.append(W)
+
+    def _close_qmm_sequence(self):
+        if self._qmm_seq:
+            seq = self._qmm_seq
+            self._next_of = {id(W["w"]): seq[(i + 1) % len(seq)] for i, W in enumerate(seq)}
+        self._qmm_seq = None
+
     def _qmm_fused(self, x, W, out, ep: QmmEpilogue):
         n, k = W["w"].shape[0], W["w"].shape[1] * 8
+        self._announce_next(W)
         st = self.lib.dflash_verify_qmm_fused(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
                                               out.data_ptr(), self._T, k, n, self.cfg.group_size, _lib.BF16,
                                               _c.byref(ep), self.qmm_ws.data_ptr(), self.qmm_ws.numel(), self._st())
@@ -377,6 +403,7 @@ class HybridVerifyModel:
 
     def _qmm(self, x, W, out):
         n, k = W["w"].shape[0], W["w"].shape[1] * 8
+        self._announce_next(W)
         # `out` is flat storage: the result is written as a contiguous [T, n] array at its start
         st = self.lib.dflash_verify_qmm(x.data_ptr(), W["w"].data_ptr(), W["s"].data_ptr(), W["b"].data_ptr(), None,
                                         out.data_ptr(), self._T, k, n, self.cfg.group_size, _lib.BF16,
@@ -639,6 +666,8 @@ class HybridVerifyModel:
             best = allp[..., 0].max(dim=0).values
             idx = torch.where(allp[..., 0] == best[None], allp[..., 1], torch.full_like(allp[..., 1], 3e8)).min(dim=0).values
             self.tokens[:T].copy_(idx.to(torch.int32))
+        if self._qmm_seq is not None:
+            self._close_qmm_sequence()
         return self.logits.view(-1)[: T * v_local].view(T, v_local)
 
     def capture(self) -> None:

@@ -126,6 +126,14 @@ DFLASH_API void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_th
  * activation tile landed [4], first pipeline stage complete [5], first operand ready for the tensor core [6], last MMA
  * issued [7], last accumulators ready [8], last output written [9], exit [10].  NULL (default) turns it off. */
 DFLASH_API void dflash_verify_qmm_set_stamps(void* dev_buffer);
+/* Announces the verify matmul that follows the NEXT dflash_verify_qmm / dflash_verify_qmm_fused call of this thread in
+ * the stream (its packed weights, scales, biases, K, N; group size 64).  That next call's kernel then pulls the first units
+ * of the announced weights into L2 once its own requests are all issued, so the announced matmul starts from L2 instead
+ * of a cold HBM ramp (~2 us per launch in a verify step, where one matmul follows another).  A hint: consumed by one
+ * call, ignored when either matmul does not run the tensor-memory kernel; results never depend on it.
+ * dflash_verify_qmm_set_prefetch_next(0) turns the hints off (measurements). */
+DFLASH_API void dflash_verify_qmm_prefetch_next(const void* w_q, const void* scales, const void* biases, int K, int N);
+DFLASH_API void dflash_verify_qmm_set_prefetch_next(int on);
 /* Which kernel the calling thread's last dflash_verify_qmm ran: 1 = mma.sync streaming, 2 = tcgen05, 3 = general. */
 DFLASH_API int dflash_verify_qmm_last_impl(void);
 /* Introspection for host-side tests (needs no GPU): writes the streaming kernel's work partition for a
