@@ -25,7 +25,7 @@ def _nvcc() -> str:
 def _stale(obj: Path, src: Path) -> bool:
     if not obj.exists():
         return True
-    newest = max(p.stat().st_mtime for p in [src, CSRC / "common.cuh", PKG.parent / "include" / "dflash_b200.h"])
+    newest = max(p.stat().st_mtime for p in [src, *CSRC.glob("*.cuh"), PKG.parent / "include" / "dflash_b200.h"])
     return obj.stat().st_mtime < newest
 
 

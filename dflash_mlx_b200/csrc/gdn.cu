@@ -13,6 +13,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "gdn_step.cuh"
 
 namespace dflash {
 namespace {
@@ -285,24 +286,10 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_kernel(const GdnArgs a) {
 // slots - with scalar FMAs the arithmetic would take as long as the memory traffic.
 constexpr int kFastRows = 64, kFastWarps = 8, kFastT = 16;
 
-__device__ __forceinline__ unsigned long long pack2(float a, float b) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
+using gdnstep::pack2;
+using gdnstep::unpack2;
+using gdnstep::mul2;
+using gdnstep::fma2;
 
 __global__ void __launch_bounds__(kFastWarps * 32, 4) tape_replay_stream_kernel(const GdnArgs a) {
   constexpr int Dk = 128;
@@ -559,10 +546,8 @@ __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
   const __nv_bfloat16* vg = (const __nv_bfloat16*)a.v;
 
   // every global load is issued before the first use
-  float4 s4[4];
-  const float* sin = (const float*)a.state_in + ((size_t)bh * a.Dv + (row_ok ? row : 0)) * 128;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) s4[i] = row_ok ? *(const float4*)(sin + 4 * (cg + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  unsigned long long S2[8];
+  gdnstep::load_row8((const float*)a.state_in + ((size_t)bh * a.Dv + (row_ok ? row : 0)) * 128, cg, row_ok, S2);
   uint4 kvec[2], qvec[2];
   float vreg[2];
 #pragma unroll
@@ -611,61 +596,17 @@ __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
   if (tid < T) { sg[tid] = g_r; sb[tid] = b_r; }
   __syncthreads();
 
-  unsigned long long S2[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { S2[2 * i] = pack2(s4[i].x, s4[i].y); S2[2 * i + 1] = pack2(s4[i].z, s4[i].w); }
   __nv_bfloat16* yg = (__nv_bfloat16*)a.y;
   for (int t = 0; t < T; ++t) {
-    unsigned long long k2[8], q2[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 kk = *(const float4*)&sk[t][4 * (cg + 8 * i)];
-      const float4 qq = *(const float4*)&sq[t][4 * (cg + 8 * i)];
-      k2[2 * i] = pack2(kk.x, kk.y); k2[2 * i + 1] = pack2(kk.z, kk.w);
-      q2[2 * i] = pack2(qq.x, qq.y); q2[2 * i + 1] = pack2(qq.z, qq.w);
-    }
-    const float g = sg[t], beta = sb[t], vv = sv[t][warp * 4 + rsub], kq = skq[t];
-    const unsigned long long g2 = pack2(g, g);
-    unsigned long long ak0 = 0ull, ak1 = 0ull, aq0 = 0ull, aq1 = 0ull;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      S2[2 * i] = mul2(S2[2 * i], g2);
-      S2[2 * i + 1] = mul2(S2[2 * i + 1], g2);
-      ak0 = fma2(S2[2 * i], k2[2 * i], ak0);
-      ak1 = fma2(S2[2 * i + 1], k2[2 * i + 1], ak1);
-      aq0 = fma2(S2[2 * i], q2[2 * i], aq0);
-      aq1 = fma2(S2[2 * i + 1], q2[2 * i + 1], aq1);
-    }
-    float a0, a1, a2, a3;
-    unpack2(ak0, a0, a1); unpack2(ak1, a2, a3);
-    float pk = (a0 + a1) + (a2 + a3);
-    unpack2(aq0, a0, a1); unpack2(aq1, a2, a3);
-    float pq = (a0 + a1) + (a2 + a3);
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-      pk += __shfl_xor_sync(0xffffffffu, pk, o);
-      pq += __shfl_xor_sync(0xffffffffu, pq, o);
-    }
-    const float dl = (vv - pk) * beta;
-    const unsigned long long d2 = pack2(dl, dl);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) S2[i] = fma2(k2[i], d2, S2[i]);
+    float yv;
+    const float dl = gdnstep::step(S2, sk[t], sq[t], cg, sg[t], sb[t], sv[t][warp * 4 + rsub], skq[t], yv);
     if (cg == 0 && row_ok) {
       const size_t idx = (((size_t)b * T + t) * a.Hv + hv) * a.Dv + row;
-      yg[idx] = __float2bfloat16_rn(fmaf(dl, kq, pq));
+      yg[idx] = __float2bfloat16_rn(yv);
       a.tape[idx] = dl;
     }
   }
-  if (row_ok) {
-    float* sout = (float*)a.state_out + ((size_t)bh * a.Dv + row) * 128;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 o;
-      unpack2(S2[2 * i], o.x, o.y);
-      unpack2(S2[2 * i + 1], o.z, o.w);
-      *(float4*)(sout + 4 * (cg + 8 * i)) = o;
-    }
-  }
+  if (row_ok) gdnstep::store_row8((float*)a.state_out + ((size_t)bh * a.Dv + row) * 128, cg, S2);
 }
 
 template <typename IT, typename ST, bool RECORD>

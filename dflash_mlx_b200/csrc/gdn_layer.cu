@@ -2,16 +2,18 @@
 // causal depthwise conv + SiLU over [conv window ; qkv], per-head RMSNorm and scaling of q and k, gate and beta, the
 // gated delta recurrence with tape, the gated RMSNorm of its output (runtime.py:368-445 of dflash-mlx with the kernels of
 // dflash_mlx/kernels.py:29-105), plus the rollback tape entries (recurrent_rollback_cache.py:116-127).
-// The same arithmetic, in the same order, as dflash_gdn_prep -> dflash_gdn_forward_tape -> dflash_gated_rmsnorm; only
-// the last norm's sum of squares is added in another order (16-row partial sums met through distributed shared memory).
+// The same arithmetic as dflash_gdn_prep -> dflash_gdn_forward_tape (its low-latency record kernel, whose step function
+// is shared) -> dflash_gated_rmsnorm: state, tape and the rollback entries come out bit for bit the same; the per-token
+// k . q and the last norm's sum of squares are added in another order (the output differs by fp32 rounding).
 //
 // Grid (Dv / 16, Hv), 128 threads, the Dv / 16 blocks of a head form one thread-block cluster.  A block owns 16 state
-// rows of one value head (a warp 4 rows, a lane 4 of the 128 key channels): it reads them before it waits for the
+// rows of one value head (a warp 4 rows, 8 lanes a row): it reads them before it waits for the
 // previous kernel (nothing of this step writes them), recomputes the head's q and k for the 16 tokens from the
 // projection output (cheap, and L2-resident), runs the 16 steps, and meets the other blocks of its head once, to
 // finish the output norm.  Restrictions: bf16 activations, fp32 state, Dk = 128, Dv a multiple of 16 up to 128,
 // at most 16 tokens, conv kernel up to 8, scalar gate.
 #include "common.cuh"
+#include "gdn_step.cuh"
 
 namespace dflash {
 namespace {
@@ -38,57 +40,113 @@ __device__ __forceinline__ float wsum(float v) {
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(128, 4) gdn_layer_kernel(const GdnLayerArgs a) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+// 16 sums over the warp's 32 lanes in 16 exchanges (every step halves the values a lane carries); the additions pair up
+// exactly as in a butterfly sum of each value.  The even lanes end with the sum of token `token_of_lane(lane)` in v[0].
+__device__ __forceinline__ void halving_sum16(float (&v)[kTok], int lane) {
+#pragma unroll
+  for (int st = 0; st < 4; ++st) {
+    const int keepn = 8 >> st, m = 16 >> st;
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < keepn; ++i) {
+      const float send = up ? v[i] : v[i + keepn], mine = up ? v[i + keepn] : v[i];
+      v[i] = mine + __shfl_xor_sync(0xffffffffu, send, m);
+    }
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+__device__ __forceinline__ int token_of_lane(int lane) {
+  return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+}
+
+__global__ void __launch_bounds__(128, 3) gdn_layer_kernel(const GdnLayerArgs a) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rsub = lane >> 3, cg = lane & 7;
   const int hv = blockIdx.y, rep = a.Hv / a.Hk, hk = hv / rep;
-  const int row_base = blockIdx.x * kRowsCta, row0 = row_base + warp * 4;
+  const int row_base = blockIdx.x * kRowsCta, row = row_base + warp * 4 + rsub;
   const int T = a.T, Kc = a.Kc, keep = Kc - 1, Dv = a.Dv;
+  const bool row_ok = row < Dv;
   const int key_dim = a.Hk * kDk, conv_dim = 2 * key_dim + a.Hv * Dv;
 
-  __shared__ float sq[kTok][kDk], sk[kTok][kDk];
+  __shared__ __align__(16) float sq[kTok][kDk];
+  __shared__ __align__(16) float sk[kTok][kDk];
   __shared__ float sv[kTok][kRowsCta], sy[kTok][kRowsCta];
   __shared__ float sg[kTok], sb[kTok], sinv[kTok];
-  __shared__ float red[2][kTok][4];
+  __shared__ __align__(16) float red[3][kTok][4];
   __shared__ float ssq_part[kTok];
 
   // the committed state is written by no kernel of this step: its rows are requested before the wait
-  float S[4][4];
-  {
-    const float* sin = a.state_in + ((size_t)hv * Dv) * kDk;
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row0 + r < Dv) v = *(const float4*)(sin + (size_t)(row0 + r) * kDk + 4 * lane);
-      S[r][0] = v.x; S[r][1] = v.y; S[r][2] = v.z; S[r][3] = v.w;
-    }
-  }
+  unsigned long long S2[8];
+  gdnstep::load_row8(a.state_in + ((size_t)hv * Dv + (row_ok ? row : 0)) * kDk, cg, row_ok, S2);
   pdl_wait();
   pdl_trigger();
   const __nv_bfloat16* proj = a.proj;
   const __nv_bfloat16* cs = a.conv_state;
   const bool writer = blockIdx.x == 0 && hv % rep == 0;  // writes what the blocks of a key head share
 
-  // ---- q and k of this key head: thread d owns channel d over all tokens (runtime.py:368-397).  Every load of
-  // this phase is issued before the first use, so the block pays one trip to L2, not one per tensor. ----
-  {
-    const int cq = hk * kDk + tid, ck = key_dim + cq;
-    float wq[kMaxKc], wk[kMaxKc], inq[kTok + kMaxKc - 1], ink[kTok + kMaxKc - 1];
+  // ---- every global load of the prologue and of the output phase is issued here, before the first use: the block
+  // pays one trip to L2 (a warp issues in order and stalls at the first instruction that needs a loaded value) ----
+  // q and k of this key head: thread d owns channel d over all tokens (runtime.py:368-397)
+  const int cq = hk * kDk + tid, ck = key_dim + cq;
+  float wq[kMaxKc], wk[kMaxKc], inq[kTok + kMaxKc - 1], ink[kTok + kMaxKc - 1];
+#pragma unroll
+  for (int j = 0; j < kMaxKc; ++j) {
+    wq[j] = j < Kc ? ldb(a.conv_w + (size_t)cq * Kc + j) : 0.f;
+    wk[j] = j < Kc ? ldb(a.conv_w + (size_t)ck * Kc + j) : 0.f;
+  }
+  const float bq = a.conv_b ? ldb(a.conv_b + cq) : 0.f, bk = a.conv_b ? ldb(a.conv_b + ck) : 0.f;
+#pragma unroll
+  for (int r = 0; r < kTok + kMaxKc - 1; ++r) {  // rows of [conv window ; qkv]
+    inq[r] = 0.f;
+    ink[r] = 0.f;
+    if (r < T + keep) {
+      const __nv_bfloat16* src = r < keep ? cs + (size_t)r * conv_dim : proj + (size_t)(r - keep) * a.ld;
+      inq[r] = ldb(src + cq);
+      ink[r] = ldb(src + ck);
+    }
+  }
+  // v rows of this block: entry p = (token, row of the block), two per thread
+  float xv[2][kMaxKc], wv[2][kMaxKc], bvv[2], zpre[2], gwpre[2];
+#pragma unroll
+  for (int pp = 0; pp < 2; ++pp) {
+    const int p = tid + 128 * pp, t = p >> 4, vrow = row_base + (p & 15);
+    const int c = 2 * key_dim + hv * Dv + vrow;
+    const bool on = t < T && vrow < Dv;
+    bvv[pp] = (on && a.conv_b) ? ldb(a.conv_b + c) : 0.f;
+    zpre[pp] = on ? ldb(proj + (size_t)t * a.ld + a.z_off + hv * Dv + vrow) : 0.f;
+    gwpre[pp] = on ? ldb(a.g_norm_w + vrow) : 0.f;
 #pragma unroll
     for (int j = 0; j < kMaxKc; ++j) {
-      wq[j] = j < Kc ? ldb(a.conv_w + (size_t)cq * Kc + j) : 0.f;
-      wk[j] = j < Kc ? ldb(a.conv_w + (size_t)ck * Kc + j) : 0.f;
-    }
-    const float bq = a.conv_b ? ldb(a.conv_b + cq) : 0.f, bk = a.conv_b ? ldb(a.conv_b + ck) : 0.f;
-#pragma unroll
-    for (int r = 0; r < kTok + kMaxKc - 1; ++r) {  // rows of [conv window ; qkv]
-      inq[r] = 0.f;
-      ink[r] = 0.f;
-      if (r < T + keep) {
-        const __nv_bfloat16* src = r < keep ? cs + (size_t)r * conv_dim : proj + (size_t)(r - keep) * a.ld;
-        inq[r] = ldb(src + cq);
-        ink[r] = ldb(src + ck);
+      xv[pp][j] = 0.f;
+      wv[pp][j] = 0.f;
+      if (on && j < Kc) {
+        const int rr = t + j;
+        xv[pp][j] = rr < keep ? ldb(cs + (size_t)rr * conv_dim + c) : ldb(proj + (size_t)(rr - keep) * a.ld + c);
+        wv[pp][j] = ldb(a.conv_w + (size_t)c * Kc + j);
       }
     }
+  }
+  // the new conv window of the block's v channels (rows T .. T+keep-1 of the concatenation): warp 1, one lane per channel
+  float ncv[kMaxKc - 1];
+  const bool nc_lane = warp == 1 && lane < kRowsCta && row_base + lane < Dv;
+  const int nc_c = 2 * key_dim + hv * Dv + row_base + (lane & 15);
+#pragma unroll
+  for (int r = 0; r < kMaxKc - 1; ++r) {
+    ncv[r] = 0.f;
+    if (nc_lane && r < keep) {
+      const int src = T + r;
+      ncv[r] = src < keep ? ldb(cs + (size_t)src * conv_dim + nc_c) : ldb(proj + (size_t)(src - keep) * a.ld + nc_c);
+    }
+  }
+  float gate_a = 0.f, gate_b = 0.f, dtb = 0.f, alog = 0.f;
+  if (tid < T) {
+    gate_a = ldb(proj + (size_t)tid * a.ld + a.a_off + hv);
+    gate_b = ldb(proj + (size_t)tid * a.ld + a.b_off + hv);
+    dtb = a.dt_bias[hv];
+    alog = a.A_log[hv];
+  }
+
+  // ---- conv + SiLU of q and k, their sums of squares ----
+  {
     float vq[kTok], vk[kTok];
 #pragma unroll
     for (int t = 0; t < kTok; ++t) {
@@ -117,82 +175,52 @@ __global__ void __launch_bounds__(128, 4) gdn_layer_kernel(const GdnLayerArgs a)
         }
       }
     }
-    // 2 x 16 sums over the warp's 32 channels in 2 x 16 exchanges (every step halves the values a lane carries); the
-    // additions pair up exactly as in a butterfly sum of each value, so the result is the same bit for bit
-#pragma unroll
-    for (int st = 0; st < 4; ++st) {
-      const int keepn = 8 >> st, m = 16 >> st;
-      const bool up = (lane & m) != 0;
-#pragma unroll
-      for (int i = 0; i < keepn; ++i) {
-        const float sendq = up ? vq[i] : vq[i + keepn], mineq = up ? vq[i + keepn] : vq[i];
-        const float sendk = up ? vk[i] : vk[i + keepn], minek = up ? vk[i + keepn] : vk[i];
-        vq[i] = mineq + __shfl_xor_sync(0xffffffffu, sendq, m);
-        vk[i] = minek + __shfl_xor_sync(0xffffffffu, sendk, m);
-      }
-    }
-    vq[0] += __shfl_xor_sync(0xffffffffu, vq[0], 1);
-    vk[0] += __shfl_xor_sync(0xffffffffu, vk[0], 1);
+    halving_sum16(vq, lane);
+    halving_sum16(vk, lane);
     if ((lane & 1) == 0) {
-      const int t = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-      red[0][t][warp] = vq[0];
-      red[1][t][warp] = vk[0];
+      red[0][token_of_lane(lane)][warp] = vq[0];
+      red[1][token_of_lane(lane)][warp] = vk[0];
     }
   }
-  // ---- v rows of this block, conv window and tape of their channels ----
+  // ---- v rows of this block, their tape entries and conv window ----
 #pragma unroll
   for (int pp = 0; pp < 2; ++pp) {
-    const int p = tid + 128 * pp;
-    const int t = p >> 4, r = p & 15, row = row_base + r;
+    const int p = tid + 128 * pp, t = p >> 4, r = p & 15, vrow = row_base + r;
     float val = 0.f;
-    if (t < T && row < Dv) {
-      const int c = 2 * key_dim + hv * Dv + row;
-      float x[kMaxKc], w[kMaxKc];
-#pragma unroll
-      for (int j = 0; j < kMaxKc; ++j) {
-        x[j] = 0.f;
-        w[j] = 0.f;
-        if (j < Kc) {
-          const int rr = t + j;
-          x[j] = rr < keep ? ldb(cs + (size_t)rr * conv_dim + c) : ldb(proj + (size_t)(rr - keep) * a.ld + c);
-          w[j] = ldb(a.conv_w + (size_t)c * Kc + j);
-        }
-      }
-      float acc = a.conv_b ? ldb(a.conv_b + c) : 0.f;
+    if (t < T && vrow < Dv) {
+      const int c = 2 * key_dim + hv * Dv + vrow;
+      float acc = bvv[pp], last = 0.f;
 #pragma unroll
       for (int j = 0; j < kMaxKc; ++j)
-        if (j < Kc) acc = fmaf(w[j], x[j], acc);
+        if (j < Kc) { acc = fmaf(wv[pp][j], xv[pp][j], acc); last = xv[pp][j]; }
       val = bf(silu_f(bf(acc)));
-      a.qkv_tape[(size_t)t * conv_dim + c] = proj[(size_t)t * a.ld + c];
+      a.qkv_tape[(size_t)t * conv_dim + c] = __float2bfloat16_rn(last);   // the last tap is the token's own value
     }
     sv[t][r] = val;
   }
-  if (warp == 1 && lane < kRowsCta && row_base + lane < Dv) {
-    const int c = 2 * key_dim + hv * Dv + row_base + lane;
-    for (int r = 0; r < keep; ++r) {  // new conv window = rows T .. T+keep-1 of the concatenation
-      const int src = T + r;
-      a.new_conv_state[(size_t)r * conv_dim + c] =
-          src < keep ? cs[(size_t)src * conv_dim + c] : proj[(size_t)(src - keep) * a.ld + c];
-    }
+  if (nc_lane) {
+#pragma unroll
+    for (int r = 0; r < kMaxKc - 1; ++r)
+      if (r < keep) a.new_conv_state[(size_t)r * conv_dim + nc_c] = __float2bfloat16_rn(ncv[r]);
   }
   // ---- gate and beta (runtime.py:399-403) ----
   if (tid < kTok) {
     float g = 1.f, beta = 0.f;
     if (tid < T) {
-      const float av = ldb(proj + (size_t)tid * a.ld + a.a_off + hv), bv = ldb(proj + (size_t)tid * a.ld + a.b_off + hv);
-      const float xs = bf(av + a.dt_bias[hv]);
+      const float xs = bf(gate_a + dtb);
       const float sp = xs > 20.f ? xs : log1pf(expf(xs));
-      g = expf(-expf(a.A_log[hv]) * sp);
-      beta = bf(1.f / (1.f + __expf(-bv)));
+      g = expf(-expf(alog) * sp);
+      beta = bf(1.f / (1.f + __expf(-gate_b)));
       if (blockIdx.x == 0) a.tape_g[(size_t)tid * a.Hv + hv] = g;
     }
     sg[tid] = g;
     sb[tid] = beta;
   }
   __syncthreads();
-  // ---- per-head RMSNorm of q and k, q scaled by 1/Dk and k by 1/sqrt(Dk) ----
+  // ---- per-head RMSNorm of q and k, q scaled by 1/Dk and k by 1/sqrt(Dk); k . q per token for the recurrence ----
   {
     const float isc = rsqrtf((float)kDk);
+    float kq[kTok];
 #pragma unroll
     for (int t = 0; t < kTok; ++t) {
       const float ssq = (red[0][t][0] + red[0][t][2]) + (red[0][t][1] + red[0][t][3]);
@@ -200,76 +228,31 @@ __global__ void __launch_bounds__(128, 4) gdn_layer_kernel(const GdnLayerArgs a)
       const float nq = bf(sq[t][tid] * rsqrtf(ssq / (float)kDk + a.eps));
       const float nk = bf(sk[t][tid] * rsqrtf(ssk / (float)kDk + a.eps));
       const __nv_bfloat16 kb = __float2bfloat16_rn(nk * isc);
-      sq[t][tid] = bf(nq * isc * isc);
-      sk[t][tid] = __bfloat162float(kb);
+      const float qf = bf(nq * isc * isc), kf = __bfloat162float(kb);
+      sq[t][tid] = qf;
+      sk[t][tid] = kf;
+      kq[t] = qf * kf;
       if (writer && t < T) a.tape_k[((size_t)t * a.Hk + hk) * kDk + tid] = kb;
     }
+    halving_sum16(kq, lane);
+    if ((lane & 1) == 0) red[2][token_of_lane(lane)][warp] = kq[0];
   }
   __syncthreads();
-  // what the output phase needs from global memory is fetched now, behind the recurrence
-  float zpre[2], gwpre[2];
-#pragma unroll
-  for (int pp = 0; pp < 2; ++pp) {
-    const int p = tid + 128 * pp, t = p >> 4, row = row_base + (p & 15);
-    zpre[pp] = 0.f;
-    gwpre[pp] = 0.f;
-    if (t < T && row < Dv) {
-      zpre[pp] = ldb(proj + (size_t)t * a.ld + a.z_off + hv * Dv + row);
-      gwpre[pp] = ldb(a.g_norm_w + row);
-    }
-  }
-  // ---- the recurrence (kernels.py:62-99): S *= g ; kv = S k ; delta = (v - kv) beta ; S += delta (x) k ; y = S q ----
+  // ---- the recurrence (kernels.py:62-99), a state row over 8 lanes ----
   for (int t = 0; t < T; ++t) {
-    float kk[4], qq[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { kk[i] = sk[t][4 * lane + i]; qq[i] = sq[t][4 * lane + i]; }
-    const float g = sg[t], beta = sb[t];
-    float kv[4], yy[4], dl[4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float p = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[r][i] *= g;
-        p = fmaf(S[r][i], kk[i], p);
-      }
-      kv[r] = p;
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) kv[r] = wsum(kv[r]);
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      dl[r] = (sv[t][warp * 4 + r] - kv[r]) * beta;
-      float p = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[r][i] = fmaf(kk[i], dl[r], S[r][i]);
-        p = fmaf(S[r][i], qq[i], p);
-      }
-      yy[r] = p;
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) yy[r] = wsum(yy[r]);
-    if (lane < 4) {
-      float yv = yy[0], dv = dl[0];
-#pragma unroll
-      for (int r = 1; r < 4; ++r)
-        if (lane == r) { yv = yy[r]; dv = dl[r]; }
-      const int row = row0 + lane;
+    const float4 kq4 = *(const float4*)red[2][t];
+    float yv;
+    const float dl = gdnstep::step(S2, sk[t], sq[t], cg, sg[t], sb[t], sv[t][warp * 4 + rsub], (kq4.x + kq4.z) + (kq4.y + kq4.w), yv);
+    if (cg == 0) {
       float ys = 0.f;
-      if (row < Dv) {
-        a.tape[((size_t)t * a.Hv + hv) * Dv + row] = dv;
+      if (row_ok) {
+        a.tape[((size_t)t * a.Hv + hv) * Dv + row] = dl;
         ys = bf(yv);  // the recurrence's output is a bf16 array in the reference
       }
-      sy[t][warp * 4 + lane] = ys;
+      sy[t][warp * 4 + rsub] = ys;
     }
   }
-  {
-    float* sout = a.state_out + ((size_t)hv * Dv) * kDk;
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-      if (row0 + r < Dv) *(float4*)(sout + (size_t)(row0 + r) * kDk + 4 * lane) = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
-  }
+  if (row_ok) gdnstep::store_row8(a.state_out + ((size_t)hv * Dv + row) * kDk, cg, S2);
   __syncthreads();
   // ---- gated RMSNorm over the head's Dv outputs (runtime.py:445): 16-row partial sums, one exchange in the cluster ----
   if (tid < kTok) {
@@ -302,10 +285,10 @@ __global__ void __launch_bounds__(128, 4) gdn_layer_kernel(const GdnLayerArgs a)
   __syncthreads();
 #pragma unroll
   for (int pp = 0; pp < 2; ++pp) {
-    const int p = tid + 128 * pp, t = p >> 4, r = p & 15, row = row_base + r;
-    if (t < T && row < Dv) {
+    const int p = tid + 128 * pp, t = p >> 4, r = p & 15, vrow = row_base + r;
+    if (t < T && vrow < Dv) {
       const float n = bf(sy[t][r] * sinv[t] * gwpre[pp]);
-      a.out[(size_t)t * a.out_ld + hv * Dv + row] = __float2bfloat16_rn(n * silu_f(zpre[pp]));
+      a.out[(size_t)t * a.out_ld + hv * Dv + vrow] = __float2bfloat16_rn(n * silu_f(zpre[pp]));
     }
   }
   cluster_wait();  // nobody exits while a neighbour may still read its partial sums
