@@ -487,9 +487,11 @@ class SdpaWorkload:
     metric, unit, higher_is_better, scaling, dtype = "verify_sdpa_latency", "us", False, "strong", "bf16"
     N = 8192
 
-    def __init__(self, rank, world, device):
+    def __init__(self, rank, world, device, kv_len=0):
         import torch
         self.torch, self.device, self.world = torch, device, world
+        if kv_len:
+            self.N = int(kv_len)       # profiling aid (--kv-len): the metric's configuration is N = 8192
         Hk = max(1, 2 // world)
         Hq = 16 // world
         self.Hq, self.Hk, D = Hq, Hk, 256
@@ -535,7 +537,7 @@ class SdpaWorkload:
         us = ms_per_step * 1e3 / self.units_per_step
         ach = self.per_launch_bytes / us / 1e3
         return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                "peak_source": peak_src, "kernel": "sdpa_partials_kernel (+ combine)",
+                "peak_source": peak_src, "kernel": "sdpa_tc_kernel (tcgen05: S / P / O in tensor memory, K / V by TMA) + combine_kernel",
                 "algorithmic_bytes_per_launch": self.per_launch_bytes, "us_per_launch": us}
 
     def cpu_sample(self):
@@ -708,6 +710,7 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense step with fewer layers")
+    ap.add_argument("--kv-len", type=int, default=0, help="profiling aid: KV length of verify_sdpa_cfg3 (default 8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -733,8 +736,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    wl = (WORKLOADS[args.workload](rank, world, device, layers=args.layers) if args.layers and args.workload == "dense_step_cfg4"
-          else WORKLOADS[args.workload](rank, world, device))
+    if args.layers and args.workload == "dense_step_cfg4":
+        wl = WORKLOADS[args.workload](rank, world, device, layers=args.layers)
+    elif args.kv_len and args.workload == "verify_sdpa_cfg3":
+        wl = WORKLOADS[args.workload](rank, world, device, kv_len=args.kv_len)
+    else:
+        wl = WORKLOADS[args.workload](rank, world, device)
 
     # ---- device-resident loop: one CUDA graph = one step ----
     def time_graph(fn, steps, warmup, sample=False):
