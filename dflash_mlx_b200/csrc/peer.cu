@@ -22,7 +22,7 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 uint32_t g_wait_polls = 1u << 22;
-int g_protocol = 0;  // 0: by rank count (entries for <= 2 ranks, flags above), 1: entries, 2: flags
+int g_protocol = 0;  // 0: by rank count (entries for <= 4 ranks, flags above), 1: entries, 2: flags
 // (every rank of a job must use the same protocol)  // polls before a row gives up; with the back-off below a few seconds
 
 struct PeerArgs {
@@ -67,9 +67,10 @@ __device__ __forceinline__ __nv_bfloat16 fromf<__nv_bfloat16>(float v) { return 
 template <>
 __device__ __forceinline__ __half fromf<__half>(float v) { return __float2half_rn(v); }
 
-// Variant for more than two ranks: 16-byte vector pushes, one system-scope fence, one flag per (rank, row) that a single
+// Variant for more than four ranks: 16-byte vector pushes, one system-scope fence, one flag per (rank, row) that a single
 // thread per rank polls.  With 8 ranks the 8-byte entries of the kernel below cost more NVLink packets and polling
-// traffic than they save in latency (measured: TP8 6.97 ms with flags, 8.32 ms with entries; TP2 8.91 vs 8.51 ms).
+// traffic than they save in latency (measured, dense step: 8 ranks 6.97 ms with flags, 8.32 ms with entries; 4 ranks 5.76
+// vs 5.46 ms, 2 ranks 8.91 vs 8.51 ms: the entries win up to 4 ranks).
 template <typename T>
 __global__ void __launch_bounds__(1024) peer_reduce_flags_kernel(const PeerArgs a) {
   pdl_wait();
@@ -345,7 +346,7 @@ extern "C" int dflash_peer_reduce_add_rmsnorm(const void* delta, void* const* in
   if (threads < 32 * ((world + 31) / 32)) threads = 32;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  const bool entries = g_protocol == 1 || (g_protocol == 0 && world <= 2);
+  const bool entries = g_protocol == 1 || (g_protocol == 0 && world <= 4);
   if (dtype == DFLASH_BF16)
     e = entries ? launch_kernel(peer_reduce_add_rmsnorm_kernel<__nv_bfloat16>, dim3(T_rows), dim3(threads), 0, st, a)
                 : launch_kernel(peer_reduce_flags_kernel<__nv_bfloat16>, dim3(T_rows), dim3(threads), 0, st, a);

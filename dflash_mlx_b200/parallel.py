@@ -229,6 +229,9 @@ class PeerReducer:
         _lib.declare("dflash_peer_reduce_add_rmsnorm", i32,
                      [vp, c.POINTER(vp), c.POINTER(vp), i32, i32, vp, vp, vp, vp, i32, i32, c.c_float, i32, vp])
         self._check = _lib.check
+        import os
+        if os.environ.get("DFLASH_PEER_PROTOCOL", "") in ("0", "1", "2"):      # hand-over protocol, see set_protocol
+            self.lib.dflash_peer_set_protocol(int(os.environ["DFLASH_PEER_PROTOCOL"]))
         self.rank, self.world, self.rows, self.hidden = rank, world, rows, hidden
         self.dev = torch.device(device)
         self._own, self._opened = [], []

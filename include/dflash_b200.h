@@ -382,7 +382,7 @@ DFLASH_API int dflash_peer_export(void* dev_ptr, unsigned char* handle64);
 DFLASH_API int dflash_peer_open(const unsigned char* handle64, void** dev_ptr);
 DFLASH_API int dflash_peer_close(void* dev_ptr);
 DFLASH_API void dflash_peer_set_wait_polls(unsigned polls);
-/* Hand-over protocol: 0 (default) = by rank count - 8-byte {data, sequence} entries for world <= 2 (one NVLink latency),
+/* Hand-over protocol: 0 (default) = by rank count - 8-byte {data, sequence} entries for world <= 4 (one NVLink latency),
  * 16-byte pushes + fence + per-row flags above (fewer packets and polls); 1 / 2 force one.  Same value on every rank. */
 DFLASH_API void dflash_peer_set_protocol(int protocol);
 DFLASH_API int dflash_peer_reduce_add_rmsnorm(const void* delta, void* const* inbox_ptrs, void* const* flag_ptrs, int rank,
