@@ -28,10 +28,11 @@ if str(ROOT) not in sys.path:
 
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) per algorithmic byte of the tcgen05 matmul, from an ncu capture of single launches
-# (profiles/qmm_tc_gate_up.md); None = not captured for this build
-QMM_TC_TRAFFIC_RATIO = 1.023
-QMM_TC_TRAFFIC_SOURCE = ("ncu capture of single gate|up launches (dram read 100.5 MB + write 3.4 MB against 101.5 MB algorithmic), "
-                         "scaled by algorithmic bytes; not measured at this launch mix")
+# (summary under profiles/: qmm_tc_kernel, configuration 1); None = not captured for this build
+QMM_TC_TRAFFIC_RATIO = 0.989
+QMM_TC_TRAFFIC_SOURCE = ("ncu capture of two configuration-1 launches (dram read 28.53 MB + write 0 - the 0.4 MB of output stay "
+                         "in L2 - against 28.84 MB algorithmic; an earlier capture of gate|up launches gave 1.023), scaled by "
+                         "algorithmic bytes; not measured at this launch mix")
 
 
 def measured_peaks():
