@@ -73,6 +73,7 @@ struct GdnArgs {
   const int* steps_dev;
   int B, T, steps, Hk, Hv, Dk, Dv, g_is_vector;
   int vec_ok;  // q and k start on 16-byte boundaries: their rows are staged with 16-byte loads
+  int early_state;  // the record kernel may read state_in before it waits for the previous kernel
 };
 
 // RECORD = true : forward with tape.  RECORD = false : replay of `steps` tape entries.
@@ -530,8 +531,6 @@ bool get_replay_map(const void* ptr, int rows_bt, int heads, int inner, int T, i
 // chunks c, c + 8, c + 16, c + 24 of its row: global and shared accesses of 8 neighbouring lanes are contiguous.
 constexpr int kRecT = 16, kRecRows = 16;
 __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
-  pdl_wait();
-  pdl_trigger();
   __shared__ __align__(16) float sk[kRecT][128];
   __shared__ __align__(16) float sq[kRecT][128];
   __shared__ float sv[kRecT][kRecRows];
@@ -545,9 +544,14 @@ __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
   const __nv_bfloat16* kg = (const __nv_bfloat16*)a.k;
   const __nv_bfloat16* vg = (const __nv_bfloat16*)a.v;
 
-  // every global load is issued before the first use
+  // every global load is issued before the first use; when the caller vouches that the kernel launched before this one
+  // does not write the state (dflash_gdn_forward_state_is_settled), its rows are requested before the wait on that kernel
   unsigned long long S2[8];
-  gdnstep::load_row8((const float*)a.state_in + ((size_t)bh * a.Dv + (row_ok ? row : 0)) * 128, cg, row_ok, S2);
+  const float* srow = (const float*)a.state_in + ((size_t)bh * a.Dv + (row_ok ? row : 0)) * 128;
+  if (a.early_state) gdnstep::load_row8(srow, cg, row_ok, S2);
+  pdl_wait();
+  pdl_trigger();
+  if (!a.early_state) gdnstep::load_row8(srow, cg, row_ok, S2);
   uint4 kvec[2], qvec[2];
   float vreg[2];
 #pragma unroll
@@ -666,6 +670,13 @@ static int g_replay_stream = 1;
  * 2 = the plain streaming kernel. */
 extern "C" void dflash_tape_replay_set_stream_kernel(int mode) { g_replay_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode; }
 
+static thread_local int t_state_settled = 0;
+/* One-shot promise for this thread's next dflash_gdn_forward_tape call: the kernel launched before it in the stream does
+ * not write `state_in` (true inside a verify step, where the projection glue runs in between; NOT true when one call's
+ * state_out is the next call's state_in).  The record kernel then requests the state rows before it waits for that
+ * kernel (programmatic dependent launch), hiding their HBM latency. */
+extern "C" void dflash_gdn_forward_state_is_settled(void) { t_state_settled = 1; }
+
 static int g_record_fast = 1;
 /* Testing knob: 0 = always the general record kernel, 1 (default) = the low-latency kernel where it applies (scalar
  * gate, no mask, Dk = 128, bf16 inputs, fp32 state, at most 16 tokens). */
@@ -675,10 +686,12 @@ extern "C" int dflash_gdn_forward_tape(const void* q, const void* k, const void*
                                        const uint8_t* mask, const void* state_in, void* state_out, void* y,
                                        float* tape, int B, int T, int Hk, int Hv, int Dk, int Dv, int g_is_vector,
                                        int in_dtype, int state_dtype, void* stream) {
+  const int settled = t_state_settled;  // good for this call only, whatever becomes of it
+  t_state_settled = 0;
   if (!q || !k || !v || !g || !beta || !state_in || !state_out || !y || !tape)
     return fail(DFLASH_ERR_BAD_ARG, "gdn_forward_tape: null operand");
   GdnArgs a{q, k, v, g, beta, mask, state_in, state_out, y, tape, nullptr, nullptr, B, T, T, Hk, Hv, Dk, Dv, g_is_vector,
-            (((uintptr_t)q | (uintptr_t)k) & 15) == 0};
+            (((uintptr_t)q | (uintptr_t)k) & 15) == 0, settled};
   if (int rc = check_common(a)) return rc;
   if (g_record_fast && !g_is_vector && mask == nullptr && Dk == 128 && in_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 &&
       T >= 1 && T <= kRecT && a.vec_ok && ((uintptr_t)v & 1) == 0) {
@@ -698,7 +711,7 @@ extern "C" int dflash_tape_replay(const float* tape, const void* k, const float*
   if (!tape || !k || !g || !state_in || !state_out) return fail(DFLASH_ERR_BAD_ARG, "tape_replay: null operand");
   if (steps < 0 || steps > T) return fail(DFLASH_ERR_BAD_SHAPE, "tape_replay: steps=%d outside 0..T=%d", steps, T);
   GdnArgs a{nullptr, k, nullptr, g, nullptr, mask, state_in, state_out, nullptr, nullptr, tape, steps_dev,
-            B, T, steps_dev ? T : steps, Hk, Hv, Dk, Dv, g_is_vector, ((uintptr_t)k & 15) == 0};
+            B, T, steps_dev ? T : steps, Hk, Hv, Dk, Dv, g_is_vector, ((uintptr_t)k & 15) == 0, 0};
   if (int rc = check_common(a)) return rc;
   if (!g_is_vector && mask == nullptr && Dk == 128 && k_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 && g_replay_stream == 1 &&
       T <= kFastT && Dv % 4 == 0 && ((uintptr_t)tape & 15) == 0 && ((uintptr_t)k & 15) == 0) {

@@ -282,8 +282,6 @@ struct GdnPrepArgs {
 };
 template <typename T>
 __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
-  pdl_wait();
-  pdl_trigger();
   __shared__ float scratch[32];
   const int t = blockIdx.x, hb = blockIdx.y, d = threadIdx.x;
   const int key_dim = a.Hk * a.Dk, conv_dim = 2 * key_dim + a.Hv * a.Dv;
@@ -302,16 +300,27 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
   const bool has_carry = live && t < keep;       // this block also writes row t of the new conv window
   float gate_a = 0.f, gate_b = 0.f, dtb = 0.f, alog = 0.f;
   const bool gates = is_v && d == 0;             // one thread per value head also produces the head's gate and beta
+  // the layer's constants (written by no kernel, cold in HBM) are requested before the wait on the previous kernel
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+      if (j < a.Kc) wv[j] = ((const T*)a.conv_w)[(size_t)c * a.Kc + j];
+    if (a.conv_b) cb = ((const T*)a.conv_b)[c];
+  }
+  if (gates) {
+    dtb = a.dt_bias[hb - 2 * a.Hk];
+    alog = a.A_log[hb - 2 * a.Hk];
+  }
+  pdl_wait();
+  pdl_trigger();
   if (live) {
 #pragma unroll
     for (int j = 0; j < kMaxTaps; ++j) {
       if (j < a.Kc) {
         const int r = t + j;  // row of [conv_state ; qkv]
         in[j] = r < keep ? cs[(size_t)r * conv_dim + c] : proj[(size_t)(r - keep) * a.ld + c];
-        wv[j] = ((const T*)a.conv_w)[(size_t)c * a.Kc + j];
       }
     }
-    if (a.conv_b) cb = ((const T*)a.conv_b)[c];
     if (has_carry) {
       const int src = a.T + t;
       carry = src < keep ? cs[(size_t)src * conv_dim + c] : proj[(size_t)(src - keep) * a.ld + c];
@@ -321,8 +330,6 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
     const int hv = hb - 2 * a.Hk;
     gate_a = tof<T>(proj[(size_t)t * a.ld + a.a_off + hv]);
     gate_b = tof<T>(proj[(size_t)t * a.ld + a.b_off + hv]);
-    dtb = a.dt_bias[hv];
-    alog = a.A_log[hv];
   }
   float val = 0.f;
   if (live) {
@@ -370,9 +377,15 @@ template <typename T>
 __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ proj,
                                                             long long ld, int z_off, const T* __restrict__ w,
                                                             T* __restrict__ out, int rows_heads, int Hv, int Dv, float eps) {
+  const int rh = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  T wv[8];  // the norm weight (written by no kernel) is requested before the wait on the previous kernel
+  if (Dv <= 256) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (lane + 32 * j < Dv) wv[j] = w[lane + 32 * j];
+  }
   pdl_wait();
   pdl_trigger();
-  const int rh = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (rh >= rows_heads) return;
   const int t = rh / Hv, hv = rh % Hv;
   const T* yr = y + (size_t)rh * Dv;
@@ -380,11 +393,11 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const T* __restrict_
   T* orow = out + (size_t)t * Hv * Dv + hv * Dv;
   if (Dv <= 256) {
     // every load is issued before the first use: one memory latency per row instead of one per 32 channels
-    T yv[8], zv[8], wv[8];
+    T yv[8], zv[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int d = lane + 32 * j;
-      if (d < Dv) { yv[j] = yr[d]; zv[j] = zr[d]; wv[j] = w[d]; }
+      if (d < Dv) { yv[j] = yr[d]; zv[j] = zr[d]; }
     }
     float ss = 0.f;
 #pragma unroll
@@ -428,12 +441,26 @@ struct AttnPrepArgs {
 };
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
-  pdl_wait();
-  pdl_trigger();
   const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int heads = a.Hq + 2 * a.Hk;
-  if (idx >= a.T * heads) return;
   const int t = idx / heads, h = idx % heads;
+  // the norm weights (written by no kernel) are requested before the wait on the previous kernel
+  T wv[8], wpv[8];
+  if (idx < a.T * heads && h < a.Hq + a.Hk && a.D <= 256) {
+    const T* w0 = (const T*)(h < a.Hq ? a.q_norm_w : a.k_norm_w);
+    const int half0 = a.rope_dims / 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = lane + 32 * j;
+      if (d < a.D) {
+        wv[j] = w0[d];
+        if (d < a.rope_dims) wpv[j] = w0[d < half0 ? d + half0 : d - half0];
+      }
+    }
+  }
+  pdl_wait();
+  pdl_trigger();
+  if (idx >= a.T * heads) return;
   const T* row = (const T*)a.proj + (size_t)t * a.ld;
   const int pos = (a.offset_dev ? *a.offset_dev : a.offset) + t;
   // A stale or mis-advanced device offset must not become a store into a neighbouring allocation: the row is dropped
@@ -466,18 +493,13 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepArgs a) {
   if (a.D <= 256) {
     // Every load (the row, the norm weights, the rotation partners) is issued before the first use, and the rotation
     // angles - double-precision pow / sincos, independent of the data - are computed while the loads are in flight.
-    T xv[8], wv[8], xpv[8], wpv[8];
+    T xv[8], xpv[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int d = lane + 32 * j;
       if (d < a.D) {
         xv[j] = src[d];
-        wv[j] = w[d];
-        if (d < a.rope_dims) {
-          const int pd = d < half ? d + half : d - half;
-          xpv[j] = src[pd];
-          wpv[j] = w[pd];
-        }
+        if (d < a.rope_dims) xpv[j] = src[d < half ? d + half : d - half];
       }
     }
     float cs_[8], sn_[8];

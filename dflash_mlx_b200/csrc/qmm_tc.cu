@@ -73,7 +73,8 @@ constexpr int kNumBars = 3 * kStages + 2 * kNA + 2;  // full, empty, x_landed, a
 // epilogue scratch: per-token factors (one copy per epilogue warp), one tile of residual values (bf16), one tile of the
 // other CTAs' summed partial sums (fp32)
 constexpr int kEpResOff = 256, kEpOthOff = kEpResOff + 16 * kRows * 2;
-constexpr int kEpSmemBytes = kEpOthOff + 16 * kRows * 4;
+constexpr int kEpNwOff = kEpOthOff + 16 * kRows * 4;   // the row's next-norm weight (mode 1), one bf16 per row
+constexpr int kEpSmemBytes = kEpNwOff + kRows * 2;
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kEpSmemBytes + 8 * kNumBars + 128;
 constexpr uint32_t kTmemCols = 512;      // operand buffers at columns 0..383, accumulators at 384..479
 constexpr uint32_t kDCol0 = 64 * kNA;
@@ -262,10 +263,13 @@ __device__ __forceinline__ void prefetch_row(const Epi& e, int n, int r, int M, 
   if (e.mode != 1) return;
   const unsigned short* rs = (const unsigned short*)e.residual;
   unsigned short v[16];
+  // the next norm's weight of this row (cold in HBM) rides with the residual values instead of waiting on the tail
+  const unsigned short nw = (e.next_w != nullptr && n < N) ? ((const unsigned short*)e.next_w)[n] : (unsigned short)0x3F80;
 #pragma unroll
   for (int t = 0; t < 16; ++t) v[t] = (n < N && t < M) ? rs[(size_t)t * N + n] : (unsigned short)0;
 #pragma unroll
   for (int t = 0; t < 16; ++t) res_sm[t * kRows + r] = v[t];
+  res_sm[(kEpNwOff - kEpResOff) / 2 + r] = nw;
 }
 
 // One finished row (all 16 tokens) of row tile nt: v = the accumulators.  Called by whole warps (modes 1 and 2 exchange
@@ -284,7 +288,7 @@ __device__ __forceinline__ void finish_row(const Epi& e, const Plan& plan, float
     return;
   }
   if (e.mode == 1) {
-    const float next_w = (e.next_w != nullptr && live) ? __bfloat162float(e.next_w[n]) : 1.f;
+    const float next_w = __uint_as_float((uint32_t)res_sm[(kEpNwOff - kEpResOff) / 2 + r] << 16);
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
       const float res = __uint_as_float((uint32_t)res_sm[t * kRows + r] << 16);

@@ -57,6 +57,7 @@ def _declare():
     d("dflash_verify_qmm_prefetch_next", None, [_vp, _vp, _vp, _i32, _i32])
     d("dflash_verify_qmm_set_prefetch_next", None, [_i32])
     d("dflash_gdn_forward_set_kernel", None, [_i32])
+    d("dflash_gdn_forward_state_is_settled", None, [])
     d("dflash_verify_qmm_fused", _i32, [_vp] * 6 + [_i32] * 5 + [_c.POINTER(QmmEpilogue), _vp, _c.c_size_t, _vp])
     d("dflash_gdn_layer_supported", _i32, [_i32] * 8)
     d("dflash_gdn_layer", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 14 + [_ll] + [_i32] * 6 + [_f32, _i32, _i32, _vp])
@@ -590,6 +591,7 @@ class HybridVerifyModel:
                                                   self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), self.conv[nxt][ig].data_ptr(),
                                                   self.tape_qkv[ig].data_ptr(), T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
                                                   cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, st), "dflash_gdn_prep")
+                    lib.dflash_gdn_forward_state_is_settled()     # the kernel before it is gdn_prep: it does not write the state
                     self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
                                                           self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
                                                           self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),

@@ -183,6 +183,10 @@ DFLASH_API void dflash_tape_replay_set_stream_kernel(int mode);
  * The two agree to fp32 rounding (another summation order), not bit for bit; either one's tape replays to its own
  * state bit for bit. */
 DFLASH_API void dflash_gdn_forward_set_kernel(int mode);
+/* One-shot promise for this thread's next dflash_gdn_forward_tape call: the kernel launched before it in the stream does
+ * not write state_in (true in a verify step, false when one call's state_out feeds the next call).  The low-latency record
+ * kernel then requests the state rows before its wait on that kernel.  Results do not change. */
+DFLASH_API void dflash_gdn_forward_state_is_settled(void);
 
 /* ---------------------------------------------------------------------------------------------
  * verify_sdpa: exact softmax attention of 16 query rows per head over N keys (split-KV + combine).
