@@ -386,7 +386,7 @@ class MoeStepWorkload(DenseStepWorkload):
         achieved = per_launch / us_per_launch / 1e3
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": peak_src,
-                "kernel": "expert-gathered qmm_stream_kernel (rows gathered: gate|up; K chunks gathered: down), timed with "
+                "kernel": "expert-gathered qmm_tc_kernel (tcgen05; rows gathered: gate|up; K chunks gathered: down), timed with "
                           "their routing and SwiGLU kernels",
                 "launches_per_step": n, "algorithmic_bytes_per_launch": per_launch, "us_per_launch": us_per_launch,
                 "matmul_share_of_step": aux_ms / ms_per_step,

@@ -879,7 +879,8 @@ extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, 
   const int K = mode == 1 ? Kb : n_max * Kb, N = mode == 1 ? n_max * block_rows : block_rows;
   if (!make_plan(M, K, N, 64, device, &plan, true)) return 0;
   plan.maxp = Cfg<64>::kSlabKMax / Cfg<64>::BK + 1;
-  return plan_workspace(plan, device);
+  const size_t a = plan_workspace(plan, device), b = tc::gather_workspace_bytes(M, block_rows, Kb, n_max, mode, device, g_max_blocks);
+  return a > b ? a : b;   // either kernel may run (dflash_verify_qmm_set_impl)
 }
 
 extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
@@ -894,6 +895,13 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
   auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al(x) || !al(w_q) || !al(scales) || !al(biases)) return fail(DFLASH_ERR_MISALIGNED, "moe_qmm: operands must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DFLASH_BF16 && g_impl != 1 && ((uintptr_t)workspace & 255) == 0) {   // the tcgen05 kernel where it applies
+    int device = 0;
+    cudaGetDevice(&device);
+    const int rc = tc::launch_gather(x, w_q, scales, biases, y, M, experts, block_rows, Kb, mode, slot_expert, n_active, n_max,
+                                     workspace, workspace_bytes, st, device, g_max_blocks);
+    if (rc <= 0) { if (rc == 0) g_last_impl = 2; return rc; }
+  }
   if (dtype == DFLASH_BF16)
     return mode == 1 ? launch_gather<__nv_bfloat16, 1>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st)
                      : launch_gather<__nv_bfloat16, 2>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st);

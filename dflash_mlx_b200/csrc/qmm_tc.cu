@@ -97,6 +97,18 @@ struct NextPlan {
   int valid, C, NT, ctas;
 };
 constexpr int kPrefetchUnits = 4;  // units per block of the next matmul (one ring's worth)
+// Expert-gathered launches (mixture-of-experts layers): the weights are stacked expert matrices of `block_rows` rows
+// and `cpb` K chunks each; only the experts slot_expert[0 .. *n_dev) take part, and their number is known on the device.
+//   GATHER 1, rows gathered:   row tile nt reads expert slot nt / block_tiles          (gate|up of the active experts)
+//   GATHER 2, chunks gathered: K chunk kc reads expert slot kc / cpb, x chunk kc        (down, summed over the experts)
+// Only the weight coordinates and the tile / chunk counts change; the host plans for n_max slots, the block patches
+// NT (or C) and the number of working blocks from *n_dev after the wait on the routing kernel.
+struct Gather {
+  int mode, block_tiles, cpb, block_rows, n_max;
+  const int* slot_expert;
+  const int* n_dev;
+};
+constexpr int kMaxSlots = 272;
 
 __device__ __forceinline__ int cta_of(unsigned u, unsigned units, unsigned ctas) {
   return (int)(((u + 1u) * ctas - 1u) / units);
@@ -387,7 +399,7 @@ struct Roles {
   static_assert(kNA % kSlots == 0 && kNA % kClasses == 0, "a ring buffer must belong to one slot and one pair class");
 };
 
-template <int NDQ>
+template <int NDQ, int GATHER>
 __global__ void __launch_bounds__(Roles<NDQ>::kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmX,
@@ -395,7 +407,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               unsigned* __restrict__ counters, const __grid_constant__ Plan plan,
               const __grid_constant__ Epi epi, int* __restrict__ err, unsigned long long* __restrict__ stamps,
               const __grid_constant__ CUtensorMap nxW, const __grid_constant__ CUtensorMap nxS,
-              const __grid_constant__ CUtensorMap nxB, const __grid_constant__ NextPlan nxt) {
+              const __grid_constant__ CUtensorMap nxB, const __grid_constant__ NextPlan nxt,
+              const __grid_constant__ Gather ga) {
   using R = Roles<NDQ>;
   // Optional time stamps (dflash_verify_qmm_set_stamps): 16 words per CTA, [0] / [1] = %globaltimer at entry / exit,
   // [2..10] = this SM's clock at entry, set-up done, first activation tile landed, first stage complete, first operand
@@ -421,10 +434,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int bl = (int)blockIdx.x;
-  if (bl >= plan.ctas) return;  // before any allocation or barrier
-  const int C = plan.C, NT = plan.NT, M = plan.M, N = plan.N;
+  Plan P = plan;
+  __shared__ int s_slots[GATHER != 0 ? kMaxSlots : 1];
+  if constexpr (GATHER != 0) {
+    pdl_wait();  // the slot list and its length are the routing kernel's output
+    int n_act = *ga.n_dev;
+    n_act = n_act < 0 ? 0 : (n_act > ga.n_max ? ga.n_max : n_act);
+    if (GATHER == 1) P.NT = n_act * ga.block_tiles; else P.C = n_act * ga.cpb;
+    const unsigned total_units = (unsigned)P.NT * (unsigned)P.C;
+    if (total_units == 0u) {  // no active expert here: the summed output is zero, the gathered rows do not exist
+      if (GATHER == 2)
+        for (int i = bl * (int)blockDim.x + tid; i < plan.M * plan.N; i += (int)(gridDim.x * blockDim.x)) y[i] = __float2bfloat16_rn(0.f);
+      return;
+    }
+    P.ctas = total_units < gridDim.x ? (int)total_units : (int)gridDim.x;
+  }
+  if (bl >= P.ctas) return;  // before any allocation or barrier
+  const int C = P.C, NT = P.NT, M = P.M, N = P.N;
   const unsigned units = (unsigned)NT * (unsigned)C;
-  const unsigned u_begin = (unsigned)bl * units / plan.ctas, u_end = (unsigned)(bl + 1) * units / plan.ctas;
+  const unsigned u_begin = (unsigned)bl * units / P.ctas, u_end = (unsigned)(bl + 1) * units / P.ctas;
   const unsigned npairs = (u_end - u_begin) * 4u;
   const int nt0 = (int)(u_begin / (unsigned)C), nt1 = (int)((u_end - 1) / (unsigned)C);
 
@@ -436,14 +464,32 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   auto request_weights = [&]() {  // the weights, scales and biases of unit p_u into stage p_stage
     const uint32_t full = bar_full + 8 * p_stage, dst = smem_u32(stages + p_stage * kStageBytes);
     mbar_arrive_expect_tx(full, kTmaBytes);
-    tma_load_2d(dst, &tmW, p_kc * (kBK / 2), p_nt * kRows, full, pol_stream);
-    tma_load_2d(dst + kRows * 128, &tmW, p_kc * (kBK / 2) + 128, p_nt * kRows, full, pol_stream);
-    tma_load_2d(dst + kWBytes, &tmS, p_kc * 8, p_nt * kRows, full, pol_keep);
-    tma_load_2d(dst + kWBytes + kSBBytes, &tmB, p_kc * 8, p_nt * kRows, full, pol_keep);
+    int wy = p_nt * kRows, wx = p_kc * (kBK / 2), sx = p_kc * 8;
+    if constexpr (GATHER == 1) {
+      const int slot = p_nt / ga.block_tiles;
+      wy = s_slots[slot] * ga.block_rows + (p_nt - slot * ga.block_tiles) * kRows;
+    }
+    if constexpr (GATHER == 2) {
+      const int slot = p_kc / ga.cpb, kin = p_kc - slot * ga.cpb;
+      wy = s_slots[slot] * ga.block_rows + p_nt * kRows;
+      wx = kin * (kBK / 2);
+      sx = kin * 8;
+    }
+    tma_load_2d(dst, &tmW, wx, wy, full, pol_stream);
+    tma_load_2d(dst + kRows * 128, &tmW, wx + 128, wy, full, pol_stream);
+    tma_load_2d(dst + kWBytes, &tmS, sx, wy, full, pol_keep);
+    tma_load_2d(dst + kWBytes + kSBBytes, &tmB, sx, wy, full, pol_keep);
     if (++p_stage == kStages) { p_stage = 0; p_par ^= 1; }
     if (++p_kc == C) { p_kc = 0; ++p_nt; }
     ++p_u;
   };
+  if constexpr (GATHER != 0) {
+    if (warp == R::kProducerWarp) {  // the slot -> expert table, for the producer thread alone
+      const int n_slots = GATHER == 1 ? NT / ga.block_tiles : C / ga.cpb;
+      for (int i = lane; i < n_slots && i < kMaxSlots; i += 32) s_slots[i] = ga.slot_expert[i];
+      __syncwarp();
+    }
+  }
   if (warp == R::kProducerWarp && lane == 0) {
     // The producer thread sets the barriers up itself and asks for the first units' weights at once (they are written by
     // no kernel): the requests are on their way while the rest of the block is still being set up.
@@ -653,7 +699,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const int seg = nt - nt0;
       prefetch_row(epi, nt * kRows + r, r, M, N, res_sm);
       int first_cta = 0;
-      const int total = tile_pieces(plan, nt, &first_cta);  // CTAs that share row tile nt
+      const int total = tile_pieces(P, nt, &first_cta);  // CTAs that share row tile nt
       // A row tile cut over several CTAs is summed from fp32 partial tiles by the tile's FIRST CTA, as (p1 + p2 + ...) +
       // p0 with p0 its own part, which never leaves its registers.  The tile is the end of that CTA's span and the start
       // (or the whole) of the others', so the others are normally done long before: the first CTA waits for their
@@ -679,7 +725,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         float acc[16];
 #pragma unroll
         for (int t = 0; t < 16; ++t) acc[t] = 0.f;
-        if (!aborted) sum_pieces(plan, pieces, nt, 1, total, r, acc);
+        if (!aborted) sum_pieces(P, pieces, nt, 1, total, r, acc);
 #pragma unroll
         for (int t = 0; t < 16; ++t) oth_sm[t * kRows + r] = acc[t];
       }
@@ -719,7 +765,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
           for (int t = 0; t < 16; ++t) out[t] = oth_sm[t * kRows + r] + out[t];
         }
-        finish_row(epi, plan, out, inv_sm, res_sm, y, bias, nt, r, lane);
+        finish_row(epi, P, out, inv_sm, res_sm, y, bias, nt, r, lane);
         if (owner && lane == 0) counters[nt * 4 + (warp & 3)] = 0;  // every other part has arrived: ready for the next launch
       }
       if (etid == 0 && nt == nt1) mark(9);
@@ -829,12 +875,12 @@ bool get_map(const void* ptr, int a, int b, int kind, CUtensorMap* out) {
   return true;
 }
 
-template <int NDQ>
+template <int NDQ, int GATHER = 0>
 cudaError_t launch_variant(int grid, cudaStream_t st, int device, const CUtensorMap& tw, const CUtensorMap& ts,
                            const CUtensorMap& tb, const CUtensorMap& tx, const void* bias, void* y, float4* pieces,
                            unsigned* counters, const Plan& plan, const Epi& epi, const CUtensorMap& nw,
-                           const CUtensorMap& ns, const CUtensorMap& nb, const NextPlan& nxt) {
-  auto kern = qmm_tc_kernel<NDQ>;
+                           const CUtensorMap& ns, const CUtensorMap& nb, const NextPlan& nxt, const Gather& ga = Gather{}) {
+  auto kern = qmm_tc_kernel<NDQ, GATHER>;
   static bool attr_done[64] = {};
   if (!attr_done[device & 63]) {
     cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
@@ -848,7 +894,7 @@ cudaError_t launch_variant(int grid, cudaStream_t st, int device, const CUtensor
   }
   return launch_kernel(kern, dim3(grid), dim3(Roles<NDQ>::kThreads), kSmemBytes, st, tw, ts, tb, tx,
                        (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, pieces, counters, plan, epi,
-                       device_error_word(device), g_stamps, nw, ns, nb, nxt);
+                       device_error_word(device), g_stamps, nw, ns, nb, nxt, ga);
 }
 
 }  // namespace
@@ -891,6 +937,64 @@ size_t workspace_bytes(int M, int K, int N, int device, int max_blocks) {
   Plan p;
   if (!make_plan(M, K, N, device, max_blocks, &p)) return 0;
   return plan_workspace(p);
+}
+
+// ---- expert-gathered launches ------------------------------------------------------------------------------------
+// The plan of the largest case (n_max active slots) and the largest number of blocks that can share a row tile over
+// every possible number of active slots (it sizes the partial-tile workspace).
+bool gather_plan(int M, int block_rows, int Kb, int n_max, int mode, int device, int max_blocks, Plan* p) {
+  if (block_rows % kRows != 0 || Kb % kBK != 0 || n_max < 1 || n_max > kMaxSlots) return false;
+  const int K = mode == 1 ? Kb : n_max * Kb, N = mode == 1 ? n_max * block_rows : block_rows;
+  if (!make_plan(M, K, N, device, max_blocks, p)) return false;
+  const long long grid = p->ctas;
+  long long worst = 1;
+  for (int n = 1; n <= n_max; ++n) {
+    const long long NT = mode == 1 ? (long long)n * (block_rows / kRows) : block_rows / kRows;
+    const long long C = mode == 1 ? Kb / kBK : (long long)n * (Kb / kBK);
+    const long long U = NT * C, ctas = U < grid ? U : grid, L = U / ctas;
+    long long mp = C > 1 ? (C - 1 + L - 1) / L + 1 : 1;
+    if (mp > ctas) mp = ctas;
+    if (mp > worst) worst = mp;
+  }
+  p->maxp = (int)worst;
+  return true;
+}
+
+size_t gather_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode, int device, int max_blocks) {
+  Plan p;
+  if (!gather_plan(M, block_rows, Kb, n_max, mode, device, max_blocks, &p)) return 0;
+  return plan_workspace(p);
+}
+
+// Returns DFLASH_OK, a negative status, or +1 when this shape is not handled here (the caller then runs qmm.cu).
+int launch_gather(const void* x, const void* wq, const void* sc, const void* bi, void* y, int M, int experts, int block_rows,
+                  int Kb, int mode, const int* slot_expert, const int* n_dev, int n_max, void* ws, size_t ws_bytes,
+                  cudaStream_t st, int device, int max_blocks) {
+  Plan plan;
+  if (!gather_plan(M, block_rows, Kb, n_max, mode, device, max_blocks, &plan)) return 1;
+  CUtensorMap tw, ts, tb, tx;
+  if (!get_map(wq, experts * block_rows, Kb / 2, 0, &tw) || !get_map(sc, experts * block_rows, Kb / kG, 1, &ts) ||
+      !get_map(bi, experts * block_rows, Kb / kG, 1, &tb) || !get_map(x, M, plan.K, 2, &tx))
+    return 1;
+  const size_t need = plan_workspace(plan);
+  if (ws == nullptr || ws_bytes < need)
+    return fail(DFLASH_ERR_WORKSPACE, "moe_qmm needs %zu workspace bytes, got %zu", need, ws_bytes);
+  unsigned* counters = (unsigned*)ws;
+  float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
+  Gather ga{mode, block_rows / kRows, Kb / kBK, block_rows, n_max, slot_expert, n_dev};
+  Epi epi = {};
+  NextPlan nxt = {};
+  cudaError_t e;
+  if (g_ndq == 12) {
+    e = mode == 1 ? launch_variant<12, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga)
+                  : launch_variant<12, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga);
+  } else {
+    e = mode == 1 ? launch_variant<8, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga)
+                  : launch_variant<8, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "moe_qmm (tcgen05) launch: %s", cudaGetErrorString(e));
+  return DFLASH_OK;
 }
 
 // Returns DFLASH_OK, a negative status, or +1 when this shape is not handled here (the caller then runs qmm.cu).
