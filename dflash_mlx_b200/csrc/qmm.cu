@@ -902,6 +902,7 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
                                      workspace, workspace_bytes, st, device, g_max_blocks);
     if (rc <= 0) { if (rc == 0) g_last_impl = 2; return rc; }
   }
+  g_last_impl = 1;
   if (dtype == DFLASH_BF16)
     return mode == 1 ? launch_gather<__nv_bfloat16, 1>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st)
                      : launch_gather<__nv_bfloat16, 2>(x, w_q, scales, biases, y, M, experts, block_rows, Kb, slot_expert, n_active, n_max, workspace, workspace_bytes, st);

@@ -201,3 +201,24 @@ def test_low_latency_record_kernel_against_the_general_one(K, T, Hk, Hv, Dv):
     assert _rel(tape, tape_ref) <= 1e-4 and _rel(s, s_ref) <= 1e-4 and _rel(y, y_ref) <= 1e-2
     full = K.tape_replay_kernel(tape, c["k"].to(d), c["g"].to(d), c["state"].to(d))
     assert torch.equal(full, s)
+
+
+def test_settled_state_promise_changes_nothing(K):
+    """dflash_gdn_forward_state_is_settled lets the record kernel read the state before it waits for the previous
+    kernel; with nothing writing the state in between the results are bit for bit the same, and the promise is good
+    for one call."""
+    from dflash_mlx_b200 import _lib
+    lib = _lib.lib()
+    _lib.declare("dflash_gdn_forward_state_is_settled", None, [])
+    c = og.make_gdn_case(seed=91)
+    d = "cuda"
+    args = [c[n].to(d) for n in ("q", "k", "v", "g", "beta", "state")]
+    torch.cuda.synchronize()
+    y0, s0, t0 = K.gated_delta_kernel_with_tape(*args)
+    lib.dflash_gdn_forward_state_is_settled()
+    y1, s1, t1 = K.gated_delta_kernel_with_tape(*args)
+    y2, s2, t2 = K.gated_delta_kernel_with_tape(*args)
+    torch.cuda.synchronize()
+    assert lib.dflash_device_error(0) == 0
+    for a, b in ((y0, y1), (s0, s1), (t0, t1), (y0, y2), (s0, s2), (t0, t2)):
+        assert torch.equal(a, b)

@@ -110,3 +110,24 @@ def test_graph_capture_with_changing_routing(mod):
         torch.cuda.synchronize()
         assert _rel(out.cpu(), om.moe_ref(x2, l2, gu, dn, 4, inter=512)) <= REL_TOL
     assert _lib.lib().dflash_device_error(0) == 0
+
+
+@pytest.mark.parametrize("T,H,inter,E,k,seed", [(16, 512, 512, 16, 4, 21), (16, 2048, 512, 64, 8, 22), (5, 1024, 512, 8, 2, 23)])
+def test_mma_sync_gather_kernels_still_match_the_oracle(mod, T, H, inter, E, k, seed):
+    """The expert-gathered matmuls run on the tcgen05 kernel by default; dflash_verify_qmm_set_impl(1) selects the
+    mma.sync gather kernels (exact integer nibbles, scale applied to the accumulator).  Both meet the oracle; they agree
+    with each other within the same tolerance."""
+    _lib, _ = mod
+    lib = _lib.lib()
+    x, logits, gu, dn = om.make_moe_case(seed, T=T, H=H, inter=inter, E=E)
+    want = om.moe_ref(x, logits, gu, dn, k, inter=inter)
+    _, tc = _run(mod, x, logits, gu, dn, k, inter, E)
+    assert lib.dflash_verify_qmm_last_impl() == 2
+    try:
+        lib.dflash_verify_qmm_set_impl(1)
+        _, old = _run(mod, x, logits, gu, dn, k, inter, E)          # its own block: a workspace is not shared between the kernels
+        assert lib.dflash_verify_qmm_last_impl() == 1
+    finally:
+        lib.dflash_verify_qmm_set_impl(0)
+    assert lib.dflash_device_error(0) == 0
+    assert _rel(tc, want) <= REL_TOL and _rel(old, want) <= REL_TOL and _rel(tc, old) <= REL_TOL

@@ -146,3 +146,35 @@ def test_refusals(env):
     st = lib.dflash_verify_qmm_fused(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None, t.data_ptr(), 16, 1024, 63,
                                      64, _lib.BF16, ctypes.byref(ep), ws.data_ptr(), ws.numel(), None)
     assert st == -2
+
+
+def test_next_matmul_hint_changes_nothing(env):
+    """dflash_verify_qmm_prefetch_next only makes the next call's kernel pull the announced weights into L2: the
+    results of that call are bit for bit those of an unannounced call; a hint naming a shape the tensor-memory kernel
+    does not take is ignored; a hint is consumed by one call."""
+    lib, _, ws, _lib = env
+    M, K, N = 16, 2048, 1536
+    x, wq, s, b = oq.make_qmm_case(M, K, N, seed=5, x_std=8.0 / K ** 0.5, w_std=0.05)
+    _, wq2, s2, b2 = oq.make_qmm_case(M, 1024, 640, seed=6, x_std=0.2, w_std=0.05)
+    d = "cuda"
+    xd, wd, sd, bd = x.to(d), wq.to(d), s.to(d), b.to(d)
+    w2, s2d, b2d = wq2.to(d), s2.to(d), b2.to(d)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=d)
+        rc = lib.dflash_verify_qmm(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), None, y.data_ptr(), M, K, N, 64,
+                                   _lib.BF16, ws.data_ptr(), ws.numel(), st)
+        assert rc == 0, lib.dflash_last_error_string()
+        torch.cuda.synchronize()
+        return y
+
+    plain = run()
+    lib.dflash_verify_qmm_prefetch_next(w2.data_ptr(), s2d.data_ptr(), b2d.data_ptr(), 1024, 640)
+    hinted = run()
+    after = run()                                     # the hint is gone
+    lib.dflash_verify_qmm_prefetch_next(w2.data_ptr(), s2d.data_ptr(), b2d.data_ptr(), 1000, 640)   # K % 512 != 0: ignored
+    odd = run()
+    assert lib.dflash_device_error(0) == 0
+    assert torch.equal(plain, hinted) and torch.equal(plain, after) and torch.equal(plain, odd)
+    assert oq.max_rel_err(plain.cpu(), x.float() @ _w_hat(wq, s, b).t()) <= REL
