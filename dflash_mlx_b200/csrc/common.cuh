@@ -40,7 +40,7 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
 size_t gather_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode, int device, int max_blocks);
 int launch_gather(const void* x, const void* wq, const void* sc, const void* bi, void* y, int M, int experts, int block_rows,
                   int Kb, int mode, const int* slot_expert, const int* n_dev, int n_max, void* ws, size_t ws_bytes,
-                  cudaStream_t st, int device, int max_blocks);
+                  cudaStream_t st, int device, int max_blocks, const dflash_qmm_epilogue* epilogue = nullptr);
 void set_roles(int dequant_warps, int issuing_threads);
 void set_k_parts(int k_parts);
 void set_stamps(void* dev);

@@ -912,6 +912,37 @@ extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
   return fail(DFLASH_ERR_BAD_ARG, "moe_qmm: dtype %d (want bf16 or f16)", dtype);
 }
 
+extern "C" int dflash_moe_qmm_fused_supported(int M, int block_rows, int Kb, int n_max, int mode, int dtype) {
+  return (dtype == DFLASH_BF16 && g_impl != 1 && M >= 1 && M <= 16 && block_rows >= 128 && block_rows % 128 == 0 && Kb >= 512 &&
+          Kb % 512 == 0 && n_max >= 1 && n_max <= 272 && (mode == 1 || mode == 2)) ? 1 : 0;
+}
+
+extern "C" int dflash_moe_qmm_fused(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
+                                    int experts, int block_rows, int Kb, int mode, const int* slot_expert,
+                                    const int* n_active, int n_max, int dtype, const dflash_qmm_epilogue* ep,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w_q || !scales || !biases || !y || !slot_expert || !n_active || !ep)
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm_fused: null operand");
+  if (n_max > experts || !dflash_moe_qmm_fused_supported(M, block_rows, Kb, n_max, mode, dtype))
+    return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm_fused: needs bf16, 1 <= M <= 16, block_rows %% 128 == 0, Kb %% 512 == 0, n_max <= 272");
+  if (ep->mode != 0 && !(ep->mode == 1 && mode == 2))
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm_fused: epilogue mode %d with gather mode %d (0 anywhere, 1 on the summed output)", ep->mode, mode);
+  if (ep->in_ssq != nullptr && (ep->in_parts < 1 || !(ep->in_dim > 0.f) || ((uintptr_t)ep->in_ssq & 15) != 0))
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm_fused: in_ssq needs in_parts >= 1, in_dim > 0 and 16-byte alignment");
+  if (ep->mode == 1 && (!ep->residual || ((const void*)ep->scaled == (const void*)y && ep->scaled)))
+    return fail(DFLASH_ERR_BAD_ARG, "moe_qmm_fused: mode 1 needs a residual, and scaled must not alias y");
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (!al(x) || !al(w_q) || !al(scales) || !al(biases) || ((uintptr_t)workspace & 255) != 0)
+    return fail(DFLASH_ERR_MISALIGNED, "moe_qmm_fused: operands must be 16-byte, the workspace 256-byte aligned");
+  int device = 0;
+  cudaGetDevice(&device);
+  const int rc = tc::launch_gather(x, w_q, scales, biases, y, M, experts, block_rows, Kb, mode, slot_expert, n_active, n_max,
+                                   workspace, workspace_bytes, (cudaStream_t)stream, device, g_max_blocks, ep);
+  if (rc > 0) return fail(DFLASH_ERR_BAD_SHAPE, "moe_qmm_fused: shape not handled by the tcgen05 kernel");
+  if (rc == 0) g_last_impl = 2;
+  return rc;
+}
+
 extern "C" void dflash_verify_qmm_set_impl(int impl) { g_impl = (impl == 2) ? 2 : (impl == 1 ? 1 : 0); }
 extern "C" int dflash_verify_qmm_last_impl(void) { return g_last_impl; }
 extern "C" void dflash_verify_qmm_set_stamps(void* dev_buffer) { tc::set_stamps(dev_buffer); }

@@ -443,6 +443,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (GATHER == 1) P.NT = n_act * ga.block_tiles; else P.C = n_act * ga.cpb;
     const unsigned total_units = (unsigned)P.NT * (unsigned)P.C;
     if (total_units == 0u) {  // no active expert here: the summed output is zero, the gathered rows do not exist
+      if (epi.mode != 0 && tid == 0) atomicCAS(err, 0, 19);  // a residual epilogue needs at least one expert (callers keep the shared one)
       if (GATHER == 2)
         for (int i = bl * (int)blockDim.x + tid; i < plan.M * plan.N; i += (int)(gridDim.x * blockDim.x)) y[i] = __float2bfloat16_rn(0.f);
       return;
@@ -969,7 +970,7 @@ size_t gather_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode
 // Returns DFLASH_OK, a negative status, or +1 when this shape is not handled here (the caller then runs qmm.cu).
 int launch_gather(const void* x, const void* wq, const void* sc, const void* bi, void* y, int M, int experts, int block_rows,
                   int Kb, int mode, const int* slot_expert, const int* n_dev, int n_max, void* ws, size_t ws_bytes,
-                  cudaStream_t st, int device, int max_blocks) {
+                  cudaStream_t st, int device, int max_blocks, const dflash_qmm_epilogue* ep) {
   Plan plan;
   if (!gather_plan(M, block_rows, Kb, n_max, mode, device, max_blocks, &plan)) return 1;
   CUtensorMap tw, ts, tb, tx;
@@ -983,6 +984,11 @@ int launch_gather(const void* x, const void* wq, const void* sc, const void* bi,
   float4* pieces = (float4*)((uint8_t*)ws + counters_bytes());
   Gather ga{mode, block_rows / kRows, Kb / kBK, block_rows, n_max, slot_expert, n_dev};
   Epi epi = {};
+  if (ep != nullptr) {
+    epi.mode = ep->mode; epi.in_parts = ep->in_parts; epi.in_dim = ep->in_dim; epi.eps = ep->eps;
+    epi.in_ssq = ep->in_ssq; epi.residual = (const __nv_bfloat16*)ep->residual;
+    epi.next_w = (const __nv_bfloat16*)ep->next_w; epi.scaled = (__nv_bfloat16*)ep->scaled; epi.out_ssq = ep->out_ssq;
+  }
   NextPlan nxt = {};
   cudaError_t e;
   if (g_ndq == 12) {

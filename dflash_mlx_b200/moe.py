@@ -32,6 +32,8 @@ def _declare():
     _lib.declare("dflash_moe_qmm_workspace_bytes", sz, [i32, i32, i32, i32, i32])
     _lib.declare("dflash_moe_qmm", i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, sz, vp])
     _lib.declare("dflash_moe_swiglu", i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp])
+    _lib.declare("dflash_moe_qmm_fused_supported", i32, [i32, i32, i32, i32, i32, i32])
+    _lib.declare("dflash_moe_qmm_fused", i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, sz, vp])
     _declared = True
 
 
@@ -85,12 +87,20 @@ class MoEBlock:
         else:
             self.ws = torch.zeros(need, dtype=torch.uint8, device=self.dev)
         self.launches = 4
+        # the two gathered matmuls can carry the epilogues of dflash_verify_qmm_fused (tcgen05 kernel, bf16)
+        with torch.cuda.device(self.dev):
+            self.epilogues = bool(self.lib.dflash_moe_qmm_fused_supported(rows, 2 * inter, hidden, self.n_max, 1, self.code)
+                                  and self.lib.dflash_moe_qmm_fused_supported(rows, hidden, inter, self.n_max, 2, self.code))
 
     def workspace_bytes(self) -> int:
         return self.ws.numel()
 
-    def __call__(self, x: torch.Tensor, logits: torch.Tensor, gate_up: dict, down: dict, out: torch.Tensor) -> torch.Tensor:
-        """x [T,H]; logits [T,E+1]; writes this rank's (partial) block output into ``out`` [T,H] and returns it."""
+    def __call__(self, x: torch.Tensor, logits: torch.Tensor, gate_up: dict, down: dict, out: torch.Tensor, *,
+                 x_ep=None, out_ep=None) -> torch.Tensor:
+        """x [T,H]; logits [T,E+1]; writes this rank's (partial) block output into ``out`` [T,H] and returns it.
+        ``x_ep`` / ``out_ep`` (ctypes ``dflash_qmm_epilogue``; both or neither, needs ``self.epilogues``): epilogue of
+        the gate|up matmul (mode 0 with ``in_ssq``: ``x`` is ``h * norm_weight``, the RMS factor is applied to the
+        accumulators) and of the summed down projection (mode 1: ``out`` is the residual stream, added in place)."""
         lib, T, H, I = self.lib, self.T, self.H, self.I
         st = torch.cuda.current_stream(self.dev).cuda_stream
         rows_total = gate_up["w"].shape[0] // (2 * I)
@@ -98,12 +108,30 @@ class MoEBlock:
                                         self.n_max, self.slot_expert.data_ptr(), self.n_active.data_ptr(),
                                         self.wdense.data_ptr(), self.topk_ids.data_ptr(), self.topk_w.data_ptr(), self.code, st),
                    "dflash_moe_route")
-        _lib.check(lib.dflash_moe_qmm(x.data_ptr(), gate_up["w"].data_ptr(), gate_up["s"].data_ptr(), gate_up["b"].data_ptr(),
-                                      self.gu.data_ptr(), T, rows_total, 2 * I, H, 1, self.slot_expert.data_ptr(),
-                                      self.n_active.data_ptr(), self.n_max, self.code, self.ws.data_ptr(), self.ws.numel(), st),
-                   "dflash_moe_qmm(rows)")
+        if (x_ep is None) != (out_ep is None):
+            raise ValueError("MoEBlock: pass both epilogues or neither")
+        if x_ep is not None:
+            if not self.epilogues:
+                raise ValueError("MoEBlock: epilogues need the tcgen05 gather kernel (bf16)")
+            _lib.check(lib.dflash_moe_qmm_fused(x.data_ptr(), gate_up["w"].data_ptr(), gate_up["s"].data_ptr(),
+                                                gate_up["b"].data_ptr(), self.gu.data_ptr(), T, rows_total, 2 * I, H, 1,
+                                                self.slot_expert.data_ptr(), self.n_active.data_ptr(), self.n_max, self.code,
+                                                ctypes.byref(x_ep), self.ws.data_ptr(), self.ws.numel(), st),
+                       "dflash_moe_qmm_fused(rows)")
+        else:
+            _lib.check(lib.dflash_moe_qmm(x.data_ptr(), gate_up["w"].data_ptr(), gate_up["s"].data_ptr(), gate_up["b"].data_ptr(),
+                                          self.gu.data_ptr(), T, rows_total, 2 * I, H, 1, self.slot_expert.data_ptr(),
+                                          self.n_active.data_ptr(), self.n_max, self.code, self.ws.data_ptr(), self.ws.numel(), st),
+                       "dflash_moe_qmm(rows)")
         _lib.check(lib.dflash_moe_swiglu(self.gu.data_ptr(), self.wdense.data_ptr(), self.n_active.data_ptr(),
                                          self.act.data_ptr(), T, I, self.n_max, self.code, st), "dflash_moe_swiglu")
+        if out_ep is not None:
+            _lib.check(lib.dflash_moe_qmm_fused(self.act.data_ptr(), down["w"].data_ptr(), down["s"].data_ptr(),
+                                                down["b"].data_ptr(), out.data_ptr(), T, rows_total, H, I, 2,
+                                                self.slot_expert.data_ptr(), self.n_active.data_ptr(), self.n_max, self.code,
+                                                ctypes.byref(out_ep), self.ws.data_ptr(), self.ws.numel(), st),
+                       "dflash_moe_qmm_fused(chunks)")
+            return out
         _lib.check(lib.dflash_moe_qmm(self.act.data_ptr(), down["w"].data_ptr(), down["s"].data_ptr(), down["b"].data_ptr(),
                                       out.data_ptr(), T, rows_total, H, I, 2, self.slot_expert.data_ptr(),
                                       self.n_active.data_ptr(), self.n_max, self.code, self.ws.data_ptr(), self.ws.numel(), st),

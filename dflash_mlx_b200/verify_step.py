@@ -301,17 +301,22 @@ class HybridVerifyModel:
         import os
         cfg, T = self.cfg, self.cfg.block
         explicit_off = fused is False
-        ok = self.moe is None and self.all_reduce is None and self.peer is None and getattr(cfg, "tp_world", 1) == 1
+        ok = self.all_reduce is None and self.peer is None and getattr(cfg, "tp_world", 1) == 1
+        if ok and self.moe is not None:
+            # the expert block as part of the chain: router and gate|up finish the post-norm from its partial sums, the
+            # summed down projection adds into the residual stream and prepares the next norm; the shared expert keeps
+            # the summed output non-empty
+            ok = self.moe.epilogues and cfg.moe_shared_here
         if ok:
             mats = [self.w["lm_head"]]
             for L in self.w["layers"]:
-                mats += [L[n] for n in ("proj", "o_proj", "out_proj", "gate_up", "down") if n in L]
+                mats += [L[n] for n in ("proj", "o_proj", "out_proj", "gate_up", "down", "router") if n in L]
             ok = all(self.lib.dflash_verify_qmm_fused_supported(T, W["w"].shape[1] * 8, W["w"].shape[0], cfg.group_size,
                                                                 _lib.BF16) == 1 for W in mats)
         if fused is None:
             fused = ok and os.environ.get("DFLASH_STEP_FUSED", "1") != "0"
         elif fused and not ok:
-            raise ValueError("the fused step needs a dense, unsharded model whose matmuls are bf16 / group 64 / K % 512 == 0")
+            raise ValueError("the fused step needs an unsharded model whose matmuls are bf16 / group 64 / K % 512 == 0")
         self.fused = bool(fused)
         # SwiGLU inside the gate|up epilogue also works for a tensor-parallel shard (nothing is summed over the ranks
         # between gate|up and SwiGLU): one launch less per layer
@@ -330,6 +335,8 @@ class HybridVerifyModel:
         self.ssq = [torch.zeros(parts, 16, dtype=torch.float32, device=self.dev) for _ in range(2)]
         self.ssq_parts = parts
         self.gate_up_il = []
+        if self.moe is not None:
+            return
         for L in self.w["layers"]:
             self.gate_up_il.append(self._interleave_gate_up(L["gate_up"]))
             if release_unfused:
@@ -431,6 +438,12 @@ class HybridVerifyModel:
         if delta is not None:
             self._reduce(delta)
         self._add_rmsnorm(delta, w)
+
+    def _moe_block_fused(self, i, L, nxt_w):
+        """Expert block inside the fused chain: x = hw (h * post_norm weight), the RMS factor from ssq[1]; the summed
+        down projection adds into h and leaves (h * next norm weight, partial sums of h^2) for the next matmul."""
+        self.moe(self.hw, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.h,
+                 x_ep=self._ep_in(1, self.ssq_parts), out_ep=self._ep_residual(nxt_w, 0))
 
     def _moe_all_to_all(self, i, L):
         """The expert block with token dispatch and combine as all-to-all exchanges (the classic expert-parallel
@@ -606,6 +619,20 @@ class HybridVerifyModel:
                 else:
                     self._qmm(self.mix_gdn, L["out_proj"], self.delta)
                 ig += 1
+            if fused and self.moe is not None:
+                # post_norm -> router / top-k -> gate|up of the active experts -> weighted SwiGLU -> summed down ->
+                # residual add -> the next layer's (or the final) norm
+                if self.routing_from is not None:
+                    self.router_logits[i].copy_(self.routing_from[i])
+                else:
+                    self._qmm_fused(self.hw, L["router"], self.router_logits[i], self._ep_in(1, self.ssq_parts))
+                nxt_w = layers[i + 1]["in_norm"] if i + 1 < len(layers) else self.w["norm"]
+                self._moe_block_fused(i, L, nxt_w)
+                self.launches_per_step += self.moe.launches
+                if self._moe_counts is not None:
+                    self._moe_counts.append(self.moe.n_active.clone())
+                in_parts = self.ssq_parts
+                continue
             if fused:
                 # post_norm -> gate|up -> SwiGLU -> down -> residual add -> the next layer's (or the final) norm
                 self._qmm_fused(self.hw, self.gate_up_il[i], self.act, self._ep_in(1, self.ssq_parts, mode=2))
@@ -709,8 +736,11 @@ class HybridVerifyModel:
                 nxt_w = layers[i + 1]["in_norm"] if i + 1 < len(layers) else self.w["norm"]
                 out.append((self.hw, L["proj"], self.proj, self._ep_in(0, in_parts)))
                 out.append((mix, Wo, self.h, self._ep_residual(L["post_norm"], 1)))
-                out.append((self.hw, self.gate_up_il[i], self.act, self._ep_in(1, self.ssq_parts, mode=2)))
-                out.append((self.act, L["down"], self.h, self._ep_residual(nxt_w, 0)))
+                if self.moe is not None:   # (the expert matmuls are not in this list)
+                    out.append((self.hw, L["router"], self.router_logits[i], self._ep_in(1, self.ssq_parts)))
+                else:
+                    out.append((self.hw, self.gate_up_il[i], self.act, self._ep_in(1, self.ssq_parts, mode=2)))
+                    out.append((self.act, L["down"], self.h, self._ep_residual(nxt_w, 0)))
                 in_parts = self.ssq_parts
                 continue
             out.append((self.x, L["proj"], self.proj, None))
@@ -728,8 +758,12 @@ class HybridVerifyModel:
 
     def run_experts_only(self):
         """The expert blocks of every layer alone, with the routing of the last verify pass (timing aid)."""
-        for i, L in enumerate(self.w["layers"]):
-            self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
+        layers = self.w["layers"]
+        for i, L in enumerate(layers):
+            if self.fused:
+                self._moe_block_fused(i, L, layers[i + 1]["in_norm"] if i + 1 < len(layers) else self.w["norm"])
+            else:
+                self.moe(self.x, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.delta)
 
     def run_qmm_only(self):
         """Every matmul of a step, with its epilogue, and nothing else (timing aid; the residual stream is overwritten)."""

@@ -361,6 +361,15 @@ DFLASH_API int dflash_moe_qmm(const void* x, const void* w_q, const void* scales
                               int n_max, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 DFLASH_API int dflash_moe_swiglu(const void* gate_up, const float* wdense, const int* n_active, void* act, int T_rows, int I,
                                  int n_max, int dtype, void* stream);
+/* dflash_moe_qmm on the tcgen05 kernel with an epilogue of dflash_verify_qmm_fused (bf16, block_rows % 128 == 0):
+ * mode 0 (+ in_ssq: x holds h * norm_weight and the per-token RMS factor multiplies the accumulators) on either gather
+ * mode; mode 1 (residual add into y, scaled = y * next_w, out_ssq) on the summed output of gather mode 2, which then
+ * needs at least one active slot (device error 19 otherwise: keep the shared expert on the rank). */
+DFLASH_API int dflash_moe_qmm_fused_supported(int M, int block_rows, int Kb, int n_max, int mode, int dtype);
+DFLASH_API int dflash_moe_qmm_fused(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
+                                    int experts, int block_rows, int Kb, int mode, const int* slot_expert,
+                                    const int* n_active, int n_max, int dtype, const dflash_qmm_epilogue* epilogue,
+                                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor-parallel reduction over peer-mapped memory, fused with the residual add and RMSNorm that consume it.

@@ -115,7 +115,8 @@ def test_moe_layers_at_configuration_5_dimensions():
     ref_logits, ref_toks, ref_new, tapes = om.verify_step_ref(cfg, W, ids, clone(caches), ctx, router_logits=injected)
     assert _rel(logits, ref_logits) <= 3e-2
     _check_tokens(m, ref_logits, ref_toks, 3e-2)
-    assert _rel(m.tape[0], tapes[0]["tape"]) <= 2e-3
+    # (the fused chain rounds the normed input at another place, as in the dense test above)
+    assert _rel(m.tape[0], tapes[0]["tape"]) <= (1.5e-2 if m.fused else 2e-3)
     # and the router itself: the CUDA router logits against the oracle's router matmul on the oracle's activations
     free_logits, _, _, _ = om.verify_step_ref(cfg, W, ids, clone(caches), ctx)
     assert _rel(logits, free_logits) <= 6e-2          # a near-tie in a top-8 choice may swap one expert

@@ -399,3 +399,45 @@ def test_suppressed_tokens_are_never_the_greedy_choice(setup):
     want = torch.where(mask[None, :], floor, logits.float()).argmax(dim=-1).to(torch.int32)
     assert torch.equal(m.tokens, want)
     assert not bool(mask[m.tokens.long()].any())
+
+
+def test_moe_fused_chain_against_separate_kernels():
+    """One GPU, mixture-of-experts layers: the router, the gathered gate|up matmul (post-norm finished from its partial
+    sums) and the summed down projection (residual add, next norm's scale and partial sums) as one chain of matmul
+    epilogues, against the same step with separate add + RMSNorm kernels.  Both passes route by the first pass's router
+    logits (a near-tie in the top-k is a discontinuity of the model, not an arithmetic difference).  3e-2 of the
+    largest logit / hidden value, as for the dense chain."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200.verify_step import HybridVerifyModel, weights_to
+    from dflash_mlx_b200 import _lib
+    from tests.test_verify_step import small_moe_case
+    cfg, W, caches, ids, ctx = small_moe_case()
+    Wd = weights_to(W, "cuda")
+
+    def load(m):
+        for l in range(len(caches["state"])):
+            m.state[m.cur][l].copy_(caches["state"][l])
+            m.conv[m.cur][l].copy_(caches["conv"][l])
+        for l in range(len(caches["k"])):
+            m.kcache[l].copy_(caches["k"][l])
+            m.vcache[l].copy_(caches["v"][l])
+        m.offset = ctx
+
+    mf = HybridVerifyModel(cfg, Wd, "cuda")
+    if not mf.fused:
+        pytest.skip("the expert block's epilogues do not apply to this shape")
+    mu = HybridVerifyModel(cfg, Wd, "cuda", fused=False)
+    assert not mu.fused
+    load(mf)
+    load(mu)
+    lf = mf.verify(ids.cuda()).float().clone()
+    mu.routing_from = mf.router_logits
+    lu = mu.verify(ids.cuda()).float().clone()
+    torch.cuda.synchronize()
+    assert _lib.lib().dflash_device_error(0) == 0
+    assert mf.launches_per_step < mu.launches_per_step
+    assert _rel(lf, lu) <= 3e-2 and _rel(mf.h, mu.h) <= 3e-2
+    top2 = lu.topk(2, dim=-1).values
+    sure = (top2[:, 0] - top2[:, 1]) > 3e-2 * lu.abs().max()
+    assert torch.equal(mf.tokens[sure], mu.tokens[sure])
