@@ -711,7 +711,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the single-op lines that ride along on one GPU")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
-    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense step with fewer layers")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run the dense / MoE step with fewer layers")
     ap.add_argument("--kv-len", type=int, default=0, help="profiling aid: KV length of verify_sdpa_cfg3 (default 8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -738,7 +738,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    if args.layers and args.workload == "dense_step_cfg4":
+    if args.layers and args.workload in ("dense_step_cfg4", "moe_step_cfg5"):
         wl = WORKLOADS[args.workload](rank, world, device, layers=args.layers)
     elif args.kv_len and args.workload == "verify_sdpa_cfg3":
         wl = WORKLOADS[args.workload](rank, world, device, kv_len=args.kv_len)

@@ -869,6 +869,14 @@ extern "C" size_t dflash_verify_qmm_workspace_bytes(int M, int K, int N, int gro
   return need;
 }
 
+namespace {
+// An announcement (dflash_verify_qmm_prefetch_next) is good for exactly one call, whichever kernel that call ends up in:
+// a hint left pending could outlive the weights it names.
+struct NextHintScope {
+  ~NextHintScope() { dflash::tc::set_next(nullptr, nullptr, nullptr, 0, 0); }
+};
+}  // namespace
+
 extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, int n_max, int mode) {
   if (M < 1 || M > 16 || block_rows < kBN || block_rows % kBN != 0 || Kb < 512 || Kb % 512 != 0 || n_max < 1 ||
       (mode != 1 && mode != 2))
@@ -886,6 +894,7 @@ extern "C" size_t dflash_moe_qmm_workspace_bytes(int M, int block_rows, int Kb, 
 extern "C" int dflash_moe_qmm(const void* x, const void* w_q, const void* scales, const void* biases, void* y, int M,
                               int experts, int block_rows, int Kb, int mode, const int* slot_expert, const int* n_active,
                               int n_max, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  NextHintScope hint_scope;
   if (!x || !w_q || !scales || !biases || !y || !slot_expert || !n_active)
     return fail(DFLASH_ERR_BAD_ARG, "moe_qmm: null operand");
   if (M < 1 || M > 16 || experts < 1 || n_max < 1 || n_max > experts || (mode != 1 && mode != 2))
@@ -921,6 +930,7 @@ extern "C" int dflash_moe_qmm_fused(const void* x, const void* w_q, const void* 
                                     int experts, int block_rows, int Kb, int mode, const int* slot_expert,
                                     const int* n_active, int n_max, int dtype, const dflash_qmm_epilogue* ep,
                                     void* workspace, size_t workspace_bytes, void* stream) {
+  NextHintScope hint_scope;
   if (!x || !w_q || !scales || !biases || !y || !slot_expert || !n_active || !ep)
     return fail(DFLASH_ERR_BAD_ARG, "moe_qmm_fused: null operand");
   if (n_max > experts || !dflash_moe_qmm_fused_supported(M, block_rows, Kb, n_max, mode, dtype))
@@ -954,14 +964,6 @@ extern "C" void dflash_verify_qmm_set_prefetch_next(int on) { tc::set_prefetch_n
 extern "C" void dflash_verify_qmm_set_tc_roles(int dequant_warps, int issuing_threads) {
   tc::set_roles(dequant_warps, issuing_threads);
 }
-
-namespace {
-// An announcement (dflash_verify_qmm_prefetch_next) is good for exactly one call, whichever kernel that call ends up in:
-// a hint left pending could outlive the weights it names.
-struct NextHintScope {
-  ~NextHintScope() { dflash::tc::set_next(nullptr, nullptr, nullptr, 0, 0); }
-};
-}  // namespace
 
 extern "C" int dflash_verify_qmm(const void* x, const void* w_q, const void* scales, const void* biases,
                                  const void* bias, void* y, int M, int K, int N, int group_size, int dtype,

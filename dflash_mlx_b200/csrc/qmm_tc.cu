@@ -550,7 +550,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       // system is idle: pull the next matmul's first units into L2 (a hint: nothing waits for it).
       if (nxt.valid) {
         const unsigned nunits = (unsigned)nxt.NT * (unsigned)nxt.C;
-        for (int nb = bl; nb < nxt.ctas; nb += (int)gridDim.x) {
+        // (at most two blocks' worth per block: the requests are issued by this one thread, and a small grid ahead of a
+        // large one would otherwise spend microseconds issuing them before its block may exit)
+        for (int nb = bl, done = 0; nb < nxt.ctas && done < 2; nb += (int)gridDim.x, ++done) {
           const unsigned b0 = (unsigned)nb * nunits / (unsigned)nxt.ctas, b1 = (unsigned)(nb + 1) * nunits / (unsigned)nxt.ctas;
           for (unsigned u = b0; u < b1 && u < b0 + (unsigned)kPrefetchUnits; ++u) {
             const int nt = (int)(u / (unsigned)nxt.C), kc = (int)(u % (unsigned)nxt.C);
@@ -940,6 +942,21 @@ size_t workspace_bytes(int M, int K, int N, int device, int max_blocks) {
   return plan_workspace(p);
 }
 
+// Consumes this thread's announcement (dflash_verify_qmm_prefetch_next), if any: the announced matmul's tensor maps and
+// block -> unit mapping.  The maps are left alone when there is none or it names a shape this kernel does not take.
+void take_next_hint(int M, int device, int max_blocks, CUtensorMap* nw, CUtensorMap* ns, CUtensorMap* nb, NextPlan* nxt) {
+  if (!t_next.valid) return;
+  t_next.valid = false;
+  Plan np;
+  CUtensorMap a, b, c;
+  if (g_prefetch_next && t_next.K % kBK == 0 && make_plan(M, t_next.K, t_next.N, device, max_blocks, &np) &&
+      get_map(t_next.wq, t_next.N, t_next.K / 2, 0, &a) && get_map(t_next.sc, t_next.N, t_next.K / kG, 1, &b) &&
+      get_map(t_next.bi, t_next.N, t_next.K / kG, 1, &c)) {
+    *nw = a; *ns = b; *nb = c;
+    nxt->valid = 1; nxt->C = np.C; nxt->NT = np.NT; nxt->ctas = np.ctas;
+  }
+}
+
 // ---- expert-gathered launches ------------------------------------------------------------------------------------
 // The plan of the largest case (n_max active slots) and the largest number of blocks that can share a row tile over
 // every possible number of active slots (it sizes the partial-tile workspace).
@@ -990,13 +1007,15 @@ int launch_gather(const void* x, const void* wq, const void* sc, const void* bi,
     epi.next_w = (const __nv_bfloat16*)ep->next_w; epi.scaled = (__nv_bfloat16*)ep->scaled; epi.out_ssq = ep->out_ssq;
   }
   NextPlan nxt = {};
+  CUtensorMap nw = tw, ns = ts, nb = tb;
+  take_next_hint(M, device, max_blocks, &nw, &ns, &nb, &nxt);
   cudaError_t e;
   if (g_ndq == 12) {
-    e = mode == 1 ? launch_variant<12, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga)
-                  : launch_variant<12, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga);
+    e = mode == 1 ? launch_variant<12, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, nw, ns, nb, nxt, ga)
+                  : launch_variant<12, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, nw, ns, nb, nxt, ga);
   } else {
-    e = mode == 1 ? launch_variant<8, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga)
-                  : launch_variant<8, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, tw, ts, tb, nxt, ga);
+    e = mode == 1 ? launch_variant<8, 1>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, nw, ns, nb, nxt, ga)
+                  : launch_variant<8, 2>(plan.ctas, st, device, tw, ts, tb, tx, nullptr, y, pieces, counters, plan, epi, nw, ns, nb, nxt, ga);
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "moe_qmm (tcgen05) launch: %s", cudaGetErrorString(e));
@@ -1029,15 +1048,7 @@ int launch(const void* x, const void* wq, const void* sc, const void* bi, const 
   // the matmul announced to follow this one: its tensor maps and block -> unit mapping ride along as a prefetch hint
   NextPlan nxt = {};
   CUtensorMap nw = tw, ns = ts, nb = tb;
-  if (t_next.valid) {
-    t_next.valid = false;
-    Plan np;
-    if (g_prefetch_next && t_next.K % kBK == 0 && make_plan(M, t_next.K, t_next.N, device, max_blocks, &np) &&
-        get_map(t_next.wq, t_next.N, t_next.K / 2, 0, &nw) && get_map(t_next.sc, t_next.N, t_next.K / kG, 1, &ns) &&
-        get_map(t_next.bi, t_next.N, t_next.K / kG, 1, &nb)) {
-      nxt.valid = 1; nxt.C = np.C; nxt.NT = np.NT; nxt.ctas = np.ctas;
-    }
-  }
+  take_next_hint(M, device, max_blocks, &nw, &ns, &nb, &nxt);
   if (g_ndq == 12) e = launch_variant<12>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi, nw, ns, nb, nxt);
   else e = launch_variant<8>(grid, st, device, tw, ts, tb, tx, bias, y, pieces, counters, plan, epi, nw, ns, nb, nxt);
   if (e == cudaSuccess) e = cudaGetLastError();

@@ -96,7 +96,7 @@ class MoEBlock:
         return self.ws.numel()
 
     def __call__(self, x: torch.Tensor, logits: torch.Tensor, gate_up: dict, down: dict, out: torch.Tensor, *,
-                 x_ep=None, out_ep=None) -> torch.Tensor:
+                 x_ep=None, out_ep=None, before_down=None) -> torch.Tensor:
         """x [T,H]; logits [T,E+1]; writes this rank's (partial) block output into ``out`` [T,H] and returns it.
         ``x_ep`` / ``out_ep`` (ctypes ``dflash_qmm_epilogue``; both or neither, needs ``self.epilogues``): epilogue of
         the gate|up matmul (mode 0 with ``in_ssq``: ``x`` is ``h * norm_weight``, the RMS factor is applied to the
@@ -125,6 +125,8 @@ class MoEBlock:
                        "dflash_moe_qmm(rows)")
         _lib.check(lib.dflash_moe_swiglu(self.gu.data_ptr(), self.wdense.data_ptr(), self.n_active.data_ptr(),
                                          self.act.data_ptr(), T, I, self.n_max, self.code, st), "dflash_moe_swiglu")
+        if before_down is not None:
+            before_down()        # e.g. the announcement of the matmul that follows the block (dflash_verify_qmm_prefetch_next)
         if out_ep is not None:
             _lib.check(lib.dflash_moe_qmm_fused(self.act.data_ptr(), down["w"].data_ptr(), down["s"].data_ptr(),
                                                 down["b"].data_ptr(), out.data_ptr(), T, rows_total, H, I, 2,

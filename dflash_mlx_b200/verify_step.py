@@ -269,6 +269,7 @@ class HybridVerifyModel:
         # DFLASH_QMM_PREFETCH_NEXT=0: no announcement of the following matmul (see _announce_next)
         self.prefetch_next = os.environ.get("DFLASH_QMM_PREFETCH_NEXT", "1") != "0"
         self._next_of, self._qmm_seq = {}, []
+        self._router_ids = {id(L["router"]["w"]) for L in self.w["layers"] if "router" in L}
         self._delta_is_full = False
         # router logits [layers, block, experts + 1] of another pass to route by instead of this pass's own (comparing two
         # formulations of one step: a near-tie in the top-k is a discontinuity, not an arithmetic difference)
@@ -357,10 +358,21 @@ class HybridVerifyModel:
             return
         nxt = self._next_of.get(id(W["w"]))
         if nxt is not None:
+            if id(W["w"]) in self._router_ids:
+                return          # the expert block follows the router and streams far more than L2 holds: see _after_experts
             self.lib.dflash_verify_qmm_prefetch_next(nxt["w"].data_ptr(), nxt["s"].data_ptr(), nxt["b"].data_ptr(),
                                                      nxt["w"].shape[1] * 8, nxt["w"].shape[0])
         elif self._qmm_seq is not None:
             self._qmm_seq.append(W)
+
+    def _after_experts(self, L):
+        """Announcement for the last matmul of an expert block (the summed down projection): the matmul that follows the
+        layer's router in the recorded order, i.e. the next layer's input projection or the lm_head."""
+        nxt = self._next_of.get(id(L["router"]["w"])) if self.prefetch_next else None
+        if nxt is None:
+            return None
+        return lambda: self.lib.dflash_verify_qmm_prefetch_next(nxt["w"].data_ptr(), nxt["s"].data_ptr(), nxt["b"].data_ptr(),
+                                                                nxt["w"].shape[1] * 8, nxt["w"].shape[0])
 
     def _close_qmm_sequence(self):
         if self._qmm_seq:
@@ -443,7 +455,7 @@ class HybridVerifyModel:
         """Expert block inside the fused chain: x = hw (h * post_norm weight), the RMS factor from ssq[1]; the summed
         down projection adds into h and leaves (h * next norm weight, partial sums of h^2) for the next matmul."""
         self.moe(self.hw, self.router_logits[i], L["experts_gate_up"], L["experts_down"], self.h,
-                 x_ep=self._ep_in(1, self.ssq_parts), out_ep=self._ep_residual(nxt_w, 0))
+                 x_ep=self._ep_in(1, self.ssq_parts), out_ep=self._ep_residual(nxt_w, 0), before_down=self._after_experts(L))
 
     def _moe_all_to_all(self, i, L):
         """The expert block with token dispatch and combine as all-to-all exchanges (the classic expert-parallel
