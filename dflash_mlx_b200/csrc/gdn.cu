@@ -530,11 +530,22 @@ bool get_replay_map(const void* ptr, int rows_bt, int heads, int inner, int T, i
 // so a replay of the tape still reproduces it bit for bit.  Lane l = 8 * (row within the warp) + c holds the 16-byte
 // chunks c, c + 8, c + 16, c + 24 of its row: global and shared accesses of 8 neighbouring lanes are contiguous.
 constexpr int kRecT = 16, kRecRows = 16;
-__global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
+// NORM: the gated RMSNorm that consumes y (runtime.py:445 of dflash-mlx) runs in the same launch.  The Dv / 16 blocks of a
+// head form one thread-block cluster and meet once, through distributed shared memory, to add up the 16-row partial
+// sums of y^2 per token; out[t, hv*Dv + d] = bf16(bf16(y) * inv_rms * w[d]) * silu(z[t, hv*Dv + d]).
+struct GdnNormArgs {
+  const __nv_bfloat16* z; long long z_ld; int z_off;
+  const __nv_bfloat16* w; __nv_bfloat16* out; long long out_ld; float eps;
+};
+__device__ __forceinline__ float bf_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <bool NORM>
+__global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a, const GdnNormArgs nm) {
   __shared__ __align__(16) float sk[kRecT][128];
   __shared__ __align__(16) float sq[kRecT][128];
   __shared__ float sv[kRecT][kRecRows];
   __shared__ float sg[kRecT], sb[kRecT], skq[kRecT];
+  __shared__ float sy[NORM ? kRecT : 1][kRecRows], ssq_part[kRecT], sinv[kRecT];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rsub = lane >> 3, cg = lane & 7;
   const int bh = blockIdx.y, b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
   const int row = blockIdx.x * kRecRows + warp * 4 + rsub;
@@ -574,6 +585,18 @@ __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
     g_r = a.g[idx];
     b_r = a.beta[idx];
   }
+  // what the output norm needs from global memory is requested now, behind the recurrence
+  float zpre[2] = {0.f, 0.f}, gwpre[2] = {0.f, 0.f};
+  if constexpr (NORM) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = u * 128 + tid, t = i >> 4, vrow = blockIdx.x * kRecRows + (i & 15);
+      if (t < T && vrow < a.Dv) {
+        zpre[u] = __bfloat162float(nm.z[((size_t)b * T + t) * nm.z_ld + nm.z_off + hv * a.Dv + vrow]);
+        gwpre[u] = __bfloat162float(nm.w[vrow]);
+      }
+    }
+  }
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int i = u * 128 + tid, t = i >> 4, c = i & 15;
@@ -604,13 +627,57 @@ __global__ void __launch_bounds__(128) gdn_record_fast_kernel(const GdnArgs a) {
   for (int t = 0; t < T; ++t) {
     float yv;
     const float dl = gdnstep::step(S2, sk[t], sq[t], cg, sg[t], sb[t], sv[t][warp * 4 + rsub], skq[t], yv);
-    if (cg == 0 && row_ok) {
-      const size_t idx = (((size_t)b * T + t) * a.Hv + hv) * a.Dv + row;
-      yg[idx] = __float2bfloat16_rn(yv);
-      a.tape[idx] = dl;
+    if (cg == 0) {
+      if (row_ok) {
+        const size_t idx = (((size_t)b * T + t) * a.Hv + hv) * a.Dv + row;
+        if (yg != nullptr) yg[idx] = __float2bfloat16_rn(yv);
+        a.tape[idx] = dl;
+      }
+      if constexpr (NORM) sy[t][warp * 4 + rsub] = row_ok ? bf_round(yv) : 0.f;   // y is a bf16 array in the reference
     }
   }
   if (row_ok) gdnstep::store_row8((float*)a.state_out + ((size_t)bh * a.Dv + row) * 128, cg, S2);
+  if constexpr (NORM) {
+    __syncthreads();
+    if (tid < kRecT) {
+      float sum = 0.f;
+      if (tid < T) {
+#pragma unroll
+        for (int r = 0; r < kRecRows; ++r) sum += sy[tid][r] * sy[tid][r];
+      }
+      ssq_part[tid] = sum;
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid < kRecT) {
+      float part[8], total = 0.f;
+      const uint32_t local = smem_u32(&ssq_part[tid]);
+#pragma unroll
+      for (unsigned rank = 0; rank < 8; ++rank) {  // all loads in flight together (a cluster has at most 8 blocks)
+        part[rank] = 0.f;
+        if (rank < gridDim.x) {
+          uint32_t remote;
+          asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[rank]) : "r"(remote));
+        }
+      }
+#pragma unroll
+      for (int rank = 0; rank < 8; ++rank) total += part[rank];  // fixed order: deterministic
+      sinv[tid] = rsqrtf(total / (float)a.Dv + nm.eps);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // done reading the others' shared memory
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = u * 128 + tid, t = i >> 4, r = i & 15, vrow = blockIdx.x * kRecRows + r;
+      if (t < T && vrow < a.Dv) {
+        const float n = bf_round(sy[t][r] * sinv[t] * gwpre[u]);
+        const float z = zpre[u];
+        nm.out[((size_t)b * T + t) * nm.out_ld + hv * a.Dv + vrow] = __float2bfloat16_rn(n * (z / (1.f + __expf(-z))));
+      }
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // nobody exits while a neighbour may still read
+  }
 }
 
 template <typename IT, typename ST, bool RECORD>
@@ -695,13 +762,42 @@ extern "C" int dflash_gdn_forward_tape(const void* q, const void* k, const void*
   if (int rc = check_common(a)) return rc;
   if (g_record_fast && !g_is_vector && mask == nullptr && Dk == 128 && in_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32 &&
       T >= 1 && T <= kRecT && a.vec_ok && ((uintptr_t)v & 1) == 0) {
-    cudaError_t e = launch_kernel(gdn_record_fast_kernel, dim3((Dv + kRecRows - 1) / kRecRows, B * Hv), dim3(128), 0,
-                                  (cudaStream_t)stream, a);
+    cudaError_t e = launch_kernel(gdn_record_fast_kernel<false>, dim3((Dv + kRecRows - 1) / kRecRows, B * Hv), dim3(128), 0,
+                                  (cudaStream_t)stream, a, GdnNormArgs{});
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "gdn_forward_tape launch: %s", cudaGetErrorString(e));
     return DFLASH_OK;
   }
   return launch_in<true>(a, in_dtype, state_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int dflash_gdn_forward_tape_norm_supported(int T, int Hk, int Hv, int Dk, int Dv, int in_dtype, int state_dtype) {
+  return (T >= 1 && T <= kRecT && Hk >= 1 && Hv >= 1 && Hv % Hk == 0 && Dk == 128 && Dv >= kRecRows && Dv % kRecRows == 0 &&
+          Dv <= 8 * kRecRows && in_dtype == DFLASH_BF16 && state_dtype == DFLASH_F32) ? 1 : 0;
+}
+
+extern "C" int dflash_gdn_forward_tape_norm(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                            const void* state_in, void* state_out, float* tape, const void* z, long long z_ld,
+                                            int z_off, const void* norm_w, void* out, long long out_ld, int B, int T, int Hk,
+                                            int Hv, int Dk, int Dv, float eps, int in_dtype, int state_dtype, void* stream) {
+  const int settled = t_state_settled;
+  t_state_settled = 0;
+  if (!q || !k || !v || !g || !beta || !state_in || !state_out || !tape || !z || !norm_w || !out)
+    return fail(DFLASH_ERR_BAD_ARG, "gdn_forward_tape_norm: null operand");
+  if (!dflash_gdn_forward_tape_norm_supported(T, Hk, Hv, Dk, Dv, in_dtype, state_dtype))
+    return fail(DFLASH_ERR_BAD_SHAPE, "gdn_forward_tape_norm: needs bf16 inputs, fp32 state, Dk = 128, Dv %% 16 == 0 and <= 128, <= 16 tokens");
+  GdnArgs a{q, k, v, g, beta, nullptr, state_in, state_out, nullptr, tape, nullptr, nullptr, B, T, T, Hk, Hv, Dk, Dv, 0,
+            (((uintptr_t)q | (uintptr_t)k) & 15) == 0, settled};
+  if (int rc = check_common(a)) return rc;
+  if (!a.vec_ok) return fail(DFLASH_ERR_MISALIGNED, "gdn_forward_tape_norm: q and k must be 16-byte aligned");
+  if (state_in == state_out || out_ld < (long long)Hv * Dv)
+    return fail(DFLASH_ERR_BAD_ARG, "gdn_forward_tape_norm: separate state buffers and out_ld >= Hv * Dv are required");
+  GdnNormArgs nm{(const __nv_bfloat16*)z, z_ld, z_off, (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)out, out_ld, eps};
+  const int nb = Dv / kRecRows;
+  cudaError_t e = launch_kernel_cluster(gdn_record_fast_kernel<true>, dim3(nb, B * Hv), dim3(128), nb, 0, (cudaStream_t)stream, a, nm);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DFLASH_ERR_LAUNCH, "gdn_forward_tape_norm launch: %s", cudaGetErrorString(e));
+  return DFLASH_OK;
 }
 
 extern "C" int dflash_tape_replay(const float* tape, const void* k, const float* g, const uint8_t* mask,

@@ -58,6 +58,8 @@ def _declare():
     d("dflash_verify_qmm_set_prefetch_next", None, [_i32])
     d("dflash_gdn_forward_set_kernel", None, [_i32])
     d("dflash_gdn_forward_state_is_settled", None, [])
+    d("dflash_gdn_forward_tape_norm_supported", _i32, [_i32] * 7)
+    d("dflash_gdn_forward_tape_norm", _i32, [_vp] * 9 + [_c.c_longlong, _i32, _vp, _vp, _c.c_longlong] + [_i32] * 6 + [_f32, _i32, _i32, _vp])
     d("dflash_verify_qmm_fused", _i32, [_vp] * 6 + [_i32] * 5 + [_c.POINTER(QmmEpilogue), _vp, _c.c_size_t, _vp])
     d("dflash_gdn_layer_supported", _i32, [_i32] * 8)
     d("dflash_gdn_layer", _i32, [_vp, _ll, _i32, _i32, _i32] + [_vp] * 14 + [_ll] + [_i32] * 6 + [_f32, _i32, _i32, _vp])
@@ -289,6 +291,13 @@ class HybridVerifyModel:
             self._a2a_recv = z(T, H)
         # DFLASH_GDN_FUSED=1: one launch per GatedDeltaNet layer between its projections instead of three (fewer launches,
         # but measured slower inside a step: its long blocks delay the next matmul's start)
+        # DFLASH_GDN_NORM_FUSED=1: the gated RMSNorm of the recurrence's output inside the record kernel, whose blocks
+        # then form clusters per head.  Off by default: one launch less per layer, but measured slower inside a step
+        # (6.58 against 6.31 ms: a launch of 8-block clusters waits for 8 free slots in one GPC while the neighbouring
+        # kernels drain, and pays two cluster barriers)
+        self.gdn_norm_fused = (os.environ.get("DFLASH_GDN_NORM_FUSED", "0") == "1" and bool(self.gdn_layers) and
+                               self.lib.dflash_gdn_forward_tape_norm_supported(T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
+                                                                               cfg.gdn_dv, _lib.BF16, _lib.F32) == 1)
         self.gdn_fused = (os.environ.get("DFLASH_GDN_FUSED", "0") == "1" and bool(self.gdn_layers) and
                           self.lib.dflash_gdn_layer_supported(T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv,
                                                               cfg.conv_kernel, _lib.BF16, _lib.F32) == 1)
@@ -617,15 +626,24 @@ class HybridVerifyModel:
                                                   self.tape_qkv[ig].data_ptr(), T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
                                                   cfg.gdn_dv, cfg.conv_kernel, cfg.eps, BF, st), "dflash_gdn_prep")
                     lib.dflash_gdn_forward_state_is_settled()     # the kernel before it is gdn_prep: it does not write the state
-                    self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
-                                                          self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
-                                                          self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
-                                                          self.gy.data_ptr(), self.tape[ig].data_ptr(), 1, T, cfg.gdn_k_heads,
-                                                          cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF, _lib.F32, st),
-                              "dflash_gdn_forward_tape")
-                    self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
-                                                       self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads, cfg.gdn_dv, cfg.eps, BF, st),
-                              "dflash_gated_rmsnorm")
+                    if self.gdn_norm_fused:
+                        # record pass + the gated RMSNorm of its output in one launch (clusters of Dv / 16 blocks)
+                        self._chk(lib.dflash_gdn_forward_tape_norm(
+                            self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(), self.tape_g[ig].data_ptr(),
+                            self.gbeta.data_ptr(), self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
+                            self.tape[ig].data_ptr(), self.proj.data_ptr(), ld, z_off, L["g_norm"].data_ptr(),
+                            self.mix_gdn.data_ptr(), self.mix_gdn.shape[1], 1, T, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk,
+                            cfg.gdn_dv, cfg.eps, BF, _lib.F32, st), "dflash_gdn_forward_tape_norm")
+                    else:
+                        self._chk(lib.dflash_gdn_forward_tape(self.gq.data_ptr(), self.tape_k[ig].data_ptr(), self.gv.data_ptr(),
+                                                              self.tape_g[ig].data_ptr(), self.gbeta.data_ptr(), None,
+                                                              self.state[cur][ig].data_ptr(), self.state[nxt][ig].data_ptr(),
+                                                              self.gy.data_ptr(), self.tape[ig].data_ptr(), 1, T,
+                                                              cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_dk, cfg.gdn_dv, 0, BF,
+                                                              _lib.F32, st), "dflash_gdn_forward_tape")
+                        self._chk(lib.dflash_gated_rmsnorm(self.gy.data_ptr(), self.proj.data_ptr(), ld, z_off,
+                                                           L["g_norm"].data_ptr(), self.mix_gdn.data_ptr(), T, cfg.gdn_v_heads,
+                                                           cfg.gdn_dv, cfg.eps, BF, st), "dflash_gated_rmsnorm")
                 if fused:
                     self._qmm_fused(self.mix_gdn, L["out_proj"], self.h, self._ep_residual(L["post_norm"], 1))
                 else:

@@ -187,6 +187,17 @@ DFLASH_API void dflash_gdn_forward_set_kernel(int mode);
  * not write state_in (true in a verify step, false when one call's state_out feeds the next call).  The low-latency record
  * kernel then requests the state rows before its wait on that kernel.  Results do not change. */
 DFLASH_API void dflash_gdn_forward_state_is_settled(void);
+/* dflash_gdn_forward_tape (low-latency record kernel: bf16 inputs, fp32 state, Dk = 128, Dv % 16 == 0 and <= 128, scalar
+ * gate, no mask, T <= 16) followed by the gated RMSNorm that consumes its output (runtime.py:445), in ONE launch: the
+ * Dv / 16 blocks of a head form a thread-block cluster and add up the norm's partial sums through distributed shared
+ * memory.  out[b*T + t, hv*Dv + d] = bf16(bf16(y) * rsqrt(mean y^2 + eps) * norm_w[d]) * silu(z[b*T + t, z_off + hv*Dv + d])
+ * (z: bf16 rows of z_ld elements, out: bf16 rows of out_ld elements); y itself is not stored.  State and tape are bit
+ * for bit those of dflash_gdn_forward_tape. */
+DFLASH_API int dflash_gdn_forward_tape_norm_supported(int T, int Hk, int Hv, int Dk, int Dv, int in_dtype, int state_dtype);
+DFLASH_API int dflash_gdn_forward_tape_norm(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                            const void* state_in, void* state_out, float* tape, const void* z, long long z_ld,
+                                            int z_off, const void* norm_w, void* out, long long out_ld, int B, int T, int Hk,
+                                            int Hv, int Dk, int Dv, float eps, int in_dtype, int state_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * verify_sdpa: exact softmax attention of 16 query rows per head over N keys (split-KV + combine).

@@ -73,6 +73,37 @@ def _torch_formulas(c, eps=1e-6):
     return dict(out=out.reshape(T, Hv * Dv), state=S, tape=torch.stack(tape), k=k, g=gate, new_conv=new_conv, qkv=qkv)
 
 
+def _run_record_norm(c):
+    """dflash_gdn_prep, then the record pass with the gated RMSNorm in the same launch."""
+    from dflash_mlx_b200 import _lib, verify_step
+    verify_step._declare()
+    lib = _lib.lib()
+    d = "cuda"
+    T, Hk, Hv, Dk, Dv, Kc, cd, ld = (c[k] for k in ("T", "Hk", "Hv", "Dk", "Dv", "Kc", "conv_dim", "ld"))
+    dev = {k: c[k].to(d) for k in ("proj", "conv_state", "conv_w", "A_log", "dt_bias", "g_norm", "state")}
+    z = lambda *s, dt=BF: torch.zeros(*s, dtype=dt, device=d)   # noqa: E731
+    o = dict(state=z(Hv, Dv, Dk, dt=torch.float32), tape=z(T, Hv, Dv, dt=torch.float32), k=z(T, Hk, Dk),
+             g=z(T, Hv, dt=torch.float32), new_conv=z(Kc - 1, cd), qkv=z(T, cd), out=z(T, Hv * Dv))
+    z_off = cd
+    b_off = z_off + Hv * Dv
+    a_off = b_off + Hv
+    st = torch.cuda.current_stream().cuda_stream
+    q, v, beta = z(T, Hk, Dk), z(T, Hv, Dv), z(T, Hv, dt=torch.float32)
+    rc = lib.dflash_gdn_prep(dev["proj"].data_ptr(), ld, z_off, b_off, a_off, dev["conv_state"].data_ptr(),
+                             dev["conv_w"].data_ptr(), None, dev["A_log"].data_ptr(), dev["dt_bias"].data_ptr(), q.data_ptr(),
+                             o["k"].data_ptr(), v.data_ptr(), o["g"].data_ptr(), beta.data_ptr(), o["new_conv"].data_ptr(),
+                             o["qkv"].data_ptr(), T, Hk, Hv, Dk, Dv, Kc, 1e-6, _lib.BF16, st)
+    assert rc == 0, lib.dflash_last_error_string()
+    rc = lib.dflash_gdn_forward_tape_norm(q.data_ptr(), o["k"].data_ptr(), v.data_ptr(), o["g"].data_ptr(), beta.data_ptr(),
+                                          dev["state"].data_ptr(), o["state"].data_ptr(), o["tape"].data_ptr(),
+                                          dev["proj"].data_ptr(), ld, z_off, dev["g_norm"].data_ptr(), o["out"].data_ptr(),
+                                          Hv * Dv, 1, T, Hk, Hv, Dk, Dv, 1e-6, _lib.BF16, _lib.F32, st)
+    assert rc == 0, lib.dflash_last_error_string()
+    torch.cuda.synchronize()
+    assert lib.dflash_device_error(0) == 0
+    return o
+
+
 def _run(c, fused):
     from dflash_mlx_b200 import _lib, verify_step
     verify_step._declare()
@@ -147,3 +178,34 @@ def test_refusals():
     assert lib.dflash_gdn_layer_supported(16, 16, 32, 128, 256, 4, _lib.BF16, _lib.F32) == 0     # Dv
     assert lib.dflash_gdn_layer_supported(17, 16, 32, 128, 128, 4, _lib.BF16, _lib.F32) == 0     # tokens
     assert lib.dflash_gdn_layer_supported(16, 16, 32, 128, 128, 4, _lib.BF16, _lib.BF16) == 0    # state dtype
+
+
+@pytest.mark.parametrize("T,Hk,Hv,Dv,Kc", [(16, 16, 32, 128, 4), (16, 2, 4, 128, 4), (7, 2, 2, 64, 3), (1, 1, 2, 16, 2),
+                                            (16, 4, 8, 96, 8)])
+def test_record_pass_with_the_output_norm_in_the_same_launch(T, Hk, Hv, Dv, Kc):
+    """dflash_gdn_forward_tape_norm against dflash_gdn_forward_tape + dflash_gated_rmsnorm: state and tape bit for bit, the
+    normed output up to the order in which the norm's sum of squares is added (last-bit differences on a few elements),
+    and against the torch formulas with the tolerances of the three-call path."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    c = _case(T, Hk, Hv, Dv, Kc, seed=300 + Hv + Dv + T)
+    two, three = _run_record_norm(c), _run(c, False)
+    for name in ("state", "tape", "k", "g", "new_conv", "qkv"):
+        assert torch.equal(two[name], three[name]), name
+    assert _rel(two["out"], three["out"]) <= 8e-3
+    assert float((two["out"].float() - three["out"].float()).abs().gt(0).float().mean()) <= 0.02
+    ref = _torch_formulas(c)
+    assert _rel(two["out"], ref["out"]) <= 1e-2 and _rel(two["state"], ref["state"]) <= 2e-3
+
+
+def test_record_norm_refusals():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from dflash_mlx_b200 import _lib, verify_step
+    verify_step._declare()
+    lib = _lib.lib()
+    assert lib.dflash_gdn_forward_tape_norm_supported(16, 16, 32, 128, 128, _lib.BF16, _lib.F32) == 1
+    assert lib.dflash_gdn_forward_tape_norm_supported(16, 16, 32, 128, 256, _lib.BF16, _lib.F32) == 0   # more than 8 blocks per head
+    assert lib.dflash_gdn_forward_tape_norm_supported(16, 16, 32, 64, 128, _lib.BF16, _lib.F32) == 0    # Dk
+    assert lib.dflash_gdn_forward_tape_norm_supported(17, 16, 32, 128, 128, _lib.BF16, _lib.F32) == 0   # tokens
+    assert lib.dflash_gdn_forward_tape_norm_supported(16, 16, 32, 128, 128, _lib.BF16, _lib.BF16) == 0  # state dtype
