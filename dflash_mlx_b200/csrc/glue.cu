@@ -680,6 +680,19 @@ __global__ void __launch_bounds__(256) moe_swiglu_kernel(const T* __restrict__ g
   const float w = wdense[t * n_max + slot];
   const T* g = gu + ((size_t)t * n_max + slot) * 2 * I;
   T* o = act + ((size_t)t * n_max + slot) * I;
+  if ((I & 7) == 0 && (((uintptr_t)gu | (uintptr_t)act) & 15) == 0) {   // 16-byte vectors: 8 channels per thread and trip
+    for (int i8 = threadIdx.x; i8 < (I >> 3); i8 += blockDim.x) {
+      const uint4 gv = *(const uint4*)(g + 8 * i8), uv = *(const uint4*)(g + I + 8 * i8);
+      const T* ge = (const T*)&gv;
+      const T* ue = (const T*)&uv;
+      T r[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        r[j] = (w == 0.f) ? fromf<T>(0.f) : fromf<T>(w * tof<T>(fromf<T>(silu(tof<T>(ge[j])) * tof<T>(ue[j]))));
+      *(uint4*)(o + 8 * i8) = *(const uint4*)r;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < I; i += blockDim.x)
     o[i] = (w == 0.f) ? fromf<T>(0.f) : fromf<T>(w * tof<T>(fromf<T>(silu(tof<T>(g[i])) * tof<T>(g[I + i]))));
 }
@@ -857,6 +870,7 @@ extern "C" int dflash_moe_swiglu(const void* gate_up, const float* wdense, const
   if (!gate_up || !wdense || !n_active || !act || T_rows < 1 || I < 1 || n_max < 1)
     return fail(DFLASH_ERR_BAD_ARG, "moe_swiglu: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
-  DFLASH_DISPATCH(dtype, (launch_kernel(moe_swiglu_kernel<T>, dim3(n_max, T_rows), dim3(256), 0, st, (const T*)gate_up, wdense,
+  const int threads = (I & 7) == 0 ? (I / 8 >= 256 ? 256 : (I / 8 + 31) / 32 * 32) : 256;
+  DFLASH_DISPATCH(dtype, (launch_kernel(moe_swiglu_kernel<T>, dim3(n_max, T_rows), dim3(threads), 0, st, (const T*)gate_up, wdense,
                                         n_active, (T*)act, T_rows, I, n_max)));
 }
